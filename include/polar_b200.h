@@ -1,0 +1,105 @@
+/*
+ * polar_b200.h -- C ABI of the B200 (sm_100a) PolarEngine quantized-linear kernels.
+ *
+ * Plain pointers and sizes only; no torch types.  Every function launches on the
+ * stream it is given and returns immediately (asynchronous with respect to the
+ * host), returning 0 on success or a negative PE_ERR_* code.  The caller owns all
+ * buffers, including outputs and scratch; nothing here allocates device memory
+ * unless its comment says so.  One caller thread per device.
+ *
+ * Reference interfaces these replace (paths inside caiovicentino/polarengine-vllm):
+ *   polarengine_vllm/kernels/polar_gemm.py:425-437   polar_matmul (dispatcher)
+ *   polarengine_vllm/kernels/polar_gemv.py:181-256   polar_gemv / polar_gemv_packed
+ *   polarengine_vllm/kernels/polar_gemv_splitk.py:421-569  split-K variants
+ *   polarengine_vllm/kernels/polar_gemm.py:312-418   polar_gemm / polar_gemm_packed
+ *   polarengine_vllm/kernels/fwht.py:77-108          fwht_matmul
+ *   polarengine_vllm/kernels/polar_gemv.py:263-283   pack_codes_int4
+ *   polarengine_vllm/kernels/cuda/polar_gemv_cuda.cu:261-349, fwht_cuda.cu:93-141
+ *                                                    (the optional pybind extension)
+ */
+#ifndef POLAR_B200_H
+#define POLAR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations / outputs */
+enum { PE_F32 = 0, PE_F16 = 1, PE_BF16 = 2 };
+
+/* what the activation pointer of pe_gemv / pe_gemm holds */
+enum {
+  PE_X_ROTATED = 0, /* already FWHT-128 rotated and zero padded to in_f_padded
+                       (the reference's `x_transformed`, fwht.py:102-108)        */
+  PE_X_RAW = 1      /* un-rotated activations with in_f valid columns; the kernel
+                       pads and rotates while staging (linear_method.py:186-197) */
+};
+
+/* error codes */
+enum {
+  PE_OK = 0,
+  PE_ERR_ARG = -1,       /* null pointer, bad enum, non-positive size            */
+  PE_ERR_SHAPE = -2,     /* in_f_padded not a multiple of 128, batch too large   */
+  PE_ERR_ALIGN = -3,     /* pointer / leading dimension not 16-byte aligned      */
+  PE_ERR_WORKSPACE = -4, /* scratch buffer too small                             */
+  PE_ERR_CUDA = -5,      /* a CUDA runtime call failed; see pe_last_cuda_error() */
+  PE_ERR_DEVICE = -6,    /* device is not sm_100                                  */
+  PE_ERR_LIMIT = -7      /* size beyond a compiled-in maximum                    */
+};
+
+int pe_version(void);
+const char* pe_error_string(int code);
+/* cudaError_t of the last failing runtime call made by this library on this thread */
+int pe_last_cuda_error(void);
+
+/* One-time per-device set-up (opt-in shared-memory sizes, SM count).  Safe to call
+ * repeatedly.  Makes `device` current.  No counterpart in the reference. */
+int pe_init(int device);
+
+/* ---- rotation ---------------------------------------------------------------
+ * x (batch, in_f) -> x_tf (batch, in_f_padded): zero pad to a multiple of 128 and
+ * rotate every 128-block by the normalised Hadamard matrix.
+ * Replaces fwht_matmul + F.pad (fwht.py:77-108, linear_method.py:194-196) and
+ * polarengine_cuda.fwht (fwht_cuda.cu:93-119).  ld_* are row strides in elements. */
+int pe_fwht128(const void* x, int x_dtype, int64_t ld_x, void* x_tf, int out_dtype, int64_t ld_out,
+               int batch, int in_f, int in_f_padded, void* stream);
+
+/* ---- nibble packing ---------------------------------------------------------
+ * int8 codes (out_f, in_f_padded) -> uint8 (out_f, in_f_padded/2), byte i of each
+ * 128-block = code[64+i] << 4 | code[i].  Replaces pack_codes_int4
+ * (polar_gemv.py:263-283) == pack_codes_half_block (packing.py:22-60). */
+int pe_pack_nibble(const int8_t* codes, uint8_t* packed, int64_t out_f, int64_t in_f_padded, void* stream);
+
+/* ---- decode-size matmul (batch <= 16) ----------------------------------------
+ * y[m, r] = sum_blk norm[r, blk] * sum_k ct_scaled[code[r, blk, k]] * FWHT(x)[m, blk, k]
+ * (+ bias[r]), fp32 accumulation, one launch, bit-reproducible from run to run.
+ *
+ *   codes   packed != 0: uint8 (out_f, in_f_padded/2) half-block nibbles
+ *           packed == 0: int8/uint8 (out_f, in_f_padded), one code per byte
+ *   ld_codes  row stride of codes in bytes (multiple of 16)
+ *   norms   fp16 (out_f, n_blocks), ld_norms row stride in elements
+ *   ct_scaled fp32 (n_levels), n_levels in 2..256 (<= 16 when packed)
+ *   x       (batch, *) row-major with row stride ld_x elements; x_kind says whether
+ *           it is rotated already (in_f_padded columns) or raw (in_f columns)
+ *   y       (batch, out_f) row stride ld_y elements, dtype y_dtype
+ *   bias    optional fp16 (out_f), may be NULL
+ *   workspace / workspace_bytes  scratch of at least pe_gemv_workspace_bytes(...);
+ *           its first use must follow a zero fill (cudaMemsetAsync) -- the kernel
+ *           leaves it zeroed again on exit, so it can be reused by later calls on
+ *           the same stream without refilling.
+ *
+ * Replaces polar_matmul's batch==1 branches and (for 2..16 rows) its GEMM branch
+ * (polar_gemm.py:485-534), plus the cast/bias epilogue of linear_method.py:214-221. */
+size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded);
+int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+            const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
+            int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+            int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POLAR_B200_H */

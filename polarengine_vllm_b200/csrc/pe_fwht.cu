@@ -1,0 +1,78 @@
+// Stand-alone rotation and nibble-packing kernels (small, HBM-trivial).
+#include "pe_common.cuh"
+
+namespace pe {
+
+// One warp per 128-block: pad, rotate (register + shuffle butterflies), convert, store.
+__global__ void __launch_bounds__(256) fwht128_kernel(const void* x, int x_dtype, int64_t ld_x, void* out,
+                                                      int out_dtype, int64_t ld_out, int batch, int in_f,
+                                                      int nb) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t total = (int64_t)batch * nb;
+  if (warp >= total) return;  // whole warps leave together
+  const int m = (int)(warp / nb), blk = (int)(warp - (int64_t)m * nb);
+  const bool vin = (ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  float v[4];
+  load4_as_float(x, x_dtype, (int64_t)m * ld_x, blk * kBlock + lane * 4, in_f, vin, v);
+  warp_fwht128(v, lane);
+  const int64_t o = (int64_t)m * ld_out + blk * kBlock + lane * 4;
+  const bool vout = (ld_out % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  if (vout && out_dtype == PE_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o) = make_float4(v[0], v[1], v[2], v[3]);
+  } else if (vout && out_dtype == PE_F16) {
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + o) = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) store_from_float(out, out_dtype, o + i, v[i]);
+  }
+}
+
+// One thread per 16 output bytes: 16 codes of the first half, 16 of the second half.
+__global__ void __launch_bounds__(256) pack_nibble_kernel(const int8_t* codes, uint8_t* packed, int64_t n_chunks) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_chunks) return;
+  // chunk i covers packed bytes [16 i, 16 i + 16): block = i / 4, offset (i % 4) * 16 inside its 64 bytes
+  const int64_t blk = i >> 2;
+  const int off = (int)(i & 3) * 16;
+  const uint4 lo = *reinterpret_cast<const uint4*>(codes + blk * kBlock + off);
+  const uint4 hi = *reinterpret_cast<const uint4*>(codes + blk * kBlock + 64 + off);
+  uint4 r;
+  r.x = (lo.x & 0x0f0f0f0fu) | ((hi.x & 0x0f0f0f0fu) << 4);
+  r.y = (lo.y & 0x0f0f0f0fu) | ((hi.y & 0x0f0f0f0fu) << 4);
+  r.z = (lo.z & 0x0f0f0f0fu) | ((hi.z & 0x0f0f0f0fu) << 4);
+  r.w = (lo.w & 0x0f0f0f0fu) | ((hi.w & 0x0f0f0f0fu) << 4);
+  *reinterpret_cast<uint4*>(packed + i * 16) = r;
+}
+
+}  // namespace pe
+
+using namespace pe;
+
+extern "C" int pe_fwht128(const void* x, int x_dtype, int64_t ld_x, void* x_tf, int out_dtype, int64_t ld_out,
+                          int batch, int in_f, int in_f_padded, void* stream) {
+  if (!x || !x_tf || batch < 1 || in_f < 1) return PE_ERR_ARG;
+  if (x_dtype < PE_F32 || x_dtype > PE_BF16 || out_dtype < PE_F32 || out_dtype > PE_BF16) return PE_ERR_ARG;
+  if (in_f_padded % kBlock || in_f > in_f_padded || in_f_padded - in_f >= kBlock) return PE_ERR_SHAPE;
+  if (ld_x < in_f || ld_out < in_f_padded) return PE_ERR_ARG;
+  const int nb = in_f_padded / kBlock;
+  const int64_t warps = (int64_t)batch * nb;
+  const int64_t blocks = (warps + 7) / 8;
+  if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
+  fwht128_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, x_dtype, ld_x, x_tf, out_dtype,
+                                                                                 ld_out, batch, in_f, nb);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
+
+extern "C" int pe_pack_nibble(const int8_t* codes, uint8_t* packed, int64_t out_f, int64_t in_f_padded, void* stream) {
+  if (!codes || !packed || out_f < 1 || in_f_padded < 1) return PE_ERR_ARG;
+  if (in_f_padded % kBlock) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(packed) & 15)) return PE_ERR_ALIGN;
+  const int64_t n_chunks = out_f * (in_f_padded / 32);
+  const int64_t blocks = (n_chunks + 255) / 256;
+  if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
+  pack_nibble_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, packed, n_chunks);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}

@@ -1,0 +1,537 @@
+// Decode-size quantized matmul (1..16 activation rows) for sm_100a.
+//
+//   y[m, r] = sum_blk norm[r, blk] * sum_k ct[code[r, blk, k]] * xt[m, blk, k]   (+ bias[r])
+//
+// The operand that costs anything is the code stream (0.5 or 1 byte per weight, read
+// once from HBM); everything else is arranged so that the SM never waits on it:
+//
+//  * One persistent CTA per SM, 16 warps.  The unit of work is a "step": one 16-row
+//    tile of the weight matrix times one 128-wide quantization block (1 KB of nibble
+//    codes, 2 KB of byte codes).  Steps are numbered (row-tile-of-256, block, warp) and
+//    the number line is cut into equal contiguous ranges, one per CTA, so every SM
+//    streams the same number of bytes whatever the layer shape is.
+//  * Lane (g, t) of a warp streams 16 B of row g and 16 B of row g+8 per step with
+//    128-bit non-allocating loads, several steps ahead of the math (register ring).
+//  * Centroids are looked up in a shared-memory table that is replicated per lane
+//    (entry e of lane l lives at table + e*256 + l*4), so 32 lanes with 32 different
+//    codes never collide on a bank.  The address is formed by ONE byte-permute from the
+//    code word and a per-lane base, which is why the table sits on a 64 KB boundary.
+//    Nibble-packed layers use a 256-entry table indexed by the whole byte whose entry is
+//    the fp16 pair (ct[lo], ct[hi]) = two weights per lookup.
+//  * The dot products run on the tensor cores (mma.sync m16n8k16, fp16 in, fp32 out):
+//    weights are the 16x16 A tile, up to 8 (or 2x8) activation rows are the B tile.
+//    The k index of the MMA is a free permutation, so a lookup result is used as it
+//    comes: for nibble layers the pair (k, k+64) of the half-block layout is one A
+//    register and the activations are staged in shared memory in the same pairing.
+//  * The block norm multiplies the 8-MMA partial sum of a block, not each weight.
+//  * Activations are staged per CTA into shared memory once: either already rotated
+//    (fp32, the reference's x_transformed) or raw fp16/bf16/fp32, in which case the
+//    zero-pad and the FWHT-128 happen in the staging warps (one launch per layer).
+//  * Split-K falls out of the range cut: a row tile whose blocks are spread over
+//    several CTAs gets one fp32 partial per CTA in scratch memory; the CTA that
+//    completes the tile (a counter per 16-row tile) sums the partials in CTA order,
+//    adds the bias, converts and stores.  No float atomics: results are bit-identical
+//    from run to run.  The counters return to zero, so the scratch is reusable.
+#include "pe_common.cuh"
+
+namespace pe {
+
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
+constexpr int kRowsPerCta = kWarps * 16;  // 256
+constexpr int kXRowBytes = 320;           // 256 B of activations + 64 B pad (bank spread)
+constexpr int kLutSpan = 65536;
+
+struct GemvArgs {
+  const uint8_t* codes; int64_t ld_codes;
+  const __half* norms; int64_t ld_norms;
+  const float* ct; int n_levels;
+  const void* x; int x_kind; int x_dtype; int64_t ld_x; int in_f;
+  void* y; int y_dtype; int64_t ld_y;
+  const __half* bias;
+  int batch, N, K, nb;
+  int n_rt16, n_rt256;
+  long long S;       // total steps = n_rt256 * nb * 16
+  int cap;           // activation slots resident in shared memory per phase
+  int max_slots;     // scratch partials per 16-row tile
+  float* ws_part; unsigned* ws_cnt;
+  unsigned dyn_bytes;
+};
+
+__device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// table lookup: address = {lane_base byte3, lane_base byte2, code byte, lane_base byte0}
+template <int BYTE>
+__device__ __forceinline__ uint32_t lut(uint32_t word, uint32_t lane_base) {
+  uint32_t addr, v;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(word), "r"(lane_base), "n"(0x7604 | (BYTE << 4)));
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+// low half of a, high half of b
+__device__ __forceinline__ uint32_t lo_hi(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, 0x7610;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+__device__ __forceinline__ long long range_start(long long S, int G, int c) { return S * (long long)c / G; }
+__device__ __forceinline__ int owner_of(long long S, int G, long long idx) { return (int)(((idx + 1) * G - 1) / S); }
+__device__ __forceinline__ int ceil_div16(long long v) { return v <= 0 ? 0 : (int)((v + 15) >> 4); }
+
+// block-step range [q_lo, q_hi) of warp w inside the CTA range [s, e), clipped to [cl, ch)
+__device__ __forceinline__ void warp_q_range(long long s, long long e, int w, int cl, int ch, int& q_lo, int& q_hi) {
+  q_lo = ceil_div16(s - w);
+  q_hi = ceil_div16(e - w);
+  if (q_lo < cl) q_lo = cl;
+  if (q_hi > ch) q_hi = ch;
+  if (q_hi < q_lo) q_hi = q_lo;
+}
+
+template <bool PACKED>
+struct CodeRegs {
+  uint4 a0, b0;  // rows g and g+8
+  uint4 a1, b1;  // second 16 B (byte codes only)
+};
+
+template <bool PACKED>
+__device__ __forceinline__ void fetch(CodeRegs<PACKED>& r, const GemvArgs& p, int rt256, int b, int w, int g, int t) {
+  int rowA = rt256 * kRowsPerCta + w * 16 + g;
+  int rowB = rowA + 8;
+  rowA = rowA < p.N ? rowA : p.N - 1;
+  rowB = rowB < p.N ? rowB : p.N - 1;
+  if (PACKED) {
+    const uint8_t* pa = p.codes + (int64_t)rowA * p.ld_codes + b * 64 + t * 16;
+    const uint8_t* pb = p.codes + (int64_t)rowB * p.ld_codes + b * 64 + t * 16;
+    r.a0 = ldg_stream(pa);
+    r.b0 = ldg_stream(pb);
+  } else {
+    const uint8_t* pa = p.codes + (int64_t)rowA * p.ld_codes + b * 128 + t * 32;
+    const uint8_t* pb = p.codes + (int64_t)rowB * p.ld_codes + b * 128 + t * 32;
+    r.a0 = ldg_stream(pa);
+    r.a1 = ldg_stream(pa + 16);
+    r.b0 = ldg_stream(pb);
+    r.b1 = ldg_stream(pb + 16);
+  }
+}
+
+// One MMA (16 rows x 16 k) from one 32-bit word of each row.
+//  PACKED: the word holds 4 bytes = two MMAs; HALF selects bytes {0,1} or {2,3}.
+//  !PACKED: the word holds the 4 codes of one MMA.
+template <bool PACKED, int HALF, int NB>
+__device__ __forceinline__ void mma_word(float d[NB / 2], uint32_t wa, uint32_t wb, uint32_t lane_base,
+                                         uint32_t x0, uint32_t x1, uint32_t y0, uint32_t y1) {
+  uint32_t a0, a1, a2, a3;
+  if (PACKED) {
+    a0 = lut<2 * HALF>(wa, lane_base);
+    a1 = lut<2 * HALF>(wb, lane_base);
+    a2 = lut<2 * HALF + 1>(wa, lane_base);
+    a3 = lut<2 * HALF + 1>(wb, lane_base);
+  } else {
+    a0 = lo_hi(lut<0>(wa, lane_base), lut<1>(wa, lane_base));
+    a1 = lo_hi(lut<0>(wb, lane_base), lut<1>(wb, lane_base));
+    a2 = lo_hi(lut<2>(wa, lane_base), lut<3>(wa, lane_base));
+    a3 = lo_hi(lut<2>(wb, lane_base), lut<3>(wb, lane_base));
+  }
+  mma16816(d, a0, a1, a2, a3, x0, x1);
+  if (NB == 16) mma16816(d + 4, a0, a1, a2, a3, y0, y1);
+}
+
+template <bool PACKED, int NB>
+__device__ __forceinline__ void step_math(float acc[NB / 2], const CodeRegs<PACKED>& r, uint32_t lane_base,
+                                          const uint8_t* xslot, float nA, float nB, int g, int t) {
+  // activation fragments of this block: 4 x 16 B per 8 rows of batch
+  uint4 xf[4], yf[4];
+  const uint8_t* xrow = xslot + g * kXRowBytes + t * 16;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    xf[j] = *reinterpret_cast<const uint4*>(xrow + j * 64);
+    if (NB == 16) yf[j] = *reinterpret_cast<const uint4*>(xrow + 8 * kXRowBytes + j * 64);
+    else yf[j] = make_uint4(0, 0, 0, 0);
+  }
+  float d[NB / 2];
+#pragma unroll
+  for (int i = 0; i < NB / 2; ++i) d[i] = 0.f;
+  if (PACKED) {
+    const uint32_t wa[4] = {r.a0.x, r.a0.y, r.a0.z, r.a0.w};
+    const uint32_t wb[4] = {r.b0.x, r.b0.y, r.b0.z, r.b0.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {  // word j -> MMAs 2j and 2j+1
+      mma_word<true, 0, NB>(d, wa[j], wb[j], lane_base, xf[j].x, xf[j].y, yf[j].x, yf[j].y);
+      mma_word<true, 1, NB>(d, wa[j], wb[j], lane_base, xf[j].z, xf[j].w, yf[j].z, yf[j].w);
+    }
+  } else {
+    const uint32_t wa[8] = {r.a0.x, r.a0.y, r.a0.z, r.a0.w, r.a1.x, r.a1.y, r.a1.z, r.a1.w};
+    const uint32_t wb[8] = {r.b0.x, r.b0.y, r.b0.z, r.b0.w, r.b1.x, r.b1.y, r.b1.z, r.b1.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {  // words 2j, 2j+1 -> MMAs 2j and 2j+1
+      mma_word<false, 0, NB>(d, wa[2 * j], wb[2 * j], lane_base, xf[j].x, xf[j].y, yf[j].x, yf[j].y);
+      mma_word<false, 0, NB>(d, wa[2 * j + 1], wb[2 * j + 1], lane_base, xf[j].z, xf[j].w, yf[j].z, yf[j].w);
+    }
+  }
+  acc[0] = fmaf(nA, d[0], acc[0]);
+  acc[1] = fmaf(nA, d[1], acc[1]);
+  acc[2] = fmaf(nB, d[2], acc[2]);
+  acc[3] = fmaf(nB, d[3], acc[3]);
+  if (NB == 16) {
+    acc[4] = fmaf(nA, d[4], acc[4]);
+    acc[5] = fmaf(nA, d[5], acc[5]);
+    acc[6] = fmaf(nB, d[6], acc[6]);
+    acc[7] = fmaf(nB, d[7], acc[7]);
+  }
+}
+
+// Final store of one element of a 16-row tile.
+__device__ __forceinline__ void emit(const GemvArgs& p, int row, int m, float v) {
+  if (row < p.N && m < p.batch) {
+    if (p.bias) v += __half2float(p.bias[row]);
+    store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + row, v);
+  }
+}
+
+// End of a run of blocks [.., ..) of one 16-row tile: either the whole K was ours
+// (store), or leave a partial and, if we complete the tile, reduce all partials.
+template <int NB>
+__device__ __forceinline__ void flush(const GemvArgs& p, float acc[NB / 2], int rt256, int w, int nblk, int G,
+                                      int cta, int lane, int g, int t) {
+  const int rt16 = rt256 * 16 + w;
+  const int row0 = rt16 * 16;
+  if (rt16 >= p.n_rt16) return;
+  if (nblk == p.nb) {
+#pragma unroll
+    for (int h = 0; h < NB / 8; ++h) {
+      emit(p, row0 + g, 8 * h + 2 * t, acc[4 * h + 0]);
+      emit(p, row0 + g, 8 * h + 2 * t + 1, acc[4 * h + 1]);
+      emit(p, row0 + g + 8, 8 * h + 2 * t, acc[4 * h + 2]);
+      emit(p, row0 + g + 8, 8 * h + 2 * t + 1, acc[4 * h + 3]);
+    }
+    return;
+  }
+  const long long span_lo = (long long)rt256 * p.nb * 16;
+  const long long span_hi = span_lo + (long long)p.nb * 16;
+  const int c_first = owner_of(p.S, G, span_lo);
+  const int c_last = owner_of(p.S, G, span_hi - 1);
+  const int tile_elems = 16 * p.batch;
+  float* mine = p.ws_part + ((int64_t)rt16 * p.max_slots + (cta - c_first)) * tile_elems;
+#pragma unroll
+  for (int h = 0; h < NB / 8; ++h) {
+    const int m0 = 8 * h + 2 * t;
+    if (m0 < p.batch) { mine[m0 * 16 + g] = acc[4 * h + 0]; mine[m0 * 16 + g + 8] = acc[4 * h + 2]; }
+    if (m0 + 1 < p.batch) { mine[(m0 + 1) * 16 + g] = acc[4 * h + 1]; mine[(m0 + 1) * 16 + g + 8] = acc[4 * h + 3]; }
+  }
+  __threadfence();
+  __syncwarp();
+  unsigned old = 0;
+  if (lane == 0) old = atomicAdd(p.ws_cnt + rt16, (unsigned)nblk);
+  old = __shfl_sync(0xffffffffu, old, 0);
+  if (old + (unsigned)nblk != (unsigned)p.nb) return;
+  __threadfence();
+  // this warp completed the tile: sum partials in CTA order (fixed, independent of arrival)
+  for (int e = lane; e < tile_elems; e += 32) {
+    float s = 0.f;
+    for (int c = c_first; c <= c_last; ++c) {
+      int qs, qe;
+      warp_q_range(range_start(p.S, G, c), range_start(p.S, G, c + 1), w, (int)(span_lo >> 4), (int)(span_hi >> 4), qs, qe);
+      if (qe > qs) s += __ldcg(p.ws_part + ((int64_t)rt16 * p.max_slots + (c - c_first)) * tile_elems + e);
+    }
+    emit(p, row0 + (e & 15), e >> 4, s);
+  }
+  if (lane == 0) p.ws_cnt[rt16] = 0;
+}
+
+// Stage activation slots [q0, q0+cnt) of this phase into shared memory.
+template <bool PACKED>
+__device__ void stage_x(const GemvArgs& p, uint8_t* xs, int q0, int cnt, int warp, int lane) {
+  const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
+  const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+  if (p.x_kind == PE_X_RAW) {
+    // one warp per (slot, activation row): load, pad, rotate, convert, place
+    for (int item = warp; item < cnt * p.batch; item += kWarps) {
+      const int s = item / p.batch, m = item - s * p.batch;
+      const int blk = (q0 + s) % p.nb;
+      float v[4];
+      load4_as_float(p.x, p.x_dtype, (int64_t)m * p.ld_x, blk * kBlock + lane * 4, p.in_f, vec_ok, v);
+      warp_fwht128(v, lane);
+      uint8_t* row = xs + s * slot_bytes + m * kXRowBytes;
+      if (PACKED) {
+        float o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        if (lane < 16) {  // pairs 4*lane..4*lane+3 = chunk `lane`
+          uint4 u = make_uint4(pack_half2(v[0], o[0]), pack_half2(v[1], o[1]), pack_half2(v[2], o[2]),
+                               pack_half2(v[3], o[3]));
+          const int c = lane;
+          *reinterpret_cast<uint4*>(row + ((c & 3) * 4 + (c >> 2)) * 16) = u;
+        }
+      } else {  // halves 4*lane..4*lane+3 = half of chunk lane/2
+        const int c = lane >> 1;
+        uint2 u = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+        *reinterpret_cast<uint2*>(row + ((c & 3) * 4 + (c >> 2)) * 16 + (lane & 1) * 8) = u;
+      }
+    }
+  } else {
+    // already rotated: one thread per 16-byte chunk
+    const int total = cnt * p.batch * 16;
+    for (int item = warp * 32 + lane; item < total; item += kThreads) {
+      const int c = item & 15;
+      const int sm = item >> 4;
+      const int s = sm / p.batch, m = sm - s * p.batch;
+      const int blk = (q0 + s) % p.nb;
+      const int64_t row_off = (int64_t)m * p.ld_x;
+      uint4 u;
+      float a[4], b[4];
+      if (PACKED) {
+        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 4 * c, p.K, vec_ok, a);
+        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 64 + 4 * c, p.K, vec_ok, b);
+        u = make_uint4(pack_half2(a[0], b[0]), pack_half2(a[1], b[1]), pack_half2(a[2], b[2]), pack_half2(a[3], b[3]));
+      } else {
+        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 8 * c, p.K, vec_ok, a);
+        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 8 * c + 4, p.K, vec_ok, b);
+        u = make_uint4(pack_half2(a[0], a[1]), pack_half2(a[2], a[3]), pack_half2(b[0], b[1]), pack_half2(b[2], b[3]));
+      }
+      *reinterpret_cast<uint4*>(xs + s * slot_bytes + m * kXRowBytes + ((c & 3) * 4 + (c >> 2)) * 16) = u;
+    }
+  }
+}
+
+// Stage the block norms of slots [q0, q0+cnt): norm_s[row][slot], row stride nstr halves.
+__device__ void stage_norms(const GemvArgs& p, __half* ns, int nstr, int q0, int cnt, int warp, int lane) {
+  for (int row = warp; row < kRowsPerCta; row += kWarps) {
+    for (int s = lane; s < cnt; s += 32) {
+      const int q = q0 + s;
+      const int rt256 = q / p.nb;
+      const int blk = q - rt256 * p.nb;
+      const int grow = rt256 * kRowsPerCta + row;
+      ns[row * nstr + s] = grow < p.N ? p.norms[(int64_t)grow * p.ld_norms + blk] : __float2half(0.f);
+    }
+  }
+}
+
+template <bool PACKED, int NB, int DEPTH>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int G = gridDim.x, cta = blockIdx.x;
+
+  // ---- this CTA's and this warp's share of the step line
+  const long long s_beg = range_start(p.S, G, cta), s_end = range_start(p.S, G, cta + 1);
+  const int Q0 = (int)(s_beg >> 4), Q1 = (int)((s_end + 15) >> 4);  // block-steps touched by the CTA
+  int q_lo, q_hi;
+  warp_q_range(s_beg, s_end, w, 0, p.n_rt256 * p.nb, q_lo, q_hi);
+
+  // ---- start the code stream before anything else
+  CodeRegs<PACKED> ring[DEPTH];
+  {
+    int rt = q_lo / p.nb, b = q_lo - rt * p.nb;
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (q_lo + d < q_hi) fetch<PACKED>(ring[d], p, rt, b, w, g, t);
+      if (++b == p.nb) { b = 0; ++rt; }
+    }
+  }
+
+  // ---- shared memory carve-up: [pad][table 64 KB-aligned][activation slots][norms]
+  const uint32_t s0 = smem_u32(smem);
+  // The table always owns a full 64 KB so that any code byte, valid or not, stays inside it.
+  const uint32_t lut_s = (s0 + kLutSpan - 1) & ~(uint32_t)(kLutSpan - 1);
+  uint8_t* lut_g = smem + (lut_s - s0);
+  const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
+  uint8_t* xs = lut_g + kLutSpan;
+  const int nstr = p.cap + 2;
+  __half* ns = reinterpret_cast<__half*>(xs + (size_t)p.cap * slot_bytes);
+
+  // ---- centroid table, replicated per lane
+  {
+    const int entries = PACKED ? 256 : p.n_levels;
+    for (int e = w; e < entries; e += kWarps) {
+      uint32_t v;
+      if (PACKED) {
+        const int lo = e & 15, hi = e >> 4;
+        v = pack_half2(lo < p.n_levels ? p.ct[lo] : 0.f, hi < p.n_levels ? p.ct[hi] : 0.f);
+      } else {
+        const float c = p.ct[e];
+        v = pack_half2(c, c);
+      }
+      *reinterpret_cast<uint32_t*>(lut_g + e * 256 + lane * 4) = v;
+    }
+  }
+  const uint32_t lane_base = lut_s + lane * 4;
+
+  float acc[NB / 2];
+#pragma unroll
+  for (int i = 0; i < NB / 2; ++i) acc[i] = 0.f;
+  int run = 0;  // blocks accumulated for the current row tile
+
+  int rt_c = q_lo / p.nb, b_c = q_lo - rt_c * p.nb;  // compute cursor
+  int rt_f = rt_c, b_f = b_c;                                                 // fetch cursor (DEPTH ahead)
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d)
+    if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+
+  int q = q_lo;
+  bool first_phase = true;
+  for (int ph = Q0; ph < Q1; ph += p.cap) {
+    const int cnt = (Q1 - ph) < p.cap ? (Q1 - ph) : p.cap;
+    if (!first_phase) __syncthreads();  // everyone done with the previous slots
+    stage_x<PACKED>(p, xs, ph, cnt, w, lane);
+    stage_norms(p, ns, nstr, ph, cnt, w, lane);
+    __syncthreads();
+    const int ph_end = ph + cnt;
+    if (!first_phase) {
+      // refill the ring after a phase break
+      int rt = rt_c, b = b_c;
+#pragma unroll
+      for (int d = 0; d < DEPTH; ++d) {
+        if (q + d < q_hi) fetch<PACKED>(ring[d], p, rt, b, w, g, t);
+        if (++b == p.nb) { b = 0; ++rt; }
+      }
+    }
+    first_phase = false;
+    const int q_stop = q_hi < ph_end ? q_hi : ph_end;
+    while (q < q_stop) {
+#pragma unroll
+      for (int d = 0; d < DEPTH; ++d) {
+        if (q < q_stop) {
+          const CodeRegs<PACKED> cur = ring[d];
+          // keep the ring full, but never past this phase when another one follows
+          // (its slots are refetched after the barrier)
+          if (q + DEPTH < q_hi && (q + DEPTH < ph_end || ph_end >= Q1)) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
+          if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+          const int slot = q - ph;
+          const float nA = __half2float(ns[(w * 16 + g) * nstr + slot]);
+          const float nB = __half2float(ns[(w * 16 + g + 8) * nstr + slot]);
+          step_math<PACKED, NB>(acc, cur, lane_base, xs + slot * slot_bytes, nA, nB, g, t);
+          ++run;
+          ++q;
+          if (++b_c == p.nb) {  // row tile finished on our side
+            flush<NB>(p, acc, rt_c, w, run, G, cta, lane, g, t);
+#pragma unroll
+            for (int i = 0; i < NB / 2; ++i) acc[i] = 0.f;
+            run = 0;
+            b_c = 0;
+            ++rt_c;
+          }
+        }
+      }
+    }
+    if (ph_end < Q1 && q < q_hi) {
+      // the ring was not refilled across the break: resynchronise the fetch cursor
+      rt_f = rt_c; b_f = b_c;
+#pragma unroll
+      for (int d = 0; d < DEPTH; ++d)
+        if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+    }
+  }
+  if (run > 0) flush<NB>(p, acc, rt_c, w, run, G, cta, lane, g, t);
+}
+
+// ---- host side -----------------------------------------------------------------
+
+static int pick_cap(int batch) { return batch <= 8 ? 32 : 16; }
+
+struct Plan {
+  int n_rt16, n_rt256, nb, G, cap, max_slots;
+  long long S;
+  size_t part_bytes, cnt_bytes;
+  unsigned dyn_bytes;
+};
+
+static Plan make_plan(int batch, int N, int K, int sms) {
+  Plan pl;
+  pl.nb = K / kBlock;
+  pl.n_rt16 = (N + 15) / 16;
+  pl.n_rt256 = (pl.n_rt16 + 15) / 16;
+  pl.S = (long long)pl.n_rt256 * pl.nb * 16;
+  long long g = pl.S / 16;
+  pl.G = (int)(g < sms ? (g < 1 ? 1 : g) : sms);
+  pl.cap = pick_cap(batch);
+  // CTAs that can share one row tile of 256: its nb*16 steps over ranges of S/G steps
+  long long per = pl.S / pl.G;
+  pl.max_slots = (int)(((long long)pl.nb * 16 + per - 1) / per) + 1;
+  if (pl.max_slots > pl.G) pl.max_slots = pl.G;
+  pl.part_bytes = (size_t)pl.n_rt16 * pl.max_slots * 16 * batch * sizeof(float);
+  pl.cnt_bytes = ((size_t)pl.n_rt16 * sizeof(unsigned) + 255) & ~(size_t)255;
+  const unsigned slot_bytes = ((batch + 7) & ~7) * kXRowBytes;
+  pl.dyn_bytes = kLutSpan /*worst-case alignment pad*/ + kLutSpan + pl.cap * slot_bytes + kRowsPerCta * (pl.cap + 2) * 2 + 64;
+  return pl;
+}
+
+// Scratch layout: [counters (n_rt16 x u32, padded to 256 B)][partials].  The size is
+// computed for the largest SM count this library supports so that it does not depend
+// on the device.
+static constexpr int kMaxSms = 256;
+
+}  // namespace pe
+
+using namespace pe;
+
+extern "C" size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded) {
+  if (batch < 1 || batch > 16 || out_f < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
+  size_t best = 0;
+  // max_slots grows with the CTA count; take the bound at kMaxSms
+  Plan pl = make_plan(batch, out_f, in_f_padded, kMaxSms);
+  best = pl.cnt_bytes + pl.part_bytes;
+  return best;
+}
+
+template <bool PACKED, int NB, int DEPTH>
+static int launch(const GemvArgs& a, int G, cudaStream_t st) {
+  auto kfn = gemv_kernel<PACKED, NB, DEPTH>;
+  static thread_local unsigned configured[16] = {0};
+  int dev = 0;
+  PE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 16 && configured[dev] < a.dyn_bytes) {
+    PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.dyn_bytes));
+    configured[dev] = a.dyn_bytes;
+  } else if (dev >= 16) {
+    PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.dyn_bytes));
+  }
+  kfn<<<G, kThreads, a.dyn_bytes, st>>>(a);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
+
+extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                       const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
+                       int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+                       int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!codes || !norms || !ct_scaled || !x || !y || !workspace) return PE_ERR_ARG;
+  if (batch < 1 || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
+  if (x_kind != PE_X_ROTATED && x_kind != PE_X_RAW) return PE_ERR_ARG;
+  if (x_dtype < PE_F32 || x_dtype > PE_BF16 || y_dtype < PE_F32 || y_dtype > PE_BF16) return PE_ERR_ARG;
+  if (n_levels < 2 || n_levels > 256 || (packed && n_levels > 16)) return PE_ERR_ARG;
+  if (batch > 16 || in_f_padded % kBlock) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15)) return PE_ERR_ALIGN;
+  if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  if (ld_x < (x_kind == PE_X_RAW ? in_f : in_f_padded) || ld_y < out_f) return PE_ERR_ARG;
+
+  const int sms = sm_count();
+  if (sms <= 0) return PE_ERR_CUDA;
+  if (sms > kMaxSms) return PE_ERR_LIMIT;
+  if ((long long)((out_f + 255) / 256) * (in_f_padded / kBlock) * 16 >= (1ll << 31) / kMaxSms) return PE_ERR_LIMIT;
+  Plan pl = make_plan(batch, out_f, in_f_padded, sms);
+  if (workspace_bytes < pl.cnt_bytes + pl.part_bytes) return PE_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 15) return PE_ERR_ALIGN;
+
+  GemvArgs a;
+  a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
+  a.norms = static_cast<const __half*>(norms); a.ld_norms = ld_norms;
+  a.ct = ct_scaled; a.n_levels = n_levels;
+  a.x = x; a.x_kind = x_kind; a.x_dtype = x_dtype; a.ld_x = ld_x; a.in_f = in_f;
+  a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  a.bias = static_cast<const __half*>(bias);
+  a.batch = batch; a.N = out_f; a.K = in_f_padded; a.nb = pl.nb;
+  a.n_rt16 = pl.n_rt16; a.n_rt256 = pl.n_rt256; a.S = pl.S; a.cap = pl.cap; a.max_slots = pl.max_slots;
+  a.ws_cnt = static_cast<unsigned*>(workspace);
+  a.ws_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.cnt_bytes);
+  a.dyn_bytes = pl.dyn_bytes;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (packed) return batch <= 8 ? launch<true, 8, 4>(a, pl.G, st) : launch<true, 16, 3>(a, pl.G, st);
+  return batch <= 8 ? launch<false, 8, 3>(a, pl.G, st) : launch<false, 16, 2>(a, pl.G, st);
+}

@@ -1,0 +1,105 @@
+"""Python face of the native matmul kernels, under the reference's function names.
+
+Reference: polarengine_vllm/kernels/polar_gemm.py:425-534 (``polar_matmul``),
+polar_gemv.py:181-283 (``polar_gemv``, ``polar_gemv_packed``, ``pack_codes_int4``),
+polar_gemv_splitk.py:421-569, polar_gemm.py:312-418.  Argument order and meaning are
+kept; every one of them ends in the same native entry point, which chooses its own
+split of the K range, so the split-K names are aliases.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _native as nv
+from .packing import pack_codes_half_block
+
+GEMV_MAX_BATCH = 16
+
+
+def pack_codes_int4(codes: torch.Tensor, block_size: int = 128) -> torch.Tensor:
+    return pack_codes_half_block(codes, block_size)
+
+
+def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scaled: torch.Tensor, x: torch.Tensor,
+                 rotated: bool, out_f: int, in_f: int, in_f_padded: int, out_dtype: torch.dtype = torch.float32,
+                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y (batch, out_f) for x (batch, in_f or in_f_padded); the single entry to the
+    native kernels used by everything else in the package."""
+    dev = nv.require_cuda(codes, norms, ct_scaled, x)
+    nv.ensure_init(dev)
+    if x.dim() != 2 or x.stride(1) != 1:
+        x = x.reshape(-1, x.shape[-1]).contiguous()
+    if norms.dtype != torch.float16:
+        norms = norms.to(torch.float16)
+    norms = norms.reshape(out_f, -1)
+    if norms.stride(1) != 1:
+        norms = norms.contiguous()
+    if codes.stride(-1) != 1:
+        codes = codes.contiguous()
+    ct = ct_scaled if ct_scaled.dtype == torch.float32 else ct_scaled.float()
+    if bias is not None and (bias.dtype != torch.float16 or not bias.is_contiguous()):
+        bias = bias.to(torch.float16).contiguous()
+    batch = x.shape[0]
+    y = torch.empty(batch, out_f, dtype=out_dtype, device=dev)
+    if batch == 0:
+        return y
+    l = nv.lib()
+    st = nv.stream_ptr(dev)
+    if batch <= GEMV_MAX_BATCH or not hasattr(l, "pe_gemm"):
+        need = l.pe_gemv_workspace_bytes(min(batch, GEMV_MAX_BATCH), out_f, in_f_padded)
+        ws = nv.gemv_scratch(dev, need)
+        for m0 in range(0, batch, GEMV_MAX_BATCH):
+            m1 = min(batch, m0 + GEMV_MAX_BATCH)
+            xs, ys = x[m0:m1], y[m0:m1]
+            nv.check(l.pe_gemv(codes.data_ptr(), int(packed), codes.stride(0) * codes.element_size(),
+                               norms.data_ptr(), norms.stride(0), ct.data_ptr(), ct.numel(),
+                               xs.data_ptr(), nv.PE_X_ROTATED if rotated else nv.PE_X_RAW, nv.dtype_code(xs),
+                               xs.stride(0), in_f, ys.data_ptr(), nv.dtype_code(ys), ys.stride(0),
+                               bias.data_ptr() if bias is not None else None, m1 - m0, out_f, in_f_padded,
+                               ws.data_ptr(), ws.numel(), st), "pe_gemv")
+        return y
+    from .gemm import quant_gemm
+    return quant_gemm(codes, packed, norms, ct, x, rotated, out_f, in_f, in_f_padded, y, bias)
+
+
+def polar_matmul(codes: Optional[torch.Tensor], x_transformed: torch.Tensor, norms: torch.Tensor,
+                 ct_scaled: torch.Tensor, out_f: int, in_f_padded: int, n_blocks: int, block_size: int = 128,
+                 packed: bool = False, packed_codes: Optional[torch.Tensor] = None,
+                 in_f_half: Optional[int] = None) -> torch.Tensor:
+    """fp32 product of rotated activations with a quantized weight.  A 1-D input
+    gives a 1-D output; a 2-D input keeps its batch dimension."""
+    if block_size != 128:
+        raise ValueError("block_size must be 128")
+    use_packed = bool(packed and packed_codes is not None and in_f_half is not None)
+    w = packed_codes if use_packed else codes
+    if w is None:
+        raise ValueError("codes (or packed_codes with packed=True) are required")
+    x2 = x_transformed.reshape(1, -1) if x_transformed.dim() == 1 else x_transformed
+    assert x2.shape[-1] == in_f_padded == n_blocks * block_size
+    y = quant_matmul(w, use_packed, norms, ct_scaled, x2, True, out_f, in_f_padded, in_f_padded)
+    return y.reshape(out_f) if x_transformed.dim() == 1 else y
+
+
+def polar_gemv(codes, x_transformed, norms, ct_scaled, out_f, in_f_padded, n_blocks, block_size=128):
+    return polar_matmul(codes, x_transformed.reshape(-1), norms, ct_scaled, out_f, in_f_padded, n_blocks, block_size)
+
+
+def polar_gemv_packed(codes_packed, x_transformed, norms, ct_scaled, out_f, in_f_half, n_blocks, block_size=128):
+    return polar_matmul(None, x_transformed.reshape(-1), norms, ct_scaled, out_f, 2 * in_f_half, n_blocks,
+                        block_size, True, codes_packed, in_f_half)
+
+
+def polar_gemm(codes, x_transformed, norms, ct_scaled, out_f, in_f_padded, n_blocks, block_size=128):
+    return polar_matmul(codes, x_transformed.reshape(-1, in_f_padded), norms, ct_scaled, out_f, in_f_padded,
+                        n_blocks, block_size)
+
+
+def polar_gemm_packed(codes_packed, x_transformed, norms, ct_scaled, out_f, in_f_half, n_blocks, block_size=128):
+    return polar_matmul(None, x_transformed.reshape(-1, 2 * in_f_half), norms, ct_scaled, out_f, 2 * in_f_half,
+                        n_blocks, block_size, True, codes_packed, in_f_half)
+
+
+polar_gemv_splitk = polar_gemv
+polar_gemv_packed_splitk = polar_gemv_packed

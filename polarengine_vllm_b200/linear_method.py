@@ -1,0 +1,114 @@
+"""Quantized linear layer behind vLLM's linear-method interface.
+
+Reference: polarengine_vllm/linear_method.py:59-258 (``PolarQuantLinearMethod``).
+Same three entry points and the same layer attributes (``codes`` / ``codes_packed``,
+``norms``, ``ct_scaled``, ``in_f``, ``out_f``, ``in_f_padded``, ``n_blocks``, ``bits``,
+``block_size``, ``packed``, ``in_f_half``); the forward keeps the reference's meaning
+(flatten, pad, rotate, multiply, cast to fp16, add ``bias.half()``) but is one native
+launch for up to 16 tokens: padding, rotation, dequantisation, dot products, the
+split-K reduction, the cast and the bias all happen inside ``pe_gemv``.
+
+Differences from the reference that a vLLM integrator should know:
+* the class derives from vLLM's ``LinearMethodBase`` when vLLM is importable, so the
+  loader calls ``process_weights_after_loading``;
+* ``codes`` and ``norms`` are non-trainable Parameters carrying ``input_dim`` /
+  ``output_dim`` / ``weight_loader`` attributes, sized from the per-rank partition
+  (``input_size_per_partition``, ``sum(output_partition_sizes)``) so tensor-parallel
+  shards load correctly; a row-parallel shard must cover whole 128-blocks.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from .fwht import FWHTCache, fwht128
+from .kernels import GEMV_MAX_BATCH, pack_codes_int4, quant_matmul
+from .utils import get_ct_scaled
+
+try:  # vLLM is optional: the class must stay importable for offline tooling
+    from vllm.model_executor.layers.linear import LinearMethodBase as _Base
+    from vllm.model_executor.utils import set_weight_attrs
+except Exception:  # pragma: no cover - exercised only without vLLM
+    class _Base:  # type: ignore[no-redef]
+        pass
+
+    def set_weight_attrs(weight: torch.Tensor, attrs: Optional[Dict[str, Any]]) -> None:
+        for k, v in (attrs or {}).items():
+            setattr(weight, k, v)
+
+
+class PolarQuantLinearMethod(_Base):
+    def __init__(self, block_size: int = 128, bits: int = 4, layer_meta: Optional[Dict[str, Any]] = None) -> None:
+        if block_size != 128:
+            raise ValueError("the B200 kernels support block_size 128 only")
+        self.block_size = block_size
+        self.bits = bits
+        self.layer_meta = layer_meta or {}
+        self._fwht_cache = FWHTCache()
+
+    # ------------------------------------------------------------------ weights
+    def create_weights(self, layer: torch.nn.Module, input_size_per_partition: int,
+                       output_partition_sizes: List[int], input_size: int, output_size: int,
+                       params_dtype: torch.dtype, **extra_weight_attrs: Any) -> None:
+        bs = self.block_size
+        in_f = int(input_size_per_partition)
+        out_f = int(sum(output_partition_sizes))
+        if in_f != input_size and in_f % bs:
+            raise ValueError(f"a K-shard of a PolarQuant layer must be a multiple of {bs}, got {in_f}")
+        padded = -(-in_f // bs) * bs
+        nblk = padded // bs
+        codes = torch.nn.Parameter(torch.zeros(out_f, padded, dtype=torch.int8), requires_grad=False)
+        norms = torch.nn.Parameter(torch.zeros(out_f, nblk, dtype=torch.float16), requires_grad=False)
+        attrs = {"input_dim": 1, "output_dim": 0}
+        if "weight_loader" in extra_weight_attrs:
+            attrs["weight_loader"] = extra_weight_attrs["weight_loader"]
+        set_weight_attrs(codes, attrs)
+        set_weight_attrs(norms, attrs)
+        layer.register_parameter("codes", codes)
+        layer.register_parameter("norms", norms)
+        layer.register_buffer("ct_scaled", get_ct_scaled(self.bits, bs).clone())
+        layer.in_f, layer.out_f = in_f, out_f
+        layer.in_f_padded, layer.n_blocks = padded, nblk
+        layer.bits, layer.block_size, layer.packed = self.bits, bs, False
+
+    def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
+        """Move the table next to the codes and nibble-pack widths <= 4 (native kernel)."""
+        dev = layer.codes.device if hasattr(layer, "codes") else layer.codes_packed.device
+        layer.ct_scaled = layer.ct_scaled.to(dev)
+        if layer.bits <= 4 and not getattr(layer, "packed", False):
+            packed = pack_codes_int4(layer.codes.data, layer.block_size)
+            if "codes" in layer._parameters:
+                del layer._parameters["codes"]
+            elif "codes" in layer._buffers:
+                del layer._buffers["codes"]
+            else:
+                del layer.codes
+            layer.codes_packed = packed
+            layer.in_f_half = layer.n_blocks * (layer.block_size // 2)
+            layer.packed = True
+
+    # ------------------------------------------------------------------ forward
+    def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, layer.in_f)
+        packed = bool(getattr(layer, "packed", False))
+        w = layer.codes_packed if packed else layer.codes
+        if x2.shape[0] <= GEMV_MAX_BATCH:
+            y = quant_matmul(w, packed, layer.norms, layer.ct_scaled, x2, False, layer.out_f, layer.in_f,
+                             layer.in_f_padded, torch.float16, bias)
+        else:
+            xt = self._fwht_cache.get(x, layer.in_f)
+            if xt is None:
+                xt = fwht128(x2, layer.in_f_padded, torch.bfloat16)
+                self._fwht_cache.put(x, layer.in_f, xt)
+            y = quant_matmul(w, packed, layer.norms, layer.ct_scaled, xt, True, layer.out_f, layer.in_f,
+                             layer.in_f_padded, torch.float16, bias)
+        return y.view(*lead, layer.out_f)
+
+
+def create_fwht_clear_hook(linear_method: PolarQuantLinearMethod):
+    """Forward pre-hook that empties the method's rotation memo (linear_method.py:265-288)."""
+    def hook(module: torch.nn.Module, args: Any) -> None:
+        linear_method._fwht_cache.clear()
+    return hook

@@ -1,0 +1,79 @@
+"""Offline producer of the kernels' inputs (reference: polarengine_vllm/quantizer.py:178-257).
+
+The codes a checkpoint carries depend on floating-point summation order, so
+``quantize_tensor`` performs the reference's torch operations in the reference's
+order (pad, block norm clamped at 1e-10, normalise, 64-row chunks of
+``(u @ H) * sqrt(block)``, first-minimum argmin of |r - c|).  On the CPU this
+reproduces reference checkpoints bit for bit.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Mapping, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .fwht import build_hadamard
+from .utils import DEFAULT_BIT_ASSIGNMENT, get_bits_for_layer, get_centroids
+from .packing import pack_codes_half_block, pack_codes_q5
+
+
+class PolarQuantizer:
+    def __init__(self, block_size: int = 128, bit_assignment: Optional[Mapping[str, int]] = None) -> None:
+        self.block_size = block_size
+        self.bit_assignment = dict(bit_assignment or DEFAULT_BIT_ASSIGNMENT)
+
+    def quantize_tensor(self, weight: torch.Tensor, bits: int) -> Dict[str, torch.Tensor]:
+        """(out_f, in_f) float -> codes int8 (out_f, in_f_padded), norms fp16
+        (out_f, n_blocks), ct_scaled fp32 (2**bits)."""
+        bs = self.block_size
+        dev = weight.device
+        levels = get_centroids(bits).to(dev)
+        had = build_hadamard(bs, dev)
+        rows, cols = weight.shape
+        padded = -(-cols // bs) * bs
+        nblk = padded // bs
+        w = weight.detach().float()
+        if padded != cols:
+            w = F.pad(w, (0, padded - cols))
+        blocks = w.view(rows, nblk, bs)
+        norms = blocks.norm(dim=2).clamp(min=1e-10)
+        unit = blocks / norms.unsqueeze(2)
+        codes = torch.empty(rows, nblk, bs, dtype=torch.int8, device=dev)
+        root = math.sqrt(bs)
+        lv = levels.view(1, 1, 1, -1)
+        for lo in range(0, rows, 64):
+            hi = min(lo + 64, rows)
+            rot = ((unit[lo:hi].reshape(-1, bs) @ had) * root).view(hi - lo, nblk, bs)
+            codes[lo:hi] = (rot.unsqueeze(-1) - lv).abs().argmin(dim=-1).to(torch.int8)
+        return {"codes": codes.reshape(rows, padded), "norms": norms.half(), "ct_scaled": levels / root}
+
+    def quantize_state_dict(self, state: Mapping[str, torch.Tensor], pack: bool = True):
+        """Quantize every eligible 2-D ``*.weight``; returns (tensors, polar_config dict)
+        in the on-disk naming of quantizer.py:341-403."""
+        out: Dict[str, torch.Tensor] = {}
+        layers: Dict[str, dict] = {}
+        any_q5 = False
+        for name, t in state.items():
+            bits = get_bits_for_layer(name, t, self.bit_assignment)
+            if bits == 16 or t.ndim != 2 or not name.endswith(".weight"):
+                out[name] = t.half() if t.is_floating_point() else t
+                continue
+            q = self.quantize_tensor(t, bits)
+            prefix = name[: -len(".weight")]
+            codes, is_packed, q5 = q["codes"], False, False
+            if pack and bits <= 4:
+                codes, is_packed = pack_codes_half_block(codes, self.block_size), True
+            elif pack and bits == 5:
+                codes, q5, any_q5 = pack_codes_q5(codes, self.block_size), True, True
+            out[prefix + ".codes"], out[prefix + ".norms"], out[prefix + ".ct_scaled"] = codes, q["norms"], q["ct_scaled"]
+            meta = {"in_features": t.shape[1], "out_features": t.shape[0],
+                    "in_features_padded": q["codes"].shape[1], "n_blocks": q["codes"].shape[1] // self.block_size,
+                    "bits": bits, "block_size": self.block_size, "packed": is_packed, "scale_dtype": "float16"}
+            if q5:
+                meta["packed_q5"] = True
+            layers[prefix] = meta
+        cfg = {"format": "polar_engine_v5" if any_q5 else "polar_engine_v4", "quantization": "polarengine",
+               "block_size": self.block_size, "bit_assignment": self.bit_assignment, "layers": layers}
+        return out, cfg
