@@ -87,9 +87,11 @@ int pe_pack_nibble(const int8_t* codes, uint8_t* packed, int64_t out_f, int64_t 
  *   y       (batch, out_f) row stride ld_y elements, dtype y_dtype
  *   bias    optional fp16 (out_f), may be NULL
  *   workspace / workspace_bytes  scratch of at least pe_gemv_workspace_bytes(...);
- *           its first use must follow a zero fill (cudaMemsetAsync) -- the kernel
- *           leaves it zeroed again on exit, so it can be reused by later calls on
- *           the same stream without refilling.
+ *           its first 256 KB hold per-tile counters that must read zero on entry
+ *           (zero-fill the buffer once after allocating it); every call returns
+ *           them to zero, so the buffer can be reused by later calls of any shape
+ *           on the same stream without refilling.  Calls that share a scratch
+ *           buffer must not overlap on the device.
  *
  * Replaces polar_matmul's batch==1 branches and (for 2..16 rows) its GEMM branch
  * (polar_gemm.py:485-534), plus the cast/bias epilogue of linear_method.py:214-221. */

@@ -51,7 +51,7 @@ struct GemvArgs {
   const __half* bias;
   int batch, N, K, nb;
   int n_rt16, n_rt256;
-  long long S;       // total steps = n_rt256 * nb * 16
+  int S;             // total steps = n_rt256 * nb * 16 (S * grid < 2^31)
   int cap;           // activation slots resident in shared memory per phase
   int max_slots;     // scratch partials per 16-row tile
   float* ws_part; unsigned* ws_cnt;
@@ -80,12 +80,13 @@ __device__ __forceinline__ uint32_t lo_hi(uint32_t a, uint32_t b) {
   return r;
 }
 
-__device__ __forceinline__ long long range_start(long long S, int G, int c) { return S * (long long)c / G; }
-__device__ __forceinline__ int owner_of(long long S, int G, long long idx) { return (int)(((idx + 1) * G - 1) / S); }
-__device__ __forceinline__ int ceil_div16(long long v) { return v <= 0 ? 0 : (int)((v + 15) >> 4); }
+// Step-line arithmetic.  The host guarantees S * G < 2^31, so 32-bit division is exact.
+__device__ __forceinline__ int range_start(int S, int G, int c) { return (int)((unsigned)S * (unsigned)c / (unsigned)G); }
+__device__ __forceinline__ int owner_of(int S, int G, int idx) { return (int)(((unsigned)(idx + 1) * (unsigned)G - 1u) / (unsigned)S); }
+__device__ __forceinline__ int ceil_div16(int v) { return v <= 0 ? 0 : (v + 15) >> 4; }
 
 // block-step range [q_lo, q_hi) of warp w inside the CTA range [s, e), clipped to [cl, ch)
-__device__ __forceinline__ void warp_q_range(long long s, long long e, int w, int cl, int ch, int& q_lo, int& q_hi) {
+__device__ __forceinline__ void warp_q_range(int s, int e, int w, int cl, int ch, int& q_lo, int& q_hi) {
   q_lo = ceil_div16(s - w);
   q_hi = ceil_div16(e - w);
   if (q_lo < cl) q_lo = cl;
@@ -212,8 +213,8 @@ __device__ __forceinline__ void flush(const GemvArgs& p, float acc[NB / 2], int 
     }
     return;
   }
-  const long long span_lo = (long long)rt256 * p.nb * 16;
-  const long long span_hi = span_lo + (long long)p.nb * 16;
+  const int span_lo = rt256 * p.nb * 16;
+  const int span_hi = span_lo + p.nb * 16;
   const int c_first = owner_of(p.S, G, span_lo);
   const int c_last = owner_of(p.S, G, span_hi - 1);
   const int tile_elems = 16 * p.batch;
@@ -234,9 +235,10 @@ __device__ __forceinline__ void flush(const GemvArgs& p, float acc[NB / 2], int 
   // this warp completed the tile: sum partials in CTA order (fixed, independent of arrival)
   for (int e = lane; e < tile_elems; e += 32) {
     float s = 0.f;
+#pragma unroll 4
     for (int c = c_first; c <= c_last; ++c) {
       int qs, qe;
-      warp_q_range(range_start(p.S, G, c), range_start(p.S, G, c + 1), w, (int)(span_lo >> 4), (int)(span_hi >> 4), qs, qe);
+      warp_q_range(range_start(p.S, G, c), range_start(p.S, G, c + 1), w, span_lo >> 4, span_hi >> 4, qs, qe);
       if (qe > qs) s += __ldcg(p.ws_part + ((int64_t)rt16 * p.max_slots + (c - c_first)) * tile_elems + e);
     }
     emit(p, row0 + (e & 15), e >> 4, s);
@@ -244,83 +246,132 @@ __device__ __forceinline__ void flush(const GemvArgs& p, float acc[NB / 2], int 
   if (lane == 0) p.ws_cnt[rt16] = 0;
 }
 
-// Stage activation slots [q0, q0+cnt) of this phase into shared memory.
+// Place one rotated 128-block (lane l holds elements 4l..4l+3) into its activation row.
 template <bool PACKED>
-__device__ void stage_x(const GemvArgs& p, uint8_t* xs, int q0, int cnt, int warp, int lane) {
+__device__ __forceinline__ void place_block(uint8_t* row, const float v[4], int lane) {
+  if (PACKED) {
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[i], 16);
+    if (lane < 16) {  // pairs (k, k+64) for k = 4*lane..4*lane+3 = chunk `lane`
+      const uint4 u = make_uint4(pack_half2(v[0], o[0]), pack_half2(v[1], o[1]), pack_half2(v[2], o[2]),
+                                 pack_half2(v[3], o[3]));
+      *reinterpret_cast<uint4*>(row + ((lane & 3) * 4 + (lane >> 2)) * 16) = u;
+    }
+  } else {  // halves 4*lane..4*lane+3 = half of chunk lane/2
+    const int c = lane >> 1;
+    const uint2 u = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+    *reinterpret_cast<uint2*>(row + ((c & 3) * 4 + (c >> 2)) * 16 + (lane & 1) * 8) = u;
+  }
+}
+
+// Stage the activation slots of this phase into shared memory.  slot_blk[s] is the
+// quantization block held by slot s.  Loads are issued in groups before any use so
+// that a warp pays one memory latency per group, not one per item.
+template <bool PACKED>
+__device__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* slot_blk, int cnt, int warp, int lane) {
   const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
   const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+  const int items = cnt * p.batch;
   if (p.x_kind == PE_X_RAW) {
     // one warp per (slot, activation row): load, pad, rotate, convert, place
-    for (int item = warp; item < cnt * p.batch; item += kWarps) {
-      const int s = item / p.batch, m = item - s * p.batch;
-      const int blk = (q0 + s) % p.nb;
-      float v[4];
-      load4_as_float(p.x, p.x_dtype, (int64_t)m * p.ld_x, blk * kBlock + lane * 4, p.in_f, vec_ok, v);
-      warp_fwht128(v, lane);
-      uint8_t* row = xs + s * slot_bytes + m * kXRowBytes;
-      if (PACKED) {
-        float o[4];
+    constexpr int U = 4;
+    for (int base = warp; base < items; base += kWarps * U) {
+      float v[U][4];
+      int sl[U], mm[U];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[i], 16);
-        if (lane < 16) {  // pairs 4*lane..4*lane+3 = chunk `lane`
-          uint4 u = make_uint4(pack_half2(v[0], o[0]), pack_half2(v[1], o[1]), pack_half2(v[2], o[2]),
-                               pack_half2(v[3], o[3]));
-          const int c = lane;
-          *reinterpret_cast<uint4*>(row + ((c & 3) * 4 + (c >> 2)) * 16) = u;
+      for (int u = 0; u < U; ++u) {
+        const int item = base + u * kWarps;
+        const bool on = item < items;
+        sl[u] = on ? item / p.batch : 0;
+        mm[u] = on ? item - sl[u] * p.batch : 0;
+        load4_as_float(p.x, p.x_dtype, (int64_t)mm[u] * p.ld_x, slot_blk[sl[u]] * kBlock + lane * 4,
+                       on ? p.in_f : 0, vec_ok, v[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (base + u * kWarps < items) {  // warp-uniform
+          warp_fwht128(v[u], lane);
+          place_block<PACKED>(xs + sl[u] * slot_bytes + mm[u] * kXRowBytes, v[u], lane);
         }
-      } else {  // halves 4*lane..4*lane+3 = half of chunk lane/2
-        const int c = lane >> 1;
-        uint2 u = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
-        *reinterpret_cast<uint2*>(row + ((c & 3) * 4 + (c >> 2)) * 16 + (lane & 1) * 8) = u;
       }
     }
   } else {
     // already rotated: one thread per 16-byte chunk
-    const int total = cnt * p.batch * 16;
-    for (int item = warp * 32 + lane; item < total; item += kThreads) {
-      const int c = item & 15;
-      const int sm = item >> 4;
-      const int s = sm / p.batch, m = sm - s * p.batch;
-      const int blk = (q0 + s) % p.nb;
-      const int64_t row_off = (int64_t)m * p.ld_x;
-      uint4 u;
-      float a[4], b[4];
-      if (PACKED) {
-        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 4 * c, p.K, vec_ok, a);
-        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 64 + 4 * c, p.K, vec_ok, b);
-        u = make_uint4(pack_half2(a[0], b[0]), pack_half2(a[1], b[1]), pack_half2(a[2], b[2]), pack_half2(a[3], b[3]));
-      } else {
-        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 8 * c, p.K, vec_ok, a);
-        load4_as_float(p.x, p.x_dtype, row_off, blk * kBlock + 8 * c + 4, p.K, vec_ok, b);
-        u = make_uint4(pack_half2(a[0], a[1]), pack_half2(a[2], a[3]), pack_half2(b[0], b[1]), pack_half2(b[2], b[3]));
+    const int total = items * 16;
+    constexpr int U = 2;
+    for (int base = warp * 32 + lane; base < total; base += kThreads * U) {
+      float a[U][4], b[U][4];
+      int dst[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int item = base + u * kThreads;
+        const bool on = item < total;
+        const int c = item & 15;
+        const int sm = on ? item >> 4 : 0;
+        const int sl = sm / p.batch, m = sm - sl * p.batch;
+        const int col = slot_blk[sl] * kBlock;
+        const int64_t row_off = (int64_t)m * p.ld_x;
+        const int lim = on ? p.K : 0;
+        if (PACKED) {
+          load4_as_float(p.x, p.x_dtype, row_off, col + 4 * c, lim, vec_ok, a[u]);
+          load4_as_float(p.x, p.x_dtype, row_off, col + 64 + 4 * c, lim, vec_ok, b[u]);
+        } else {
+          load4_as_float(p.x, p.x_dtype, row_off, col + 8 * c, lim, vec_ok, a[u]);
+          load4_as_float(p.x, p.x_dtype, row_off, col + 8 * c + 4, lim, vec_ok, b[u]);
+        }
+        dst[u] = on ? sl * slot_bytes + m * kXRowBytes + ((c & 3) * 4 + (c >> 2)) * 16 : -1;
       }
-      *reinterpret_cast<uint4*>(xs + s * slot_bytes + m * kXRowBytes + ((c & 3) * 4 + (c >> 2)) * 16) = u;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (dst[u] >= 0) {
+          uint4 r;
+          if (PACKED)
+            r = make_uint4(pack_half2(a[u][0], b[u][0]), pack_half2(a[u][1], b[u][1]), pack_half2(a[u][2], b[u][2]),
+                           pack_half2(a[u][3], b[u][3]));
+          else
+            r = make_uint4(pack_half2(a[u][0], a[u][1]), pack_half2(a[u][2], a[u][3]), pack_half2(b[u][0], b[u][1]),
+                           pack_half2(b[u][2], b[u][3]));
+          *reinterpret_cast<uint4*>(xs + dst[u]) = r;
+        }
+      }
     }
   }
 }
 
-// Stage the block norms of slots [q0, q0+cnt): norm_s[row][slot], row stride nstr halves.
-__device__ void stage_norms(const GemvArgs& p, __half* ns, int nstr, int q0, int cnt, int warp, int lane) {
-  for (int row = warp; row < kRowsPerCta; row += kWarps) {
-    for (int s = lane; s < cnt; s += 32) {
-      const int q = q0 + s;
-      const int rt256 = q / p.nb;
-      const int blk = q - rt256 * p.nb;
-      const int grow = rt256 * kRowsPerCta + row;
-      ns[row * nstr + s] = grow < p.N ? p.norms[(int64_t)grow * p.ld_norms + blk] : __float2half(0.f);
-    }
+// Stage the block norms of this phase: ns[row][slot], row stride nstr halves.  Thread
+// (row = idx / 32, slot = idx % 32): lanes walk the blocks of one weight row (adjacent
+// in memory); all 16 loads of a thread are in flight together.
+__device__ void stage_norms(const GemvArgs& p, __half* ns, int nstr, const int* slot_rt, const int* slot_blk, int cnt,
+                            int tid) {
+  constexpr int U = kRowsPerCta * 32 / kThreads;  // 16
+  const int s = tid & 31;
+  const bool on = s < cnt;
+  const int rt = on ? slot_rt[s] : 0, blk = on ? slot_blk[s] : 0;
+  unsigned short v[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int row = (tid >> 5) + u * kWarps;
+    const int grow = rt * kRowsPerCta + row;
+    v[u] = (on && grow < p.N) ? __ldg(reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)grow * p.ld_norms + blk)
+                              : (unsigned short)0;
+  }
+  if (on) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) reinterpret_cast<unsigned short*>(ns)[((tid >> 5) + u * kWarps) * nstr + s] = v[u];
   }
 }
 
 template <bool PACKED, int NB, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ int slot_rt[32], slot_blk[32];
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int G = gridDim.x, cta = blockIdx.x;
 
   // ---- this CTA's and this warp's share of the step line
-  const long long s_beg = range_start(p.S, G, cta), s_end = range_start(p.S, G, cta + 1);
+  const int s_beg = range_start(p.S, G, cta), s_end = range_start(p.S, G, cta + 1);
   const int Q0 = (int)(s_beg >> 4), Q1 = (int)((s_end + 15) >> 4);  // block-steps touched by the CTA
   int q_lo, q_hi;
   warp_q_range(s_beg, s_end, w, 0, p.n_rt256 * p.nb, q_lo, q_hi);
@@ -346,19 +397,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   const int nstr = p.cap + 2;
   __half* ns = reinterpret_cast<__half*>(xs + (size_t)p.cap * slot_bytes);
 
-  // ---- centroid table, replicated per lane
-  {
-    const int entries = PACKED ? 256 : p.n_levels;
-    for (int e = w; e < entries; e += kWarps) {
-      uint32_t v;
-      if (PACKED) {
-        const int lo = e & 15, hi = e >> 4;
-        v = pack_half2(lo < p.n_levels ? p.ct[lo] : 0.f, hi < p.n_levels ? p.ct[hi] : 0.f);
-      } else {
-        const float c = p.ct[e];
-        v = pack_half2(c, c);
-      }
-      *reinterpret_cast<uint32_t*>(lut_g + e * 256 + lane * 4) = v;
+  // ---- centroid table, replicated per lane.  Warp w writes entries w, w+16, ...; the
+  // levels come from one load per lane and travel by shuffle.
+  if (PACKED) {
+    const float mine = (lane & 15) < p.n_levels ? p.ct[lane & 15] : 0.f;
+    const float lo = __shfl_sync(0xffffffffu, mine, w);  // entry e = w + 16 i: low nibble w, high nibble i
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float hi = __shfl_sync(0xffffffffu, mine, i);
+      *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 256 + lane * 4) = pack_half2(lo, hi);
+    }
+  } else {
+    const int e_mine = w + 16 * (lane & 15);
+    const float mine = e_mine < p.n_levels ? p.ct[e_mine] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float c = __shfl_sync(0xffffffffu, mine, i);
+      if (w + 16 * i < p.n_levels) *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 256 + lane * 4) = pack_half2(c, c);
     }
   }
   const uint32_t lane_base = lut_s + lane * 4;
@@ -379,8 +434,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   for (int ph = Q0; ph < Q1; ph += p.cap) {
     const int cnt = (Q1 - ph) < p.cap ? (Q1 - ph) : p.cap;
     if (!first_phase) __syncthreads();  // everyone done with the previous slots
-    stage_x<PACKED>(p, xs, ph, cnt, w, lane);
-    stage_norms(p, ns, nstr, ph, cnt, w, lane);
+    if (tid < cnt) {
+      const int qq = ph + tid, r = qq / p.nb;
+      slot_rt[tid] = r;
+      slot_blk[tid] = qq - r * p.nb;
+    }
+    __syncthreads();
+    stage_norms(p, ns, nstr, slot_rt, slot_blk, cnt, tid);
+    stage_x<PACKED>(p, xs, slot_blk, cnt, w, lane);
     __syncthreads();
     const int ph_end = ph + cnt;
     if (!first_phase) {
@@ -435,6 +496,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
 
 static int pick_cap(int batch) { return batch <= 8 ? 32 : 16; }
 
+// Scratch layout: [tile counters, fixed 256 KB][fp32 partials].  The counter region has
+// the same size for every shape so that partials of one call can never land where a
+// later call of another shape keeps its counters (counters must read zero on entry and
+// are returned to zero; partials need no initial value).
+constexpr size_t kCounterBytes = 262144;
+constexpr int kMaxRowTiles = (int)(kCounterBytes / sizeof(unsigned));
+
 struct Plan {
   int n_rt16, n_rt256, nb, G, cap, max_slots;
   long long S;
@@ -456,15 +524,14 @@ static Plan make_plan(int batch, int N, int K, int sms) {
   pl.max_slots = (int)(((long long)pl.nb * 16 + per - 1) / per) + 1;
   if (pl.max_slots > pl.G) pl.max_slots = pl.G;
   pl.part_bytes = (size_t)pl.n_rt16 * pl.max_slots * 16 * batch * sizeof(float);
-  pl.cnt_bytes = ((size_t)pl.n_rt16 * sizeof(unsigned) + 255) & ~(size_t)255;
+  pl.cnt_bytes = kCounterBytes;
   const unsigned slot_bytes = ((batch + 7) & ~7) * kXRowBytes;
   pl.dyn_bytes = kLutSpan /*worst-case alignment pad*/ + kLutSpan + pl.cap * slot_bytes + kRowsPerCta * (pl.cap + 2) * 2 + 64;
   return pl;
 }
 
-// Scratch layout: [counters (n_rt16 x u32, padded to 256 B)][partials].  The size is
-// computed for the largest SM count this library supports so that it does not depend
-// on the device.
+// The scratch size is computed for the largest SM count this library supports so that
+// it does not depend on the device.
 static constexpr int kMaxSms = 256;
 
 }  // namespace pe
@@ -473,6 +540,7 @@ using namespace pe;
 
 extern "C" size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded) {
   if (batch < 1 || batch > 16 || out_f < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
+  if ((out_f + 15) / 16 > kMaxRowTiles) return 0;
   size_t best = 0;
   // max_slots grows with the CTA count; take the bound at kMaxSms
   Plan pl = make_plan(batch, out_f, in_f_padded, kMaxSms);
@@ -513,7 +581,7 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
 
   const int sms = sm_count();
   if (sms <= 0) return PE_ERR_CUDA;
-  if (sms > kMaxSms) return PE_ERR_LIMIT;
+  if (sms > kMaxSms || (out_f + 15) / 16 > kMaxRowTiles) return PE_ERR_LIMIT;
   if ((long long)((out_f + 255) / 256) * (in_f_padded / kBlock) * 16 >= (1ll << 31) / kMaxSms) return PE_ERR_LIMIT;
   Plan pl = make_plan(batch, out_f, in_f_padded, sms);
   if (workspace_bytes < pl.cnt_bytes + pl.part_bytes) return PE_ERR_WORKSPACE;
@@ -527,7 +595,7 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
   a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
   a.bias = static_cast<const __half*>(bias);
   a.batch = batch; a.N = out_f; a.K = in_f_padded; a.nb = pl.nb;
-  a.n_rt16 = pl.n_rt16; a.n_rt256 = pl.n_rt256; a.S = pl.S; a.cap = pl.cap; a.max_slots = pl.max_slots;
+  a.n_rt16 = pl.n_rt16; a.n_rt256 = pl.n_rt256; a.S = (int)pl.S; a.cap = pl.cap; a.max_slots = pl.max_slots;
   a.ws_cnt = static_cast<unsigned*>(workspace);
   a.ws_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.cnt_bytes);
   a.dyn_bytes = pl.dyn_bytes;
