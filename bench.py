@@ -1,0 +1,306 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear decode path: one "step" is one pass of the four
+projection launches of a 9B-class decoder layer (fused q/k/v 6144x4096 Q5, o 4096x4096
+Q6, fused gate/up 24576x4096 Q3, down 4096x12288 Q4; block 128, fp16 norms) over a
+batch of fp16 activations, rotating through a ring of layers larger than L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+Prints ONE JSON line.  `value` is algorithmic GB/s of the whole job with everything
+resident in HBM; `e2e` goes through linear_method.apply with host buffers; `roofline`
+is the dominant kernel (nibble-code GEMV) against the measured HBM copy bandwidth;
+`cpu_baseline` is the CPU oracle (the reference's torch math) on a bounded sample.
+With N > 1 (torchrun) every rank streams its own ring of layers (independent units, no
+collective on the data path): weak scaling.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, QKV = 4096, 12288, 6144
+# (name, out_f, in_f, bits)
+PROJ = [("qkv_proj", QKV, HIDDEN, 5), ("o_proj", HIDDEN, HIDDEN, 6),
+        ("gate_up_proj", 2 * INTER, HIDDEN, 3), ("down_proj", HIDDEN, INTER, 4)]
+NCU_DRAM_BYTES_DOWN_B1 = 26065664  # ncu capture of the down_proj launch, see profiles/
+RING = 8  # layers in the ring: 8 x 120.5 MB = 964 MB >> 126 MB of L2
+
+
+def alg_bytes(out_f, in_f, bits, batch):
+    """Algorithmic bytes of one launch: codes + fp16 norms + activations in/out + table."""
+    code = out_f * in_f // 2 if bits <= 4 else out_f * in_f
+    return code + out_f * (in_f // 128) * 2 + batch * in_f * 2 + batch * out_f * 2 + (1 << bits) * 4
+
+
+def step_bytes(batch):
+    return sum(alg_bytes(n, k, b, batch) for _, n, k, b in PROJ)
+
+
+def lloyd_max_boundaries(ct):
+    return (ct[1:] + ct[:-1]) / 2
+
+
+def make_layer(dev, seed):
+    """Synthetic quantized layer: codes are the Lloyd-Max cells of N(0,1) draws (the
+    distribution the quantizer produces for Gaussian weights), norms ~ 0.02*sqrt(128)."""
+    from polarengine_vllm_b200.utils import get_centroids, get_ct_scaled
+    from polarengine_vllm_b200.packing import pack_codes_half_block
+    g = torch.Generator(device=dev).manual_seed(seed)
+    out = {}
+    for name, n, k, bits in PROJ:
+        ct = get_centroids(bits).to(dev)
+        r = torch.randn(n, k, device=dev, generator=g)
+        codes = torch.bucketize(r, lloyd_max_boundaries(ct)).to(torch.int8)
+        del r
+        norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(n, k // 128, device=dev, generator=g))).half()
+        w = pack_codes_half_block(codes) if bits <= 4 else codes
+        out[name] = (w, bits <= 4, norms, get_ct_scaled(bits).to(dev), n, k)
+    return out
+
+
+class ClockSampler(threading.Thread):
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self.stop_flag = index, [], False
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag:
+            try:
+                o = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                   capture_output=True, text=True, timeout=5).stdout.strip()
+                if o:
+                    self.rows.append([c.strip() for c in o.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_baseline(batch, budget_s=12.0):
+    """The reference's CPU-runnable form of the path (rotate, gather centroids, scale by
+    norms, contract) timed on the host cores for whole layer passes until ~budget_s."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import polar_oracle as oracle
+    g = torch.Generator().manual_seed(0)
+    layers = []
+    for name, n, k, bits in PROJ:
+        codes = torch.randint(0, 1 << bits, (n, k), generator=g, dtype=torch.int16).to(torch.int8)
+        norms = (torch.rand(n, k // 128, generator=g) * 0.02 + 0.2).half()
+        layers.append((codes, norms, oracle.ct_scaled(bits), k))
+    x = {k: torch.randn(batch, k, generator=g).half() for k in (HIDDEN, INTER)}
+    def one_pass():
+        for codes, norms, cts, k in layers:
+            oracle.linear_hadamard_domain(x[k], codes, norms, cts)
+    one_pass()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        one_pass()
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 50:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": step_bytes(batch) * n / dt / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n} decoder-layer passes (4 projections, batch {batch}) of the CPU oracle in {dt:.1f} s"}, dt / n
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--warmup", type=int, default=40)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--probe", default=None, metavar="PROJ",
+                    help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": "decoder_layer_gemv (BASELINE configs[1]): q/k/v Q5 fused, o Q6, gate/up Q3 fused, down Q4; "
+                          "hidden 4096, intermediate 12288", "batch": a.batch, "ring_layers": RING,
+              "l2_defeat": "inputs larger than L2 (ring of 8 layers = 964 MB of codes)",
+              "parallelism": f"replicas x{a.gpus}: each rank streams its own layers, no collective"}
+    base = {"metric": "quantized GEMV HBM GB/s", "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": config}
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        # The reference has no CPU implementation of apply() (its Triton wrappers need a GPU);
+        # its CPU-runnable path is the torch math its kernels are tested against = the oracle.
+        cb, per_step = cpu_baseline(a.batch, budget_s=max(5.0, min(60.0, 0.3 * (a.steps + a.warmup))))
+        line = dict(base, impl="reference", value=cb["value"], ms_per_step=per_step * 1e3, cpu_baseline=cb, gpu_launches=0,
+                    e2e={"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from polarengine_vllm_b200 import kernels
+    from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
+
+    steps = max(RING, a.steps // RING * RING)
+    warm = max(3, a.warmup)
+    layers = [make_layer(dev, 1000 + 16 * i + 97 * rank) for i in range(RING)]
+    g = torch.Generator(device=dev).manual_seed(7)
+    xh = torch.randn(a.batch, HIDDEN, device=dev, generator=g).half()
+    xi = torch.randn(a.batch, INTER, device=dev, generator=g).half()
+    outs = {name: torch.empty(a.batch, n, dtype=torch.float16, device=dev) for name, n, _, _ in PROJ}
+
+    def launch(layer, name):
+        w, packed, norms, ct, n, k = layer[name]
+        return kernels.quant_matmul(w, packed, norms, ct, xh if k == HIDDEN else xi, False, n, k, k, torch.float16)
+
+    def ring_pass(names):
+        for layer in layers:
+            for name in names:
+                launch(layer, name)
+
+    all_names = [p[0] for p in PROJ]
+    if a.probe:
+        ring_pass([a.probe])
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": a.probe, "launches": RING, "batch": a.batch}))
+        return
+    stream = torch.cuda.Stream(dev)
+
+    def timed_graph(names, reps, warm_reps):
+        """Capture one ring pass (RING steps) as a CUDA graph and time `reps` replays."""
+        with torch.cuda.stream(stream):
+            ring_pass(names)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                ring_pass(names)
+            for _ in range(warm_reps):
+                graph.replay()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            return e0.elapsed_time(e1) / 1e3
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    elapsed = timed_graph(all_names, steps // RING, max(1, math.ceil(warm / RING)))
+    # dominant kernel alone: the nibble-code GEMV on the 4096x12288 Q4 layer (down_proj)
+    dom = ["down_proj"]
+    dom_elapsed = timed_graph(dom, steps // RING, 1)
+    sampler.stop_flag = True
+    if world > 1:
+        t = torch.tensor([elapsed], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed = float(t)
+    value = step_bytes(a.batch) * steps * world / elapsed / 1e9
+
+    # ---- end to end through the plugin surface with host buffers
+    method = {}
+    mods = {}
+    for name, n, k, bits in PROJ:
+        m = PolarQuantLinearMethod(128, bits)
+        mod = torch.nn.Module()
+        w, packed, norms, ct, _, _ = layers[0][name]
+        mod.in_f, mod.out_f, mod.in_f_padded, mod.n_blocks, mod.bits, mod.block_size = k, n, k, k // 128, bits, 128
+        mod.packed, mod.norms, mod.ct_scaled = packed, norms, ct
+        if packed:
+            mod.codes_packed, mod.in_f_half = w, k // 2
+        else:
+            mod.codes = w
+        method[name], mods[name] = m, mod
+    hx = {k: torch.randn(a.batch, k).half().pin_memory() for k in (HIDDEN, INTER)}
+    hy = torch.empty(a.batch, HIDDEN, dtype=torch.float16).pin_memory()
+    e2e_steps = min(steps, 200)
+
+    def e2e_step(i):
+        layer = layers[i % RING]
+        dx = {k: v.to(dev, non_blocking=True) for k, v in hx.items()}
+        y = None
+        for name, n, k, bits in PROJ:
+            mod = mods[name]
+            w, packed, norms, ct, _, _ = layer[name]
+            mod.norms = norms
+            if packed:
+                mod.codes_packed = w
+            else:
+                mod.codes = w
+            y = method[name].apply(mod, dx[k])
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(5):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_dt = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_dt = float(t)
+    e2e = {"value": step_bytes(a.batch) * e2e_steps * world / e2e_dt / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": a.batch * (HIDDEN + INTER) * 2, "d2h_bytes_per_step": a.batch * HIDDEN * 2,
+           "steps": e2e_steps, "api": "PolarQuantLinearMethod.apply x4 per step, pinned host in/out"}
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        dom_launches = steps
+        dom_bytes = sum(alg_bytes(n, k, b, a.batch) for nm, n, k, b in PROJ if nm in dom)
+        achieved = dom_bytes / (dom_elapsed / dom_launches) / 1e9
+        roofline = {"bound": "hbm", "kernel": "gemv_kernel<packed> on down_proj 4096x12288 Q4", "achieved": achieved,
+                    "peak": peak, "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
+                    "unit": "GB/s", "frac": achieved / peak, "avg_launch_us": dom_elapsed / dom_launches * 1e6,
+                    "alg_bytes_per_launch": dom_bytes,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one batch-1 launch (profiles/)
+                    "traffic": NCU_DRAM_BYTES_DOWN_B1 if a.batch == 1 else None}
+        line = dict(base, value=value, ms_per_step=elapsed / steps * 1e3, steps=steps, e2e=e2e, gpu_launches=4 * steps,
+                    roofline=roofline, clocks=sampler.summary(),
+                    frac_of_measured_hbm=value / world / peak)
+        if not a.no_cpu_baseline:
+            line["cpu_baseline"], _ = cpu_baseline(a.batch)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

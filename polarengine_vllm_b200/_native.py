@@ -36,7 +36,8 @@ SIGNATURES = {
 
 
 def library_path() -> str:
-    return os.path.join(os.path.dirname(os.path.abspath(__file__)), _LIB_NAME)
+    """The in-tree build; POLAR_B200_LIB points developers at an instrumented build."""
+    return os.environ.get("POLAR_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), _LIB_NAME)
 
 
 def lib() -> ctypes.CDLL:

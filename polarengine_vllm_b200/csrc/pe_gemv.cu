@@ -56,7 +56,14 @@ struct GemvArgs {
   int max_slots;     // scratch partials per 16-row tile
   float* ws_part; unsigned* ws_cnt;
   unsigned dyn_bytes;
+  long long* prof;  // optional per-warp time stamps (developer builds with -DPE_PROFILE)
 };
+
+#ifdef PE_PROFILE
+#define PE_STAMP(i) do { if (p.prof && lane == 0) p.prof[((size_t)blockIdx.x * kWarps + w) * 8 + (i)] = clock64(); } while (0)
+#else
+#define PE_STAMP(i) do { } while (0)
+#endif
 
 __device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -65,14 +72,7 @@ __device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, u
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// table lookup: address = {lane_base byte3, lane_base byte2, code byte, lane_base byte0}
-template <int BYTE>
-__device__ __forceinline__ uint32_t lut(uint32_t word, uint32_t lane_base) {
-  uint32_t addr, v;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(word), "r"(lane_base), "n"(0x7604 | (BYTE << 4)));
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
+// A table address is {lane_base byte3, lane_base byte2, code byte, lane_base byte0}.
 // low half of a, high half of b
 __device__ __forceinline__ uint32_t lo_hi(uint32_t a, uint32_t b) {
   uint32_t r;
@@ -121,69 +121,130 @@ __device__ __forceinline__ void fetch(CodeRegs<PACKED>& r, const GemvArgs& p, in
   }
 }
 
-// One MMA (16 rows x 16 k) from one 32-bit word of each row.
-//  PACKED: the word holds 4 bytes = two MMAs; HALF selects bytes {0,1} or {2,3}.
-//  !PACKED: the word holds the 4 codes of one MMA.
-template <bool PACKED, int HALF, int NB>
-__device__ __forceinline__ void mma_word(float d[NB / 2], uint32_t wa, uint32_t wb, uint32_t lane_base,
-                                         uint32_t x0, uint32_t x1, uint32_t y0, uint32_t y1) {
-  uint32_t a0, a1, a2, a3;
+// table address of byte BYTE of a code word (see lut_ld)
+template <int BYTE>
+__device__ __forceinline__ uint32_t lut_addr(uint32_t word, uint32_t lane_base) {
+  uint32_t addr;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(word), "r"(lane_base), "n"(0x7604 | (BYTE << 4)));
+  return addr;
+}
+__device__ __forceinline__ uint32_t lut_ld(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// Four MMAs (16 rows x 64 k) from two code words of row g (wa) and of row g+8 (wb).
+// All 16 table addresses are formed first, then the 16 lookups are issued back to back,
+// then the MMAs alternate between two accumulator sets so that none waits on its
+// predecessor.
+//  PACKED: word i holds bytes for MMAs 2i (bytes 0,1) and 2i+1 (bytes 2,3).
+//  !PACKED: the caller passes four words per row; word i is MMA i (codes 0,1 | 2,3).
+template <bool PACKED, int NB>
+__device__ __forceinline__ void quad_mma(float d0[NB / 2], float d1[NB / 2], const uint32_t* wa, const uint32_t* wb,
+                                         uint32_t lane_base, const uint4& xa, const uint4& xb, const uint4& ya,
+                                         const uint4& yb) {
+  uint32_t ad[16], v[16];
   if (PACKED) {
-    a0 = lut<2 * HALF>(wa, lane_base);
-    a1 = lut<2 * HALF>(wb, lane_base);
-    a2 = lut<2 * HALF + 1>(wa, lane_base);
-    a3 = lut<2 * HALF + 1>(wb, lane_base);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      ad[8 * i + 0] = lut_addr<0>(wa[i], lane_base);
+      ad[8 * i + 1] = lut_addr<0>(wb[i], lane_base);
+      ad[8 * i + 2] = lut_addr<1>(wa[i], lane_base);
+      ad[8 * i + 3] = lut_addr<1>(wb[i], lane_base);
+      ad[8 * i + 4] = lut_addr<2>(wa[i], lane_base);
+      ad[8 * i + 5] = lut_addr<2>(wb[i], lane_base);
+      ad[8 * i + 6] = lut_addr<3>(wa[i], lane_base);
+      ad[8 * i + 7] = lut_addr<3>(wb[i], lane_base);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = lut_ld(ad[i]);
+    mma16816(d0, v[0], v[1], v[2], v[3], xa.x, xa.y);
+    mma16816(d1, v[4], v[5], v[6], v[7], xa.z, xa.w);
+    mma16816(d0, v[8], v[9], v[10], v[11], xb.x, xb.y);
+    mma16816(d1, v[12], v[13], v[14], v[15], xb.z, xb.w);
+    if (NB == 16) {
+      mma16816(d0 + 4, v[0], v[1], v[2], v[3], ya.x, ya.y);
+      mma16816(d1 + 4, v[4], v[5], v[6], v[7], ya.z, ya.w);
+      mma16816(d0 + 4, v[8], v[9], v[10], v[11], yb.x, yb.y);
+      mma16816(d1 + 4, v[12], v[13], v[14], v[15], yb.z, yb.w);
+    }
   } else {
-    a0 = lo_hi(lut<0>(wa, lane_base), lut<1>(wa, lane_base));
-    a1 = lo_hi(lut<0>(wb, lane_base), lut<1>(wb, lane_base));
-    a2 = lo_hi(lut<2>(wa, lane_base), lut<3>(wa, lane_base));
-    a3 = lo_hi(lut<2>(wb, lane_base), lut<3>(wb, lane_base));
+    // two MMAs at a time (16 lookups): words 0,1 then words 2,3
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t a = wa[2 * h + i], b = wb[2 * h + i];
+        ad[8 * i + 0] = lut_addr<0>(a, lane_base);
+        ad[8 * i + 1] = lut_addr<1>(a, lane_base);
+        ad[8 * i + 2] = lut_addr<0>(b, lane_base);
+        ad[8 * i + 3] = lut_addr<1>(b, lane_base);
+        ad[8 * i + 4] = lut_addr<2>(a, lane_base);
+        ad[8 * i + 5] = lut_addr<3>(a, lane_base);
+        ad[8 * i + 6] = lut_addr<2>(b, lane_base);
+        ad[8 * i + 7] = lut_addr<3>(b, lane_base);
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = lut_ld(ad[i]);
+      const uint4& xx = h ? xb : xa;
+      const uint4& yy = h ? yb : ya;
+      const uint32_t p0 = lo_hi(v[0], v[1]), p1 = lo_hi(v[2], v[3]), p2 = lo_hi(v[4], v[5]), p3 = lo_hi(v[6], v[7]);
+      const uint32_t r0 = lo_hi(v[8], v[9]), r1 = lo_hi(v[10], v[11]), r2 = lo_hi(v[12], v[13]), r3 = lo_hi(v[14], v[15]);
+      mma16816(d0, p0, p1, p2, p3, xx.x, xx.y);
+      mma16816(d1, r0, r1, r2, r3, xx.z, xx.w);
+      if (NB == 16) {
+        mma16816(d0 + 4, p0, p1, p2, p3, yy.x, yy.y);
+        mma16816(d1 + 4, r0, r1, r2, r3, yy.z, yy.w);
+      }
+    }
   }
-  mma16816(d, a0, a1, a2, a3, x0, x1);
-  if (NB == 16) mma16816(d + 4, a0, a1, a2, a3, y0, y1);
 }
 
 template <bool PACKED, int NB>
 __device__ __forceinline__ void step_math(float acc[NB / 2], const CodeRegs<PACKED>& r, uint32_t lane_base,
-                                          const uint8_t* xslot, float nA, float nB, int g, int t) {
-  // activation fragments of this block: 4 x 16 B per 8 rows of batch
+                                          const uint8_t* xslot, float nA, float nB, int g, int t, int batch) {
+  // activation fragments of this block: 4 x 16 B per 8 rows of batch.  Lanes whose batch
+  // row does not exist skip the load (their MMA columns are never read), which also
+  // shrinks the shared-memory transaction to the quarter-warps that hold live rows.
   uint4 xf[4], yf[4];
   const uint8_t* xrow = xslot + g * kXRowBytes + t * 16;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    xf[j] = *reinterpret_cast<const uint4*>(xrow + j * 64);
-    if (NB == 16) yf[j] = *reinterpret_cast<const uint4*>(xrow + 8 * kXRowBytes + j * 64);
-    else yf[j] = make_uint4(0, 0, 0, 0);
+    xf[j] = make_uint4(0, 0, 0, 0);
+    yf[j] = make_uint4(0, 0, 0, 0);
   }
-  float d[NB / 2];
+  if (g < batch) {
 #pragma unroll
-  for (int i = 0; i < NB / 2; ++i) d[i] = 0.f;
+    for (int j = 0; j < 4; ++j) xf[j] = *reinterpret_cast<const uint4*>(xrow + j * 64);
+  }
+  if (NB == 16 && g + 8 < batch) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) yf[j] = *reinterpret_cast<const uint4*>(xrow + 8 * kXRowBytes + j * 64);
+  }
+  float d0[NB / 2], d1[NB / 2];
+#pragma unroll
+  for (int i = 0; i < NB / 2; ++i) d0[i] = d1[i] = 0.f;
   if (PACKED) {
     const uint32_t wa[4] = {r.a0.x, r.a0.y, r.a0.z, r.a0.w};
     const uint32_t wb[4] = {r.b0.x, r.b0.y, r.b0.z, r.b0.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {  // word j -> MMAs 2j and 2j+1
-      mma_word<true, 0, NB>(d, wa[j], wb[j], lane_base, xf[j].x, xf[j].y, yf[j].x, yf[j].y);
-      mma_word<true, 1, NB>(d, wa[j], wb[j], lane_base, xf[j].z, xf[j].w, yf[j].z, yf[j].w);
-    }
+    quad_mma<true, NB>(d0, d1, wa, wb, lane_base, xf[0], xf[1], yf[0], yf[1]);
+    quad_mma<true, NB>(d0, d1, wa + 2, wb + 2, lane_base, xf[2], xf[3], yf[2], yf[3]);
   } else {
     const uint32_t wa[8] = {r.a0.x, r.a0.y, r.a0.z, r.a0.w, r.a1.x, r.a1.y, r.a1.z, r.a1.w};
     const uint32_t wb[8] = {r.b0.x, r.b0.y, r.b0.z, r.b0.w, r.b1.x, r.b1.y, r.b1.z, r.b1.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {  // words 2j, 2j+1 -> MMAs 2j and 2j+1
-      mma_word<false, 0, NB>(d, wa[2 * j], wb[2 * j], lane_base, xf[j].x, xf[j].y, yf[j].x, yf[j].y);
-      mma_word<false, 0, NB>(d, wa[2 * j + 1], wb[2 * j + 1], lane_base, xf[j].z, xf[j].w, yf[j].z, yf[j].w);
-    }
+    quad_mma<false, NB>(d0, d1, wa, wb, lane_base, xf[0], xf[1], yf[0], yf[1]);
+    quad_mma<false, NB>(d0, d1, wa + 4, wb + 4, lane_base, xf[2], xf[3], yf[2], yf[3]);
   }
-  acc[0] = fmaf(nA, d[0], acc[0]);
-  acc[1] = fmaf(nA, d[1], acc[1]);
-  acc[2] = fmaf(nB, d[2], acc[2]);
-  acc[3] = fmaf(nB, d[3], acc[3]);
+  acc[0] = fmaf(nA, d0[0] + d1[0], acc[0]);
+  acc[1] = fmaf(nA, d0[1] + d1[1], acc[1]);
+  acc[2] = fmaf(nB, d0[2] + d1[2], acc[2]);
+  acc[3] = fmaf(nB, d0[3] + d1[3], acc[3]);
   if (NB == 16) {
-    acc[4] = fmaf(nA, d[4], acc[4]);
-    acc[5] = fmaf(nA, d[5], acc[5]);
-    acc[6] = fmaf(nB, d[6], acc[6]);
-    acc[7] = fmaf(nB, d[7], acc[7]);
+    acc[4] = fmaf(nA, d0[4] + d1[4], acc[4]);
+    acc[5] = fmaf(nA, d0[5] + d1[5], acc[5]);
+    acc[6] = fmaf(nB, d0[6] + d1[6], acc[6]);
+    acc[7] = fmaf(nB, d0[7] + d1[7], acc[7]);
   }
 }
 
@@ -198,7 +259,7 @@ __device__ __forceinline__ void emit(const GemvArgs& p, int row, int m, float v)
 // End of a run of blocks [.., ..) of one 16-row tile: either the whole K was ours
 // (store), or leave a partial and, if we complete the tile, reduce all partials.
 template <int NB>
-__device__ __forceinline__ void flush(const GemvArgs& p, float acc[NB / 2], int rt256, int w, int nblk, int G,
+__device__ __noinline__ void flush(const GemvArgs& p, float acc[NB / 2], int rt256, int w, int nblk, int G,
                                       int cta, int lane, int g, int t) {
   const int rt16 = rt256 * 16 + w;
   const int row0 = rt16 * 16;
@@ -233,13 +294,21 @@ __device__ __forceinline__ void flush(const GemvArgs& p, float acc[NB / 2], int 
   if (old + (unsigned)nblk != (unsigned)p.nb) return;
   __threadfence();
   // this warp completed the tile: sum partials in CTA order (fixed, independent of arrival)
+  // (all loads of a group of eight partials are issued before the first add)
   for (int e = lane; e < tile_elems; e += 32) {
     float s = 0.f;
-#pragma unroll 4
-    for (int c = c_first; c <= c_last; ++c) {
-      int qs, qe;
-      warp_q_range(range_start(p.S, G, c), range_start(p.S, G, c + 1), w, span_lo >> 4, span_hi >> 4, qs, qe);
-      if (qe > qs) s += __ldcg(p.ws_part + ((int64_t)rt16 * p.max_slots + (c - c_first)) * tile_elems + e);
+    for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int c = c0 + u;
+        int qs = 0, qe = 0;
+        if (c <= c_last)
+          warp_q_range(range_start(p.S, G, c), range_start(p.S, G, c + 1), w, span_lo >> 4, span_hi >> 4, qs, qe);
+        v[u] = qe > qs ? __ldcg(p.ws_part + ((int64_t)rt16 * p.max_slots + (c - c_first)) * tile_elems + e) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
     }
     emit(p, row0 + (e & 15), e >> 4, s);
   }
@@ -269,7 +338,7 @@ __device__ __forceinline__ void place_block(uint8_t* row, const float v[4], int 
 // quantization block held by slot s.  Loads are issued in groups before any use so
 // that a warp pays one memory latency per group, not one per item.
 template <bool PACKED>
-__device__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* slot_blk, int cnt, int warp, int lane) {
+__device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* slot_blk, int cnt, int warp, int lane) {
   const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
   const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
   const int items = cnt * p.batch;
@@ -342,7 +411,7 @@ __device__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* slot_blk, int
 // Stage the block norms of this phase: ns[row][slot], row stride nstr halves.  Thread
 // (row = idx / 32, slot = idx % 32): lanes walk the blocks of one weight row (adjacent
 // in memory); all 16 loads of a thread are in flight together.
-__device__ void stage_norms(const GemvArgs& p, __half* ns, int nstr, const int* slot_rt, const int* slot_blk, int cnt,
+__device__ __noinline__ void stage_norms(const GemvArgs& p, __half* ns, int nstr, const int* slot_rt, const int* slot_blk, int cnt,
                             int tid) {
   constexpr int U = kRowsPerCta * 32 / kThreads;  // 16
   const int s = tid & 31;
@@ -369,105 +438,162 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int G = gridDim.x, cta = blockIdx.x;
+  PE_STAMP(0);
 
   // ---- this CTA's and this warp's share of the step line
   const int s_beg = range_start(p.S, G, cta), s_end = range_start(p.S, G, cta + 1);
-  const int Q0 = (int)(s_beg >> 4), Q1 = (int)((s_end + 15) >> 4);  // block-steps touched by the CTA
+  const int Q0 = s_beg >> 4, Q1 = (s_end + 15) >> 4;  // block-steps touched by the CTA
   int q_lo, q_hi;
   warp_q_range(s_beg, s_end, w, 0, p.n_rt256 * p.nb, q_lo, q_hi);
 
-  // ---- start the code stream before anything else
+  // ---- everything the prologue needs from memory is requested here, before any of it
+  // is used, so that the prologue costs one memory latency: codes, centroids, norms and
+  // the first group of activations.
   CodeRegs<PACKED> ring[DEPTH];
-  {
-    int rt = q_lo / p.nb, b = q_lo - rt * p.nb;
+  int rt_c = q_lo / p.nb, b_c = q_lo - rt_c * p.nb;  // compute cursor
+  int rt_f = rt_c, b_f = b_c;                        // fetch cursor
+  // Programmatic dependent launch: this grid may have been started while the previous
+  // kernel in the stream was still draining.  Weights, norms and centroids never change,
+  // so they are requested right away; the activations and the scratch buffer belong to
+  // the previous kernel until griddepcontrol.wait returns.
+  asm volatile("griddepcontrol.launch_dependents;");
+  float ct_mine;
+  if (PACKED) ct_mine = (lane & 15) < p.n_levels ? __ldg(p.ct + (lane & 15)) : 0.f;
+  else ct_mine = (w + 16 * (lane & 15)) < p.n_levels ? __ldg(p.ct + w + 16 * (lane & 15)) : 0.f;
+
+  const int cnt0 = (Q1 - Q0) < p.cap ? (Q1 - Q0) : p.cap;
+  // slot `lane` of the first phase
+  const int my_q = Q0 + lane;
+  const int my_rt = my_q / p.nb, my_blk = my_q - my_rt * p.nb;
+  constexpr int NU = kRowsPerCta * 32 / kThreads;  // norm loads per thread (16)
+  unsigned short nv[NU];
 #pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      if (q_lo + d < q_hi) fetch<PACKED>(ring[d], p, rt, b, w, g, t);
-      if (++b == p.nb) { b = 0; ++rt; }
-    }
+  for (int u = 0; u < NU; ++u) {
+    const int grow = my_rt * kRowsPerCta + w + u * kWarps;
+    nv[u] = (lane < cnt0 && grow < p.N)
+                ? __ldg(reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)grow * p.ld_norms + my_blk)
+                : (unsigned short)0;
+  }
+  // first activation item of this warp (raw input): slot = item / batch, row = item % batch
+  const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
+  const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+  const int items0 = cnt0 * p.batch;
+  float xv[4];
+  int x_sl = 0, x_m = 0;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (p.x_kind == PE_X_RAW) {
+    const bool on = w < items0;
+    x_sl = on ? w / p.batch : 0;
+    x_m = on ? w - x_sl * p.batch : 0;
+    const int qq = Q0 + x_sl;
+    load4_as_float(p.x, p.x_dtype, (int64_t)x_m * p.ld_x, (qq % p.nb) * kBlock + lane * 4, on ? p.in_f : 0, vec_ok, xv);
   }
 
+  // the code stream goes last: it is the bulk, and whatever is requested after it
+  // would queue behind megabytes of it in the memory system
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    if (q_lo + d < q_hi) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
+    if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+  }
+
+  PE_STAMP(7);
   // ---- shared memory carve-up: [pad][table 64 KB-aligned][activation slots][norms]
   const uint32_t s0 = smem_u32(smem);
   // The table always owns a full 64 KB so that any code byte, valid or not, stays inside it.
   const uint32_t lut_s = (s0 + kLutSpan - 1) & ~(uint32_t)(kLutSpan - 1);
   uint8_t* lut_g = smem + (lut_s - s0);
-  const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
   uint8_t* xs = lut_g + kLutSpan;
   const int nstr = p.cap + 2;
   __half* ns = reinterpret_cast<__half*>(xs + (size_t)p.cap * slot_bytes);
+  if (lane < cnt0 && w == 0) { slot_rt[lane] = my_rt; slot_blk[lane] = my_blk; }
 
   // ---- centroid table, replicated per lane.  Warp w writes entries w, w+16, ...; the
-  // levels come from one load per lane and travel by shuffle.
+  // levels came with one load per lane and travel by shuffle.
   if (PACKED) {
-    const float mine = (lane & 15) < p.n_levels ? p.ct[lane & 15] : 0.f;
-    const float lo = __shfl_sync(0xffffffffu, mine, w);  // entry e = w + 16 i: low nibble w, high nibble i
+    const float lo = __shfl_sync(0xffffffffu, ct_mine, w);  // entry e = w + 16 i: low nibble w, high nibble i
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float hi = __shfl_sync(0xffffffffu, mine, i);
+      const float hi = __shfl_sync(0xffffffffu, ct_mine, i);
       *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 256 + lane * 4) = pack_half2(lo, hi);
     }
   } else {
-    const int e_mine = w + 16 * (lane & 15);
-    const float mine = e_mine < p.n_levels ? p.ct[e_mine] : 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float c = __shfl_sync(0xffffffffu, mine, i);
+      const float c = __shfl_sync(0xffffffffu, ct_mine, i);
       if (w + 16 * i < p.n_levels) *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 256 + lane * 4) = pack_half2(c, c);
     }
   }
   const uint32_t lane_base = lut_s + lane * 4;
+  PE_STAMP(1);
+  if (lane < cnt0) {
+#pragma unroll
+    for (int u = 0; u < NU; ++u) reinterpret_cast<unsigned short*>(ns)[(w + u * kWarps) * nstr + lane] = nv[u];
+  }
+  PE_STAMP(2);
+  if (p.x_kind == PE_X_RAW) {
+    if (w < items0) {
+      warp_fwht128(xv, lane);
+      place_block<PACKED>(xs + x_sl * slot_bytes + x_m * kXRowBytes, xv, lane);
+    }
+    if (items0 > kWarps) {  // more than one item per warp: the rest, in groups
+      __syncthreads();      // slot table visible
+      stage_x<PACKED>(p, xs, slot_blk, cnt0, w + kWarps, lane);
+    }
+  } else {
+    __syncthreads();
+    stage_x<PACKED>(p, xs, slot_blk, cnt0, w, lane);
+  }
+  PE_STAMP(3);
 
   float acc[NB / 2];
 #pragma unroll
   for (int i = 0; i < NB / 2; ++i) acc[i] = 0.f;
   int run = 0;  // blocks accumulated for the current row tile
 
-  int rt_c = q_lo / p.nb, b_c = q_lo - rt_c * p.nb;  // compute cursor
-  int rt_f = rt_c, b_f = b_c;                                                 // fetch cursor (DEPTH ahead)
-#pragma unroll
-  for (int d = 0; d < DEPTH; ++d)
-    if (++b_f == p.nb) { b_f = 0; ++rt_f; }
-
   int q = q_lo;
   bool first_phase = true;
   for (int ph = Q0; ph < Q1; ph += p.cap) {
     const int cnt = (Q1 - ph) < p.cap ? (Q1 - ph) : p.cap;
-    if (!first_phase) __syncthreads();  // everyone done with the previous slots
-    if (tid < cnt) {
-      const int qq = ph + tid, r = qq / p.nb;
-      slot_rt[tid] = r;
-      slot_blk[tid] = qq - r * p.nb;
-    }
-    __syncthreads();
-    stage_norms(p, ns, nstr, slot_rt, slot_blk, cnt, tid);
-    stage_x<PACKED>(p, xs, slot_blk, cnt, w, lane);
-    __syncthreads();
     const int ph_end = ph + cnt;
     if (!first_phase) {
+      __syncthreads();  // everyone done with the previous slots
+      if (tid < cnt) {
+        const int qq = ph + tid, r = qq / p.nb;
+        slot_rt[tid] = r;
+        slot_blk[tid] = qq - r * p.nb;
+      }
+      __syncthreads();
+      stage_norms(p, ns, nstr, slot_rt, slot_blk, cnt, tid);
+      stage_x<PACKED>(p, xs, slot_blk, cnt, w, lane);
+    }
+    __syncthreads();
+    PE_STAMP(4);
+    if (!first_phase) {
       // refill the ring after a phase break
-      int rt = rt_c, b = b_c;
+      rt_f = rt_c; b_f = b_c;
 #pragma unroll
       for (int d = 0; d < DEPTH; ++d) {
-        if (q + d < q_hi) fetch<PACKED>(ring[d], p, rt, b, w, g, t);
-        if (++b == p.nb) { b = 0; ++rt; }
+        if (q + d < q_hi) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
+        if (++b_f == p.nb) { b_f = 0; ++rt_f; }
       }
     }
     first_phase = false;
     const int q_stop = q_hi < ph_end ? q_hi : ph_end;
+    const bool last_phase = ph_end >= Q1;
     while (q < q_stop) {
 #pragma unroll
       for (int d = 0; d < DEPTH; ++d) {
         if (q < q_stop) {
           const CodeRegs<PACKED> cur = ring[d];
           // keep the ring full, but never past this phase when another one follows
-          // (its slots are refetched after the barrier)
-          if (q + DEPTH < q_hi && (q + DEPTH < ph_end || ph_end >= Q1)) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
+          // (the ring is refilled after the barrier)
+          if (q + DEPTH < q_hi && (last_phase || q + DEPTH < ph_end)) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
           if (++b_f == p.nb) { b_f = 0; ++rt_f; }
           const int slot = q - ph;
           const float nA = __half2float(ns[(w * 16 + g) * nstr + slot]);
           const float nB = __half2float(ns[(w * 16 + g + 8) * nstr + slot]);
-          step_math<PACKED, NB>(acc, cur, lane_base, xs + slot * slot_bytes, nA, nB, g, t);
+          step_math<PACKED, NB>(acc, cur, lane_base, xs + slot * slot_bytes, nA, nB, g, t, p.batch);
           ++run;
           ++q;
           if (++b_c == p.nb) {  // row tile finished on our side
@@ -481,15 +607,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
         }
       }
     }
-    if (ph_end < Q1 && q < q_hi) {
-      // the ring was not refilled across the break: resynchronise the fetch cursor
-      rt_f = rt_c; b_f = b_c;
-#pragma unroll
-      for (int d = 0; d < DEPTH; ++d)
-        if (++b_f == p.nb) { b_f = 0; ++rt_f; }
-    }
   }
+  PE_STAMP(5);
   if (run > 0) flush<NB>(p, acc, rt_c, w, run, G, cta, lane, g, t);
+  PE_STAMP(6);
 }
 
 // ---- host side -----------------------------------------------------------------
@@ -538,6 +659,12 @@ static constexpr int kMaxSms = 256;
 
 using namespace pe;
 
+static long long* g_prof = nullptr;
+#ifdef PE_PROFILE
+// developer hook: device buffer of gridDim * 16 * 8 int64 receiving clock64 stamps
+extern "C" void pe_debug_set_profile_buffer(void* p) { g_prof = static_cast<long long*>(p); }
+#endif
+
 extern "C" size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded) {
   if (batch < 1 || batch > 16 || out_f < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
   if ((out_f + 15) / 16 > kMaxRowTiles) return 0;
@@ -560,8 +687,17 @@ static int launch(const GemvArgs& a, int G, cudaStream_t st) {
   } else if (dev >= 16) {
     PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.dyn_bytes));
   }
-  kfn<<<G, kThreads, a.dyn_bytes, st>>>(a);
-  PE_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(G);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = a.dyn_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, a));
   return PE_OK;
 }
 
@@ -599,6 +735,7 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
   a.ws_cnt = static_cast<unsigned*>(workspace);
   a.ws_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.cnt_bytes);
   a.dyn_bytes = pl.dyn_bytes;
+  a.prof = g_prof;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (packed) return batch <= 8 ? launch<true, 8, 4>(a, pl.G, st) : launch<true, 16, 3>(a, pl.G, st);
   return batch <= 8 ? launch<false, 8, 3>(a, pl.G, st) : launch<false, 16, 2>(a, pl.G, st);
