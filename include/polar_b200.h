@@ -101,6 +101,31 @@ int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, 
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
             int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- decode-size matmul without caller scratch ----------------------------------
+ * Same computation and arguments as pe_gemv, minus workspace / workspace_bytes.  It has
+ * no counterpart in the reference.  It is meant for integrations that are not in a
+ * position to allocate device memory when a layer runs: servers that give all free HBM
+ * to their own cache at start-up, after which an extra cudaMalloc may fail, and glue
+ * code that sits below the framework's allocator and cannot call it.  The scratch is an
+ * 8 MiB array inside the library image (pe_gemv_noalloc_max_bytes()); every GPU that
+ * loads the library holds those 8 MiB until the process exits.
+ *
+ *  - Shapes whose pe_gemv_workspace_bytes() exceeds the array return PE_ERR_LIMIT
+ *    (all 9B-class decoder projections at batch <= 16 fit; a 151,936-row head fits up
+ *    to batch 6).
+ *  - The call allocates nothing and frees nothing.  The first call on each device looks
+ *    up the array's device address (cudaGetSymbolAddress) with that device current;
+ *    make that first call outside of any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's
+ *    contents; the entry point clears the counters it needs, in stream order, before
+ *    the kernel.  Two calls that overlap on the GPU (different streams) race on it:
+ *    keep them on one stream or order them with events. */
+size_t pe_gemv_noalloc_max_bytes(void);
+int pe_gemv_noalloc(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                    const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
+                    int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+                    int in_f_padded, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

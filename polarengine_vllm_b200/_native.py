@@ -32,6 +32,9 @@ SIGNATURES = {
     "pe_gemv_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                      _vp, _sz, _vp]),
+    "pe_gemv_noalloc_max_bytes": (_sz, []),
+    "pe_gemv_noalloc": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
+                             _vp]),
 }
 
 
@@ -105,3 +108,4 @@ def gemv_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
         buf = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
+

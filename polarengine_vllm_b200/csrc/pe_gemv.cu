@@ -740,3 +740,44 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
   if (packed) return batch <= 8 ? launch<true, 8, 4>(a, pl.G, st) : launch<true, 16, 3>(a, pl.G, st);
   return batch <= 8 ? launch<false, 8, 3>(a, pl.G, st) : launch<false, 16, 2>(a, pl.G, st);
 }
+
+// ---- entry point for callers that cannot allocate device memory -------------------
+//
+// Some hosts of this library hand every byte of device memory to their own pool at
+// start-up (an inference server sizes its KV cache from "whatever is free" and keeps
+// it), so a cudaMalloc made later on behalf of one linear layer can fail, and the code
+// that calls into the layer has no allocator of its own to ask.  For them the split-K
+// scratch lives inside the library image: a fixed array in device global memory that
+// exists on every GPU that loads the library, from load until exit.
+constexpr size_t kNoAllocScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// In host code the array's name only stands for the symbol; the device address has to
+// be asked for, once per device, with that device current.
+static void* g_noalloc_ptr[64] = {nullptr};
+
+extern "C" size_t pe_gemv_noalloc_max_bytes(void) { return kNoAllocScratchBytes; }
+
+extern "C" int pe_gemv_noalloc(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                               const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype,
+                               int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch,
+                               int out_f, int in_f_padded, void* stream) {
+  const size_t need = pe_gemv_workspace_bytes(batch, out_f, in_f_padded);
+  if (need == 0) return batch > 16 || (in_f_padded % kBlock) ? PE_ERR_SHAPE : PE_ERR_ARG;
+  if (need > kNoAllocScratchBytes) return PE_ERR_LIMIT;  // shape needs more scratch than the built-in array holds
+  int dev = 0;
+  PE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return PE_ERR_LIMIT;
+  if (!g_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    PE_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = ptr;
+  }
+  void* ws = g_noalloc_ptr[dev];
+  // The array keeps whatever the previous call left.  Only the tile counters have to
+  // read zero on entry; clear the ones this shape uses, in stream order.
+  const size_t counter_bytes = (size_t)((out_f + 15) / 16) * sizeof(unsigned);
+  PE_CUDA_TRY(cudaMemsetAsync(ws, 0, counter_bytes, static_cast<cudaStream_t>(stream)));
+  return pe_gemv(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
+                 y_dtype, ld_y, bias, batch, out_f, in_f_padded, ws, kNoAllocScratchBytes, stream);
+}
