@@ -101,6 +101,22 @@ int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, 
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
             int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- prefill-size matmul (any number of rows; meant for m > 16) -------------------
+ * Same result as pe_gemv with the arguments in the same order; the contraction runs on
+ * tcgen05 tensor cores in bf16 with fp32 accumulation (activations and dequantised
+ * weights are rounded to bf16).  Two launches: activation preparation (pad, rotate when
+ * x_kind is PE_X_RAW, bf16) into the workspace, then the matmul.
+ *   workspace  at least pe_gemm_workspace_bytes(m, in_f_padded), 256-byte aligned.  Its
+ *              first int32 is a status word written by the kernel: 0 on success, 1..5
+ *              if a bounded device-side wait ran out (the output is then undefined).
+ * Replaces polar_matmul's batched branch: polar_gemm / polar_gemm_packed
+ * (polar_gemm.py:312-418, 526-534) and the epilogue of linear_method.py:214-221. */
+size_t pe_gemm_workspace_bytes(int m, int in_f_padded);
+int pe_gemm(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+            const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
+            int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int m, int out_f,
+            int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- decode-size matmul without caller scratch ----------------------------------
  * Same computation and arguments as pe_gemv, minus workspace / workspace_bytes.  It has
  * no counterpart in the reference.  It is meant for integrations that are not in a

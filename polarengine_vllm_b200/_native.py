@@ -32,6 +32,9 @@ SIGNATURES = {
     "pe_gemv_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                      _vp, _sz, _vp]),
+    "pe_gemm_workspace_bytes": (_sz, [_i, _i]),
+    "pe_gemm": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
+                     _vp, _sz, _vp]),
     "pe_gemv_noalloc_max_bytes": (_sz, []),
     "pe_gemv_noalloc": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                              _vp]),
@@ -109,3 +112,15 @@ def gemv_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
         _scratch[key] = buf
     return buf
 
+
+_gemm_ws = {}
+
+
+def gemm_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Grow-only per-(device, stream) buffer for pe_gemm (status word + bf16 activations)."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _gemm_ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes + (nbytes >> 2), dtype=torch.uint8, device=device)
+        _gemm_ws[key] = buf
+    return buf

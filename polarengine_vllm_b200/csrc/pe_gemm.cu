@@ -1,0 +1,493 @@
+// Prefill-size quantized matmul (many activation rows) on the 5th-generation tensor
+// cores: tcgen05.mma with TMEM accumulators, TMA-staged activations, in-kernel dequant.
+//
+//   Y[m, n] = sum_k Xt[m, k] * (ct[code[n, k]] * norm[n, k / 128])        (+ bias[n])
+//
+// A CTA owns a 256 (tokens) x 256 (weight rows) output tile and walks K in steps of 64:
+//   * warp 0, one lane: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) brings two
+//     128 x 64 bf16 activation tiles per step into shared memory;
+//   * warps 2..9 (256 threads, one weight row each): stream that row's codes, look the
+//     centroids up in a lane-replicated shared table, scale by the block norm (bf16x2
+//     multiply) and store the 256 x 64 bf16 weight tile in the same swizzled K-major
+//     layout the tensor core reads -- the decoded weights never touch HBM or L2;
+//   * warp 1, one lane: eight tcgen05.mma (128 x 256 x 16, bf16 in, fp32 accumulate) per
+//     step, two accumulators of 256 TMEM columns each (all 512 columns), commit to the
+//     stage's "empty" barrier;
+//   * after the last step the decode warps read the accumulators back (tcgen05.ld),
+//     add the bias, convert and store.
+// Decoding a weight tile once per 256 tokens keeps the table lookups at a quarter of
+// the shared-memory bandwidth; three 64 KB stages keep TMA, decode and MMA overlapped.
+// The activations are prepared by a small kernel (pad + FWHT-128 for raw input, bf16,
+// and for nibble layers the (k, k+64) pairing of the half-block layout so that one code
+// byte decodes to two adjacent K elements).
+//
+// Every wait is bounded: on time-out the kernel records a status code in the first word
+// of the workspace, all roles leave their loops, TMEM is released and the grid returns.
+#include <cuda.h>
+
+#include "pe_common.cuh"
+
+namespace pe {
+
+constexpr int kTileM = 256;          // tokens per CTA tile (two UMMA M=128 halves)
+constexpr int kTileN = 256;          // weight rows per CTA tile (UMMA N)
+constexpr int kStepK = 64;           // K elements per pipeline stage (128 bytes of bf16)
+constexpr int kStages = 3;
+constexpr int kXTileBytes = 128 * kStepK * 2;        // 16 KB
+constexpr int kWTileBytes = kTileN * kStepK * 2;     // 32 KB
+constexpr int kStageBytes = 2 * kXTileBytes + kWTileBytes;  // 64 KB
+constexpr int kLutBytes = 32768;                     // 256 entries x 32 lanes x 4 B
+constexpr int kGemmThreads = 320;                    // 10 warps
+constexpr int kDecodeThreads = 256;
+constexpr unsigned kGemmSmem = kStages * kStageBytes + kLutBytes + 256 + 1024 /*alignment slack*/;
+constexpr long long kTimeoutCycles = 1ll << 31;
+
+struct GemmArgs {
+  const uint8_t* codes; int64_t ld_codes;
+  const __half* norms; int64_t ld_norms;
+  const float* ct; int n_levels;
+  void* y; int y_dtype; int64_t ld_y;
+  const __half* bias;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if the CTA is aborting (somebody timed out, maybe us).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kTimeoutCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// K-major, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart (SBO), LBO field 1,
+// descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// low half of a, high half of b
+__device__ __forceinline__ uint32_t lo_hi16(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, 0x7610;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// table entry address: lut + byte * 128 + lane * 4
+template <int BYTE>
+__device__ __forceinline__ uint32_t glut(uint32_t word, uint32_t lane_base) {
+  uint32_t b, v;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(b) : "r"(word), "r"(0), "n"(0x4440 | BYTE));
+  const uint32_t addr = b * 128u + lane_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+template <bool PACKED>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  uint8_t* sm = smem_raw + (base - raw);
+  const uint32_t lut_s = base + kStages * kStageBytes;
+  uint8_t* lut_g = sm + kStages * kStageBytes;
+  const uint32_t bars = lut_s + kLutBytes;  // full_x[3], full_w[3], empty[3], acc_full : 10 x 8 B
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(lut_g + kLutBytes + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(lut_g + kLutBytes + 132);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto full_x = [&](int s) { return bars + 8 * s; };
+  auto full_w = [&](int s) { return bars + 24 + 8 * s; };
+  auto empty = [&](int s) { return bars + 48 + 8 * s; };
+  const uint32_t acc_full = bars + 72;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_x(s), 1);
+      mbar_init(full_w(s), kDecodeThreads / 32);
+      mbar_init(empty(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // centroid table, one copy per lane: decode threads write entries tid-64, +256 ... (8192 words)
+  if (warp >= 2) {
+    const int d = tid - 64;
+    for (int e = d >> 5; e < (PACKED ? 256 : p.n_levels); e += kDecodeThreads / 32) {
+      uint32_t v;
+      if (PACKED) {
+        const int lo = e & 15, hi = e >> 4;
+        v = pack_bf16(lo < p.n_levels ? p.ct[lo] : 0.f, hi < p.n_levels ? p.ct[hi] : 0.f);
+      } else {
+        v = pack_bf16(p.ct[e], p.ct[e]);
+      }
+      *reinterpret_cast<uint32_t*>(lut_g + e * 128 + lane * 4) = v;
+    }
+  }
+  if (warp == 1) {  // TMEM: all 512 columns, allocated and later freed by this warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  const int ksteps = p.K / kStepK;
+  const int n_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * kTileM;
+        const bool two = m0 + 128 < p.M;
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 1)) goto done_producer;
+          mbar_expect_tx(full_x(s), two ? 2 * kXTileBytes : kXTileBytes);
+          tma_load_2d(base + s * kStageBytes, &xmap, ks * kStepK, m0, full_x(s));
+          if (two) tma_load_2d(base + s * kStageBytes + kXTileBytes, &xmap, ks * kStepK, m0 + 128, full_x(s));
+        }
+      }
+    done_producer:;
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+        const int m0 = (tile % p.tiles_m) * kTileM;
+        const bool two = m0 + 128 < p.M;
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(full_x(s), ph, abort_flag, p.status, 2)) goto done_mma;
+          if (!mbar_wait(full_w(s), ph, abort_flag, p.status, 3)) goto done_mma;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t xa = base + s * kStageBytes, wb = xa + 2 * kXTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < kStepK / 16; ++kk) {
+            const uint64_t db = smem_desc_sw128(wb + kk * 32);
+            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+            umma_bf16(tmem, smem_desc_sw128(xa + kk * 32), db, kIdesc, acc);
+            if (two) umma_bf16(tmem + 256, smem_desc_sw128(xa + kXTileBytes + kk * 32), db, kIdesc, acc);
+          }
+          umma_commit(empty(s));  // frees the stage when these MMAs have read it
+        }
+        umma_commit(acc_full);    // accumulators of this tile complete
+      }
+    done_mma:;
+    }
+  } else {
+    // ---------------- decode + epilogue warps ----------------
+    const int d = tid - 64;                 // weight row inside the tile
+    const uint32_t lane_base = lut_s + lane * 4;
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;       // accumulator (token half) this warp drains
+    int it = 0, tcount = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+      const int m0 = (tile % p.tiles_m) * kTileM;
+      const int n0 = (tile / p.tiles_m) * kTileN;
+      const bool two = m0 + 128 < p.M;
+      int row = n0 + d;
+      const bool row_ok = row < p.N;
+      if (!row_ok) row = p.N - 1;
+      const uint8_t* crow = p.codes + (int64_t)row * p.ld_codes;
+      const unsigned short* nrow = reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)row * p.ld_norms;
+      const uint32_t wrow = (uint32_t)((d >> 3) * 1024 + (d & 7) * 128);
+      const int sw = d & 7;
+      bool dead = false;
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        // fetch this row's codes and norm before waiting for the buffer
+        uint4 c[PACKED ? 2 : 4];
+        const uint8_t* src = crow + (PACKED ? ks * 32 : ks * 64);
+#pragma unroll
+        for (int i = 0; i < (PACKED ? 2 : 4); ++i) c[i] = ldg_stream(src + 16 * i);
+        const int blk = (ks * kStepK) >> 7;
+        const float nf = row_ok ? __half2float(__ushort_as_half(__ldg(nrow + blk))) : 0.f;
+        const uint32_t n2 = pack_bf16(nf, nf);
+        const bool ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 4);
+        if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }  // leave together or not at all
+        uint8_t* wt = sm + s * kStageBytes + 2 * kXTileBytes + wrow;
+        if (PACKED) {
+          // one code byte -> two adjacent K elements; word ch (4 bytes) -> chunk ch (8 elements, 16 B)
+          const uint32_t wq[8] = {c[0].x, c[0].y, c[0].z, c[0].w, c[1].x, c[1].y, c[1].z, c[1].w};
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t w = wq[ch];
+            uint4 o;
+            o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
+            o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
+            o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
+            o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+            *reinterpret_cast<uint4*>(wt + ((ch ^ sw) << 4)) = o;
+          }
+        } else {
+          // one code byte -> one K element; words 2ch, 2ch+1 -> chunk ch
+          const uint4 c2 = c[PACKED ? 0 : 2], c3 = c[PACKED ? 0 : 3];
+          const uint32_t wq[16] = {c[0].x, c[0].y, c[0].z, c[0].w, c[1].x, c[1].y, c[1].z, c[1].w,
+                                   c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t wa = wq[2 * ch], wb = wq[2 * ch + 1];
+            uint4 o;
+            o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
+            o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
+            o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
+            o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
+            *reinterpret_cast<uint4*>(wt + ((ch ^ sw) << 4)) = o;
+          }
+        }
+        // make the generic-proxy stores visible to the tensor core, then one arrive per warp
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_w(s));
+      }
+      if (dead) break;
+      // ---------------- epilogue: TMEM -> registers -> global ----------------
+      {
+        const bool ok = mbar_wait(acc_full, tcount & 1, abort_flag, p.status, 5);
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (half == 0 || two) {
+        const int m = m0 + half * 128 + q * 32 + lane;
+        const uint32_t trow = tmem + half * 256 + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+        for (int cc = 0; cc < kTileN / 32; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(trow + cc * 32, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int nb0 = n0 + cc * 32;
+          if (m < p.M && nb0 < p.N) {
+            const bool full = nb0 + 32 <= p.N && (p.ld_y % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
+            if (full && p.y_dtype != PE_F32) {
+              uint32_t o[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float a = __uint_as_float(r[2 * j]), b = __uint_as_float(r[2 * j + 1]);
+                if (p.bias) { a += __half2float(p.bias[nb0 + 2 * j]); b += __half2float(p.bias[nb0 + 2 * j + 1]); }
+                o[j] = p.y_dtype == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.y) + (int64_t)m * p.ld_y + nb0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            } else {
+              for (int j = 0; j < 32 && nb0 + j < p.N; ++j) {
+                float a = __uint_as_float(r[j]);
+                if (p.bias) a += __half2float(p.bias[nb0 + j]);
+                store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + nb0 + j, a);
+              }
+            }
+          }
+        }
+      }
+      // TMEM reads are done before the next tile's first MMA: the fence orders them
+      // before the full_w arrivals that MMA waits for.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+  }
+
+  // ---------------- common exit ----------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag && tid == 0) {  // give copies that may still be in flight time to land
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+  }
+}
+
+// Activation preparation: (pad + FWHT for raw input), bf16, kernel K order.
+// One warp per (row, 128-block).
+__global__ void __launch_bounds__(256) gemm_prep_kernel(const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f,
+                                                        __nv_bfloat16* xq, int M, int K, int pair_layout) {
+  const int lane = threadIdx.x & 31;
+  const int nb = K / kBlock;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp >= (int64_t)M * nb) return;
+  const int m = (int)(warp / nb), blk = (int)(warp - (int64_t)m * nb);
+  const bool vin = (ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  float v[4];
+  load4_as_float(x, x_dtype, (int64_t)m * ld_x, blk * kBlock + lane * 4, x_kind == PE_X_RAW ? in_f : K, vin, v);
+  if (x_kind == PE_X_RAW) warp_fwht128(v, lane);
+  __nv_bfloat16* dst = xq + (int64_t)m * K + blk * kBlock;
+  if (pair_layout) {
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[i], 16);
+    if (lane < 16)  // positions 8*lane .. 8*lane+7 = pairs (k, k+64), k = 4*lane..4*lane+3
+      *reinterpret_cast<uint4*>(dst + 8 * lane) = make_uint4(pack_bf16(v[0], o[0]), pack_bf16(v[1], o[1]),
+                                                             pack_bf16(v[2], o[2]), pack_bf16(v[3], o[3]));
+  } else {
+    *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace pe
+
+using namespace pe;
+
+// workspace: [status word, padded to 256 B][bf16 activations M x K]
+extern "C" size_t pe_gemm_workspace_bytes(int m, int in_f_padded) {
+  if (m < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
+  return 256 + (size_t)m * in_f_padded * 2;
+}
+
+extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                       const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
+                       int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int m, int out_f, int in_f_padded,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  if (!codes || !norms || !ct_scaled || !x || !y || !workspace) return PE_ERR_ARG;
+  if (m < 1 || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
+  if (x_kind != PE_X_ROTATED && x_kind != PE_X_RAW) return PE_ERR_ARG;
+  if (x_dtype < PE_F32 || x_dtype > PE_BF16 || y_dtype < PE_F32 || y_dtype > PE_BF16) return PE_ERR_ARG;
+  if (n_levels < 2 || n_levels > 256 || (packed && n_levels > 16)) return PE_ERR_ARG;
+  if (in_f_padded % kBlock) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15)) return PE_ERR_ALIGN;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return PE_ERR_ALIGN;
+  if (workspace_bytes < pe_gemm_workspace_bytes(m, in_f_padded)) return PE_ERR_WORKSPACE;
+  if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  if (ld_x < (x_kind == PE_X_RAW ? in_f : in_f_padded) || ld_y < out_f) return PE_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int sms = sm_count();
+  if (sms <= 0) return PE_ERR_CUDA;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return PE_ERR_CUDA;
+
+  int* status = static_cast<int*>(workspace);
+  __nv_bfloat16* xq = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(workspace) + 256);
+  PE_CUDA_TRY(cudaMemsetAsync(status, 0, 4, st));
+  const int nb = in_f_padded / kBlock;
+  const int64_t warps = (int64_t)m * nb;
+  gemm_prep_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, m, in_f_padded,
+                                                                 packed ? 1 : 0);
+  PE_CUDA_TRY(cudaGetLastError());
+
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)in_f_padded, (cuuint64_t)m};
+  const cuuint64_t strides[1] = {(cuuint64_t)in_f_padded * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kStepK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return PE_ERR_CUDA;
+
+  GemmArgs a;
+  a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
+  a.norms = static_cast<const __half*>(norms); a.ld_norms = ld_norms;
+  a.ct = ct_scaled; a.n_levels = n_levels;
+  a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  a.bias = static_cast<const __half*>(bias);
+  a.M = m; a.N = out_f; a.K = in_f_padded;
+  a.tiles_m = (m + kTileM - 1) / kTileM;
+  a.tiles_n = (out_f + kTileN - 1) / kTileN;
+  a.status = status;
+  const int tiles = a.tiles_m * a.tiles_n;
+  const int grid = tiles < sms ? tiles : sms;
+  if (packed) {
+    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+    gemm_kernel<true><<<grid, kGemmThreads, kGemmSmem, st>>>(a, map);
+  } else {
+    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+    gemm_kernel<false><<<grid, kGemmThreads, kGemmSmem, st>>>(a, map);
+  }
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}

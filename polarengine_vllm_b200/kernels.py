@@ -47,7 +47,7 @@ def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scal
         return y
     l = nv.lib()
     st = nv.stream_ptr(dev)
-    if batch <= GEMV_MAX_BATCH or not hasattr(l, "pe_gemm"):
+    if batch <= GEMV_MAX_BATCH:
         need = l.pe_gemv_workspace_bytes(min(batch, GEMV_MAX_BATCH), out_f, in_f_padded)
         ws = nv.gemv_scratch(dev, need)
         for m0 in range(0, batch, GEMV_MAX_BATCH):

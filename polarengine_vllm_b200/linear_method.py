@@ -22,8 +22,8 @@ from typing import Any, Dict, List, Optional
 
 import torch
 
-from .fwht import FWHTCache, fwht128
-from .kernels import GEMV_MAX_BATCH, pack_codes_int4, quant_matmul
+from .fwht import FWHTCache
+from .kernels import pack_codes_int4, quant_matmul
 from .utils import get_ct_scaled
 
 try:  # vLLM is optional: the class must stay importable for offline tooling
@@ -94,16 +94,10 @@ class PolarQuantLinearMethod(_Base):
         x2 = x.reshape(-1, layer.in_f)
         packed = bool(getattr(layer, "packed", False))
         w = layer.codes_packed if packed else layer.codes
-        if x2.shape[0] <= GEMV_MAX_BATCH:
-            y = quant_matmul(w, packed, layer.norms, layer.ct_scaled, x2, False, layer.out_f, layer.in_f,
-                             layer.in_f_padded, torch.float16, bias)
-        else:
-            xt = self._fwht_cache.get(x, layer.in_f)
-            if xt is None:
-                xt = fwht128(x2, layer.in_f_padded, torch.bfloat16)
-                self._fwht_cache.put(x, layer.in_f, xt)
-            y = quant_matmul(w, packed, layer.norms, layer.ct_scaled, xt, True, layer.out_f, layer.in_f,
-                             layer.in_f_padded, torch.float16, bias)
+        # one native entry for every batch size: <= 16 rows run the fused decode kernel,
+        # more rows the tensor-core kernel (rotation is done by its preparation launch)
+        y = quant_matmul(w, packed, layer.norms, layer.ct_scaled, x2, False, layer.out_f, layer.in_f,
+                         layer.in_f_padded, torch.float16, bias)
         return y.view(*lead, layer.out_f)
 
 
