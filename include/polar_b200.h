@@ -67,6 +67,17 @@ int pe_init(int device);
 int pe_fwht128(const void* x, int x_dtype, int64_t ld_x, void* x_tf, int out_dtype, int64_t ld_out,
                int batch, int in_f, int in_f_padded, void* stream);
 
+/* ---- quantized embedding lookup ----------------------------------------------
+ * out[t, :] = dequantised row ids[t] of a quantized (vocab, hidden) table:
+ * FWHT-128(ct_scaled[codes[row, blk, :]]) * norm[row, blk] per block (the rotation is
+ * its own inverse), i.e. row ids[t] of weight_converter._dequant_weight
+ * (weight_converter.py:34-67) without materialising the table.  The reference keeps
+ * embeddings unquantized at run time (config.py:188-193); its quantizer assigns them
+ * 5 bits (utils.py:112-114).  ids are int64 on the device; out-of-range ids give zeros. */
+int pe_embedding(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                 const float* ct_scaled, int n_levels, const int64_t* ids, int64_t vocab, void* out, int out_dtype,
+                 int64_t ld_out, int tokens, int hidden, int hidden_padded, void* stream);
+
 /* ---- nibble packing ---------------------------------------------------------
  * int8 codes (out_f, in_f_padded) -> uint8 (out_f, in_f_padded/2), byte i of each
  * 128-block = code[64+i] << 4 | code[i].  Replaces pack_codes_int4

@@ -28,6 +28,7 @@ SIGNATURES = {
     "pe_last_cuda_error": (_i, []),
     "pe_init": (_i, [_i]),
     "pe_fwht128": (_i, [_vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
+    "pe_embedding": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "pe_pack_nibble": (_i, [_vp, _vp, _i64, _i64, _vp]),
     "pe_gemv_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,

@@ -48,6 +48,7 @@ class PolarQuantConfig(QuantizationConfig):
         self.bit_assignment: Dict[str, int] = bit_assignment or {}
         self.layers_meta: Dict[str, Dict[str, Any]] = layers_meta or {}
         self.format = fmt
+        self.quantize_experts = False  # True: MoE experts carry PolarQuant codes (PolarQuantMoEMethod)
         self.packed_modules_mapping: Dict[str, Any] = {}
 
     def __repr__(self) -> str:
@@ -78,8 +79,10 @@ class PolarQuantConfig(QuantizationConfig):
         fmt = config.get("format", "polar_engine_v4")
         if fmt not in KNOWN_FORMATS:
             log.warning("Unrecognised PolarEngine/HLWQ format '%s'; weight loading may fail.", fmt)
-        return cls(block_size=config.get("block_size", 128), bit_assignment=config.get("bit_assignment", {}),
-                   layers_meta=config.get("layers", {}), fmt=fmt)
+        out = cls(block_size=config.get("block_size", 128), bit_assignment=config.get("bit_assignment", {}),
+                  layers_meta=config.get("layers", {}), fmt=fmt)
+        out.quantize_experts = bool(config.get("quantize_experts", False))
+        return out
 
     def get_quant_method(self, layer: torch.nn.Module, prefix: str) -> Optional["QuantizeMethodBase"]:
         from .linear_method import PolarQuantLinearMethod

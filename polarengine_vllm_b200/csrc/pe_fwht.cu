@@ -45,9 +45,69 @@ __global__ void __launch_bounds__(256) pack_nibble_kernel(const int8_t* codes, u
   *reinterpret_cast<uint4*>(packed + i * 16) = r;
 }
 
+// Quantized embedding lookup: row ids[t] of the table is dequantised on the fly.
+// One warp per (token, 128-block): centroid gather, inverse rotation (the rotation is its
+// own inverse), block norm, cast.
+__global__ void __launch_bounds__(256) embed_kernel(const uint8_t* codes, int packed, int64_t ld_codes, const __half* norms,
+                                                    int64_t ld_norms, const float* ct, int n_levels, const int64_t* ids,
+                                                    int64_t vocab, void* out, int out_dtype, int64_t ld_out, int tokens,
+                                                    int hidden, int nb) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp >= (int64_t)tokens * nb) return;
+  const int t = (int)(warp / nb), blk = (int)(warp - (int64_t)t * nb);
+  int64_t row = ids[t];
+  const bool ok = row >= 0 && row < vocab;  // out-of-range ids give a zero row
+  if (!ok) row = 0;
+  float v[4];
+  if (packed) {
+    // elements 4l..4l+3: low nibbles of bytes 4l.. for l < 16, high nibbles of bytes 4(l-16).. otherwise
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(codes + row * ld_codes + blk * 64 + (lane & 15) * 4);
+    const uint32_t nib = (lane < 16 ? w : (w >> 4)) & 0x0f0f0f0fu;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = (nib >> (8 * i)) & 0xff;
+      v[i] = c < n_levels ? __ldg(ct + c) : 0.f;
+    }
+  } else {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(codes + row * ld_codes + blk * kBlock + lane * 4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = (w >> (8 * i)) & 0xff;
+      v[i] = c < n_levels ? __ldg(ct + c) : 0.f;
+    }
+  }
+  warp_fwht128(v, lane);
+  const float nrm = ok ? __half2float(norms[row * ld_norms + blk]) : 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int col = blk * kBlock + lane * 4 + i;
+    if (col < hidden) store_from_float(out, out_dtype, (int64_t)t * ld_out + col, v[i] * nrm);
+  }
+}
+
 }  // namespace pe
 
 using namespace pe;
+
+extern "C" int pe_embedding(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                            const float* ct_scaled, int n_levels, const int64_t* ids, int64_t vocab, void* out,
+                            int out_dtype, int64_t ld_out, int tokens, int hidden, int hidden_padded, void* stream) {
+  if (!codes || !norms || !ct_scaled || !ids || !out || tokens < 1 || hidden < 1 || vocab < 1) return PE_ERR_ARG;
+  if (out_dtype < PE_F32 || out_dtype > PE_BF16 || n_levels < 2 || n_levels > 256 || (packed && n_levels > 16)) return PE_ERR_ARG;
+  if (hidden_padded % kBlock || hidden > hidden_padded || hidden_padded - hidden >= kBlock) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 3) || (ld_codes & 3)) return PE_ERR_ALIGN;
+  if (ld_out < hidden) return PE_ERR_ARG;
+  const int nb = hidden_padded / kBlock;
+  const int64_t warps = (int64_t)tokens * nb;
+  const int64_t blocks = (warps + 7) / 8;
+  if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
+  embed_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(codes), packed, ld_codes, static_cast<const __half*>(norms), ld_norms, ct_scaled, n_levels,
+      ids, vocab, out, out_dtype, ld_out, tokens, hidden, nb);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
 
 extern "C" int pe_fwht128(const void* x, int x_dtype, int64_t ld_x, void* x_tf, int out_dtype, int64_t ld_out,
                           int batch, int in_f, int in_f_padded, void* stream) {

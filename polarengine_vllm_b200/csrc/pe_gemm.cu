@@ -37,8 +37,8 @@ constexpr int kXTileBytes = 128 * kStepK * 2;        // 16 KB
 constexpr int kWTileBytes = kTileN * kStepK * 2;     // 32 KB
 constexpr int kStageBytes = 2 * kXTileBytes + kWTileBytes;  // 64 KB
 constexpr int kLutBytes = 32768;                     // 256 entries x 32 lanes x 4 B
-constexpr int kGemmThreads = 320;                    // 10 warps
-constexpr int kDecodeThreads = 256;
+constexpr int kGemmThreads = 576;                    // 18 warps: TMA, MMA, 16 decode/epilogue
+constexpr int kDecodeThreads = 512;
 constexpr unsigned kGemmSmem = kStages * kStageBytes + kLutBytes + 256 + 1024 /*alignment slack*/;
 constexpr long long kTimeoutCycles = 1ll << 31;
 
@@ -51,6 +51,7 @@ struct GemmArgs {
   int M, N, K;
   int tiles_m, tiles_n;
   int* status;
+  unsigned long long* prof;  // developer builds (-DPE_PROFILE): cycles spent in each wait, per CTA
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -75,13 +76,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false if the CTA is aborting (somebody timed out, maybe us).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          unsigned long long* prof = nullptr) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
-      if (mbar_try(bar, parity)) return true;
+      if (mbar_try(bar, parity)) {
+#ifdef PE_PROFILE
+        if (prof && (threadIdx.x & 31) == 0 && (threadIdx.x < 96))
+          atomicAdd(prof + blockIdx.x * 8 + code, (unsigned long long)(clock64() - t0));
+#endif
+        return true;
+      }
     if (*abort_flag) return false;
     if (clock64() - t0 > kTimeoutCycles) {
       *abort_flag = 1;
@@ -217,7 +225,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 1)) goto done_producer;
+          if (!mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 1, p.prof)) goto done_producer;
           mbar_expect_tx(full_x(s), two ? 2 * kXTileBytes : kXTileBytes);
           tma_load_2d(base + s * kStageBytes, &xmap, ks * kStepK, m0, full_x(s));
           if (two) tma_load_2d(base + s * kStageBytes + kXTileBytes, &xmap, ks * kStepK, m0 + 128, full_x(s));
@@ -235,8 +243,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(full_x(s), ph, abort_flag, p.status, 2)) goto done_mma;
-          if (!mbar_wait(full_w(s), ph, abort_flag, p.status, 3)) goto done_mma;
+          if (!mbar_wait(full_x(s), ph, abort_flag, p.status, 2, p.prof)) goto done_mma;
+          if (!mbar_wait(full_w(s), ph, abort_flag, p.status, 3, p.prof)) goto done_mma;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t xa = base + s * kStageBytes, wb = xa + 2 * kXTileBytes;
 #pragma unroll
@@ -254,75 +262,100 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
     }
   } else {
     // ---------------- decode + epilogue warps ----------------
-    const int d = tid - 64;                 // weight row inside the tile
+    // thread d: weight row d % 256 of the tile, K half d / 256 of every 64-wide step
+    // (four 16-byte chunks).  Codes and norms are requested two steps ahead.
+    const int d = tid - 64;
+    const int r = d & 255, kh = d >> 8;
     const uint32_t lane_base = lut_s + lane * 4;
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;       // accumulator (token half) this warp drains
+    const int grp = (warp - 2) >> 2;        // 0..3
+    const int half = grp & 1;               // accumulator (token half) this warp drains
+    const int chalf = grp >> 1;             // which 128 of its 256 columns
+    constexpr int CW = PACKED ? 1 : 2;      // 16-byte code loads per thread per step
     int it = 0, tcount = 0;
     for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
       const int m0 = (tile % p.tiles_m) * kTileM;
       const int n0 = (tile / p.tiles_m) * kTileN;
       const bool two = m0 + 128 < p.M;
-      int row = n0 + d;
+      int row = n0 + r;
       const bool row_ok = row < p.N;
       if (!row_ok) row = p.N - 1;
-      const uint8_t* crow = p.codes + (int64_t)row * p.ld_codes;
+      const uint8_t* crow = p.codes + (int64_t)row * p.ld_codes + kh * (PACKED ? 16 : 32);
       const unsigned short* nrow = reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)row * p.ld_norms;
-      const uint32_t wrow = (uint32_t)((d >> 3) * 1024 + (d & 7) * 128);
-      const int sw = d & 7;
+      const uint32_t wrow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+      const int sw = r & 7;
       bool dead = false;
-      for (int ks = 0; ks < ksteps; ++ks, ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
-        // fetch this row's codes and norm before waiting for the buffer
-        uint4 c[PACKED ? 2 : 4];
-        const uint8_t* src = crow + (PACKED ? ks * 32 : ks * 64);
+      uint4 cq[2][CW];
+      unsigned short nq[2];
 #pragma unroll
-        for (int i = 0; i < (PACKED ? 2 : 4); ++i) c[i] = ldg_stream(src + 16 * i);
-        const int blk = (ks * kStepK) >> 7;
-        const float nf = row_ok ? __half2float(__ushort_as_half(__ldg(nrow + blk))) : 0.f;
-        const uint32_t n2 = pack_bf16(nf, nf);
-        const bool ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 4);
-        if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }  // leave together or not at all
-        uint8_t* wt = sm + s * kStageBytes + 2 * kXTileBytes + wrow;
-        if (PACKED) {
-          // one code byte -> two adjacent K elements; word ch (4 bytes) -> chunk ch (8 elements, 16 B)
-          const uint32_t wq[8] = {c[0].x, c[0].y, c[0].z, c[0].w, c[1].x, c[1].y, c[1].z, c[1].w};
+      for (int pre = 0; pre < 2; ++pre) {
+        if (pre < ksteps) {
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            const uint32_t w = wq[ch];
-            uint4 o;
-            o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
-            o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
-            o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
-            o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
-            *reinterpret_cast<uint4*>(wt + ((ch ^ sw) << 4)) = o;
-          }
-        } else {
-          // one code byte -> one K element; words 2ch, 2ch+1 -> chunk ch
-          const uint4 c2 = c[PACKED ? 0 : 2], c3 = c[PACKED ? 0 : 3];
-          const uint32_t wq[16] = {c[0].x, c[0].y, c[0].z, c[0].w, c[1].x, c[1].y, c[1].z, c[1].w,
-                                   c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};
+          for (int i = 0; i < CW; ++i) cq[pre][i] = ldg_stream(crow + pre * (PACKED ? 32 : 64) + 16 * i);
+          nq[pre] = __ldg(nrow + (pre >> 1));
+        }
+      }
+      for (int ks = 0; ks < ksteps; ks += 2) {
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            const uint32_t wa = wq[2 * ch], wb = wq[2 * ch + 1];
-            uint4 o;
-            o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
-            o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
-            o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
-            o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
-            *reinterpret_cast<uint4*>(wt + ((ch ^ sw) << 4)) = o;
+        for (int par = 0; par < 2; ++par) {
+          const int k1 = ks + par;
+          if (k1 < ksteps) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            ++it;
+            uint4 c[CW];
+#pragma unroll
+            for (int i = 0; i < CW; ++i) c[i] = cq[par][i];
+            const float nf = row_ok ? __half2float(__ushort_as_half(nq[par])) : 0.f;
+            if (k1 + 2 < ksteps) {
+#pragma unroll
+              for (int i = 0; i < CW; ++i) cq[par][i] = ldg_stream(crow + (k1 + 2) * (PACKED ? 32 : 64) + 16 * i);
+              nq[par] = __ldg(nrow + ((k1 + 2) >> 1));
+            }
+            const uint32_t n2 = pack_bf16(nf, nf);
+            const bool ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 4, p.prof);
+            if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }  // leave together or not at all
+            uint8_t* wt = sm + s * kStageBytes + 2 * kXTileBytes + wrow;
+            if (PACKED) {
+              // one code byte -> two adjacent K elements; word j (4 bytes) -> chunk 4 kh + j (8 elements, 16 B)
+              const uint32_t wq[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t w = wq[j];
+                uint4 o;
+                o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
+                o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
+                o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
+                o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+                *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw) << 4)) = o;
+              }
+            } else {
+              // one code byte -> one K element; words 2j, 2j+1 -> chunk 4 kh + j
+              const uint4 c1 = c[CW - 1];
+              const uint32_t wq[8] = {c[0].x, c[0].y, c[0].z, c[0].w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t wa = wq[2 * j], wb = wq[2 * j + 1];
+                uint4 o;
+                o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
+                o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
+                o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
+                o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
+                *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw) << 4)) = o;
+              }
+            }
+        // make the generic-proxy stores visible to the tensor core, then one arrive per warp
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_w(s));
           }
         }
-        // make the generic-proxy stores visible to the tensor core, then one arrive per warp
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_w(s));
+        if (dead) break;
       }
       if (dead) break;
       // ---------------- epilogue: TMEM -> registers -> global ----------------
       {
-        const bool ok = mbar_wait(acc_full, tcount & 1, abort_flag, p.status, 5);
+        const bool ok = mbar_wait(acc_full, tcount & 1, abort_flag, p.status, 5, p.prof);
         if (!__all_sync(0xffffffffu, ok)) break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -330,7 +363,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
         const int m = m0 + half * 128 + q * 32 + lane;
         const uint32_t trow = tmem + half * 256 + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-        for (int cc = 0; cc < kTileN / 32; ++cc) {
+        for (int cc = chalf * 4; cc < chalf * 4 + 4; ++cc) {
           uint32_t r[32];
           tmem_ld32(trow + cc * 32, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -424,6 +457,11 @@ static EncodeTiledFn encode_fn() {
 
 using namespace pe;
 
+static unsigned long long* g_gemm_prof = nullptr;
+#ifdef PE_PROFILE
+extern "C" void pe_debug_set_gemm_profile_buffer(void* p) { g_gemm_prof = static_cast<unsigned long long*>(p); }
+#endif
+
 // workspace: [status word, padded to 256 B][bf16 activations M x K]
 extern "C" size_t pe_gemm_workspace_bytes(int m, int in_f_padded) {
   if (m < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
@@ -479,6 +517,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   a.tiles_m = (m + kTileM - 1) / kTileM;
   a.tiles_n = (out_f + kTileN - 1) / kTileN;
   a.status = status;
+  a.prof = g_gemm_prof;
   const int tiles = a.tiles_m * a.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
   if (packed) {

@@ -103,3 +103,18 @@ def polar_gemm_packed(codes_packed, x_transformed, norms, ct_scaled, out_f, in_f
 
 polar_gemv_splitk = polar_gemv
 polar_gemv_packed_splitk = polar_gemv_packed
+
+
+def quant_embedding(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scaled: torch.Tensor, ids: torch.Tensor,
+                    hidden: int, out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Rows ``ids`` of a quantized embedding table, dequantised on the fly: (*ids.shape, hidden)."""
+    dev = nv.require_cuda(codes, norms, ct_scaled, ids)
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    hp = norms.shape[-1] * 128
+    out = torch.empty(flat.numel(), hidden, dtype=out_dtype, device=dev)
+    if flat.numel():
+        nv.check(nv.lib().pe_embedding(codes.data_ptr(), int(packed), codes.stride(0) * codes.element_size(), norms.data_ptr(),
+                                       norms.stride(0), ct_scaled.data_ptr(), ct_scaled.numel(), flat.data_ptr(),
+                                       codes.shape[0], out.data_ptr(), nv.dtype_code(out), out.stride(0), flat.numel(),
+                                       hidden, hp, nv.stream_ptr(dev)), "pe_embedding")
+    return out.reshape(*ids.shape, hidden)

@@ -1,12 +1,23 @@
 """MoE methods behind vLLM's fused-MoE interface.
 
-Reference: polarengine_vllm/moe_method.py:18-107 (``PolarPassthroughMoEMethod``), which
-keeps expert weights in bf16 and forwards every call to vLLM's unquantized fused MoE.
-That pass-through is kept here under the same name and with the same lazy construction.
+Reference: polarengine_vllm/moe_method.py:18-107.  The reference keeps expert weights in
+bf16 and forwards to vLLM's unquantized fused MoE (``PolarPassthroughMoEMethod``, kept
+here unchanged in behaviour).  ``PolarQuantMoEMethod`` is the quantized counterpart the
+reference lists as future work: experts are stored as PolarQuant codes (gate/up fused as
+``w13``, Q3 by default; down ``w2``, Q4) and every expert projection runs through the
+same native kernels as a linear layer.  Routing and activation follow the reference's
+MoE layer (nemotron_offload.py:180-226): softmax, top-k, renormalise, silu(gate) * up,
+weighted sum over the selected experts.
 """
 from __future__ import annotations
 
+from typing import Optional, Tuple
+
 import torch
+
+from .kernels import quant_matmul
+from .packing import pack_codes_half_block
+from .utils import get_ct_scaled
 
 
 class PolarPassthroughMoEMethod:
@@ -45,12 +56,133 @@ class PolarPassthroughMoEMethod:
         return None
 
 
+def route_softmax_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 softmax over experts, top-k, optional renormalisation (nemotron_offload.py:180-189)."""
+    p = torch.softmax(router_logits.float(), dim=-1)
+    w, ids = p.topk(top_k, dim=-1)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids
+
+
+class PolarQuantMoEMethod:
+    """Quantized experts.  Layer tensors (E = local experts, I = intermediate, H = hidden,
+    K padded to multiples of 128):
+
+        w13_codes  uint8 (E, 2I, H_pad/2) nibbles if w13_bits <= 4 else int8 (E, 2I, H_pad)
+        w13_norms  fp16  (E, 2I, H_pad/128)
+        w2_codes   uint8 (E, H, I_pad/2)  or int8 (E, H, I_pad)
+        w2_norms   fp16  (E, H, I_pad/128)
+        w13_ct_scaled / w2_ct_scaled  fp32 tables
+
+    ``expert_map`` (optional int tensor of size global experts, -1 = not on this rank)
+    supports expert-parallel placement: tokens routed elsewhere contribute zero here and
+    the caller all-reduces.
+    """
+
+    def __init__(self, w13_bits: int = 3, w2_bits: int = 4, block_size: int = 128) -> None:
+        self.w13_bits, self.w2_bits, self.block_size = w13_bits, w2_bits, block_size
+
+    @staticmethod
+    def _pad(n: int, b: int = 128) -> int:
+        return -(-n // b) * b
+
+    def create_weights(self, layer, num_experts, hidden_size, intermediate_size_per_partition, params_dtype, **kw):
+        e, h, i = num_experts, hidden_size, intermediate_size_per_partition
+        hp, ip = self._pad(h), self._pad(i)
+        def codes(rows, kp, bits):
+            return torch.zeros(e, rows, kp // 2 if bits <= 4 else kp, dtype=torch.uint8 if bits <= 4 else torch.int8)
+        for name, t in (("w13_codes", codes(2 * i, hp, self.w13_bits)),
+                        ("w13_norms", torch.zeros(e, 2 * i, hp // 128, dtype=torch.float16)),
+                        ("w2_codes", codes(h, ip, self.w2_bits)),
+                        ("w2_norms", torch.zeros(e, h, ip // 128, dtype=torch.float16))):
+            prm = torch.nn.Parameter(t, requires_grad=False)
+            if "weight_loader" in kw:
+                prm.weight_loader = kw["weight_loader"]
+            layer.register_parameter(name, prm)
+        layer.register_buffer("w13_ct_scaled", get_ct_scaled(self.w13_bits).clone())
+        layer.register_buffer("w2_ct_scaled", get_ct_scaled(self.w2_bits).clone())
+        layer.moe_hidden, layer.moe_inter, layer.moe_hidden_padded, layer.moe_inter_padded = h, i, hp, ip
+        layer.moe_w13_bits, layer.moe_w2_bits = self.w13_bits, self.w2_bits
+
+    def load_expert(self, layer, e: int, gate: dict, up: dict, down: dict) -> None:
+        """Copy one expert's quantizer outputs (dicts with int8 ``codes`` and ``norms``)."""
+        i = layer.moe_inter
+        for lo, src in ((0, gate), (i, up)):
+            c = src["codes"]
+            layer.w13_codes.data[e, lo:lo + i] = (pack_codes_half_block(c) if self.w13_bits <= 4 else c).to(layer.w13_codes.device)
+            layer.w13_norms.data[e, lo:lo + i] = src["norms"].to(layer.w13_norms.device)
+        c = down["codes"]
+        layer.w2_codes.data[e] = (pack_codes_half_block(c) if self.w2_bits <= 4 else c).to(layer.w2_codes.device)
+        layer.w2_norms.data[e] = down["norms"].to(layer.w2_norms.device)
+
+    def process_weights_after_loading(self, layer) -> None:
+        dev = layer.w13_codes.device
+        layer.w13_ct_scaled = layer.w13_ct_scaled.to(dev)
+        layer.w2_ct_scaled = layer.w2_ct_scaled.to(dev)
+
+    def apply(self, layer, x, a, b, *rest, expert_map: Optional[torch.Tensor] = None, **kwargs):
+        """Both calling conventions of vLLM's fused-MoE methods:
+        ``apply(layer, x, topk_weights, topk_ids, ...)`` (routing done by the caller, vLLM 0.2x) and
+        ``apply(layer, x, router_logits, top_k, renormalize, ...)`` (the reference's, moe_method.py:74-78)."""
+        if torch.is_tensor(b) and not b.is_floating_point():
+            topk_weights, topk_ids = a, b
+        else:
+            renorm = rest[0] if rest else kwargs.get("renormalize", True)
+            topk_weights, topk_ids = route_softmax_topk(a, int(b), bool(renorm))
+        return self.moe_forward(layer, x, topk_weights, topk_ids, expert_map)
+
+    def moe_forward(self, layer, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                    expert_map: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """y[t] = sum_k w[t,k] * down_e(silu(gate_e(x[t])) * up_e(x[t])), e = ids[t,k]; fp16 out.
+        Tokens are grouped by expert on the device; each expert's tokens go through the
+        two projections in batches (native kernels pick decode or tensor-core path)."""
+        lead = x.shape[:-1]
+        h, i = layer.moe_hidden, layer.moe_inter
+        x2 = x.reshape(-1, h)
+        t, k = topk_ids.shape
+        ids = topk_ids.reshape(-1)
+        if expert_map is not None:
+            ids = expert_map.to(ids.device)[ids.long()]
+        order = torch.argsort(ids, stable=True)
+        sorted_ids = ids[order]
+        n_local = layer.w13_codes.shape[0]
+        skipped = int((sorted_ids < 0).sum()) if expert_map is not None else 0  # routed to other ranks; sorted first
+        counts = torch.bincount(sorted_ids[skipped:], minlength=n_local)
+        tok = (order // k)
+        wts = topk_weights.reshape(-1)[order].float()
+        out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
+        pos = skipped
+        for e, n in enumerate(counts.tolist()):
+            if n == 0:
+                continue
+            sel = tok[pos:pos + n]
+            xe = x2.index_select(0, sel)
+            gu = quant_matmul(layer.w13_codes[e], self.w13_bits <= 4, layer.w13_norms[e], layer.w13_ct_scaled, xe, False,
+                              2 * i, h, layer.moe_hidden_padded, torch.float32)
+            act = torch.nn.functional.silu(gu[:, :i]) * gu[:, i:]
+            d = quant_matmul(layer.w2_codes[e], self.w2_bits <= 4, layer.w2_norms[e], layer.w2_ct_scaled, act, False,
+                             h, i, layer.moe_inter_padded, torch.float32)
+            out.index_add_(0, sel, d * wts[pos:pos + n].unsqueeze(1))
+            pos += n
+        return out.to(torch.float16).view(*lead, h)
+
+    def get_fused_moe_quant_config(self, *args):
+        return None
+
+
 def make_moe_method(config, layer, prefix):
+    """Quantized experts when the checkpoint's bit table names them, else the reference's pass-through."""
+    bits13 = config._resolve_bits(prefix + ".experts.0.gate_proj") if hasattr(config, "_resolve_bits") else None
+    bits2 = config._resolve_bits(prefix + ".experts.0.down_proj") if hasattr(config, "_resolve_bits") else None
+    if bits13 is not None and bits2 is not None and getattr(config, "quantize_experts", False):
+        return PolarQuantMoEMethod(bits13, bits2, config.block_size)
     return PolarPassthroughMoEMethod()
 
 
 try:
     from vllm.model_executor.layers.fused_moe.layer import FusedMoEMethodBase
     FusedMoEMethodBase.register(PolarPassthroughMoEMethod)
+    FusedMoEMethodBase.register(PolarQuantMoEMethod)
 except Exception:
     pass

@@ -45,3 +45,23 @@ def test_pack_golden(golden):
     from polarengine_vllm_b200.packing import pack_codes_half_block
     out = pack_codes_half_block(torch.from_numpy(golden["nib_codes"]).cuda()).cpu().numpy()
     assert np.array_equal(out, golden["nib_packed"])
+
+
+@pytest.mark.parametrize("bits,hidden", [(5, 4096), (4, 300), (6, 1856)])
+def test_quantized_embedding_rows(bits, hidden):
+    """Embedding gather = rows of the fp32 dequantised table (weight_converter.py:34-67 math)."""
+    from polarengine_vllm_b200 import kernels, packing
+    g = torch.Generator().manual_seed(bits)
+    w = torch.randn(500, hidden, generator=g) * 0.02
+    q = oracle.quantize_tensor(w, bits)
+    table = oracle.dequant_fp32(q["codes"], q["norms"], q["ct_scaled"])[:, :hidden]
+    ids = torch.randint(0, 500, (3, 7), generator=g)
+    packed = bits <= 4
+    cd = q["codes"].cuda()
+    cw = packing.pack_codes_half_block(cd) if packed else cd
+    out = kernels.quant_embedding(cw, packed, q["norms"].cuda(), q["ct_scaled"].cuda(), ids.cuda(), hidden, torch.float32)
+    assert out.shape == (3, 7, hidden)
+    ref = table[ids]
+    assert (out.cpu() - ref).abs().max() <= 1e-5 * ref.abs().max() + 1e-7
+    out16 = kernels.quant_embedding(cw, packed, q["norms"].cuda(), q["ct_scaled"].cuda(), ids.cuda(), hidden)
+    assert out16.dtype == torch.float16 and (out16.float().cpu() - ref).abs().max() <= 2e-3 * ref.abs().max()
