@@ -32,14 +32,12 @@ namespace pe {
 constexpr int kTileM = 256;          // tokens per CTA tile (two UMMA M=128 halves)
 constexpr int kTileN = 256;          // weight rows per CTA tile (UMMA N)
 constexpr int kStepK = 64;           // K elements per pipeline stage (128 bytes of bf16)
-constexpr int kStages = 3;
+constexpr int kXStages = 3;          // activation stages (two 128-token tiles each): deep, they come from L2/HBM
+constexpr int kWStages = 2;          // decoded-weight stages: produced locally
 constexpr int kXTileBytes = 128 * kStepK * 2;        // 16 KB
 constexpr int kWTileBytes = kTileN * kStepK * 2;     // 32 KB
-constexpr int kStageBytes = 2 * kXTileBytes + kWTileBytes;  // 64 KB
-constexpr int kLutBytes = 32768;                     // 256 entries x 32 lanes x 4 B
 constexpr int kGemmThreads = 576;                    // 18 warps: TMA, MMA, 16 decode/epilogue
 constexpr int kDecodeThreads = 512;
-constexpr unsigned kGemmSmem = kStages * kStageBytes + kLutBytes + 256 + 1024 /*alignment slack*/;
 constexpr long long kTimeoutCycles = 1ll << 31;
 
 struct GemmArgs {
@@ -50,6 +48,8 @@ struct GemmArgs {
   const __half* bias;
   int M, N, K;
   int tiles_m, tiles_n;
+  int lut_bytes;  // n_levels (256 for nibble pairs) x 128 B
+  int nc;         // code stages
   int* status;
   unsigned long long* prof;  // developer builds (-DPE_PROFILE): cycles spent in each wait, per CTA
 };
@@ -162,34 +162,44 @@ __device__ __forceinline__ uint32_t glut(uint32_t word, uint32_t lane_base) {
 }
 
 template <bool PACKED>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap cmap) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023) & ~1023u;  // swizzled tiles need 1024-byte alignment
   uint8_t* sm = smem_raw + (base - raw);
-  const uint32_t lut_s = base + kStages * kStageBytes;
-  uint8_t* lut_g = sm + kStages * kStageBytes;
-  const uint32_t bars = lut_s + kLutBytes;  // full_x[3], full_w[3], empty[3], acc_full : 10 x 8 B
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(lut_g + kLutBytes + 128);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(lut_g + kLutBytes + 132);
+  // [X stages 3 x 32 KB][W stages 2 x 32 KB][table][code stages nc x (256 rows x 32|64 B)][barriers]
+  constexpr int kXStage = 2 * kXTileBytes;
+  constexpr uint32_t kWOff = kXStages * kXStage;
+  constexpr uint32_t kLutOff = kWOff + kWStages * kWTileBytes;
+  constexpr int kCodeRow = PACKED ? 32 : 64;          // code bytes per weight row per K step
+  constexpr int kCodeStage = kTileN * kCodeRow;
+  const uint32_t c_off = kLutOff + p.lut_bytes;
+  const uint32_t bar_off = c_off + p.nc * kCodeStage;
+  const uint32_t lut_s = base + kLutOff;
+  uint8_t* lut_g = sm + kLutOff;
+  const uint32_t bars = base + bar_off;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + bar_off + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + bar_off + 196);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  auto full_x = [&](int s) { return bars + 8 * s; };
-  auto full_w = [&](int s) { return bars + 24 + 8 * s; };
-  auto empty = [&](int s) { return bars + 48 + 8 * s; };
-  const uint32_t acc_full = bars + 72;
+  auto full_x = [&](int s) { return bars + 8 * s; };         // 3
+  auto empty_x = [&](int s) { return bars + 24 + 8 * s; };   // 3
+  auto full_w = [&](int s) { return bars + 48 + 8 * s; };    // 2
+  auto empty_w = [&](int s) { return bars + 64 + 8 * s; };   // 2
+  auto full_c = [&](int s) { return bars + 80 + 8 * s; };    // up to 4
+  auto empty_c = [&](int s) { return bars + 112 + 8 * s; };  // up to 4
+  const uint32_t acc_full = bars + 144;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_x(s), 1);
-      mbar_init(full_w(s), kDecodeThreads / 32);
-      mbar_init(empty(s), 1);
-    }
+    for (int s = 0; s < kXStages; ++s) { mbar_init(full_x(s), 1); mbar_init(empty_x(s), 1); }
+    for (int s = 0; s < kWStages; ++s) { mbar_init(full_w(s), kDecodeThreads / 32); mbar_init(empty_w(s), 1); }
+    for (int s = 0; s < p.nc; ++s) { mbar_init(full_c(s), 1); mbar_init(empty_c(s), kDecodeThreads / 32); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // centroid table, one copy per lane: decode threads write entries tid-64, +256 ... (8192 words)
+  // centroid table, one copy per lane (entry e of lane l at e * 128 + l * 4)
   if (warp >= 2) {
     const int d = tid - 64;
     for (int e = d >> 5; e < (PACKED ? 256 : p.n_levels); e += kDecodeThreads / 32) {
@@ -216,19 +226,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
   const int n_tiles = p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer: activations and codes ----------------
     if (lane == 0) {
       int it = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * kTileM;
+        const int n0 = (tile / p.tiles_m) * kTileN;
         const bool two = m0 + 128 < p.M;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 1, p.prof)) goto done_producer;
-          mbar_expect_tx(full_x(s), two ? 2 * kXTileBytes : kXTileBytes);
-          tma_load_2d(base + s * kStageBytes, &xmap, ks * kStepK, m0, full_x(s));
-          if (two) tma_load_2d(base + s * kStageBytes + kXTileBytes, &xmap, ks * kStepK, m0 + 128, full_x(s));
+          const int sc = it % p.nc;
+          if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6, p.prof)) goto done_producer;
+          mbar_expect_tx(full_c(sc), kCodeStage);
+          tma_load_2d(base + c_off + sc * kCodeStage, &cmap, ks * kCodeRow, n0, full_c(sc));
+          const int sx = it % kXStages;
+          if (!mbar_wait(empty_x(sx), ((it / kXStages) & 1) ^ 1, abort_flag, p.status, 1, p.prof)) goto done_producer;
+          mbar_expect_tx(full_x(sx), two ? 2 * kXTileBytes : kXTileBytes);
+          tma_load_2d(base + sx * kXStage, &xmap, ks * kStepK, m0, full_x(sx));
+          if (two) tma_load_2d(base + sx * kXStage + kXTileBytes, &xmap, ks * kStepK, m0 + 128, full_x(sx));
         }
       }
     done_producer:;
@@ -236,17 +250,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      int it = 0, tcount = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+      int it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * kTileM;
         const bool two = m0 + 128 < p.M;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(full_x(s), ph, abort_flag, p.status, 2, p.prof)) goto done_mma;
-          if (!mbar_wait(full_w(s), ph, abort_flag, p.status, 3, p.prof)) goto done_mma;
+          const int sx = it % kXStages, sw = it % kWStages;
+          if (!mbar_wait(full_x(sx), (it / kXStages) & 1, abort_flag, p.status, 2, p.prof)) goto done_mma;
+          if (!mbar_wait(full_w(sw), (it / kWStages) & 1, abort_flag, p.status, 3, p.prof)) goto done_mma;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t xa = base + s * kStageBytes, wb = xa + 2 * kXTileBytes;
+          const uint32_t xa = base + sx * kXStage, wb = base + kWOff + sw * kWTileBytes;
 #pragma unroll
           for (int kk = 0; kk < kStepK / 16; ++kk) {
             const uint64_t db = smem_desc_sw128(wb + kk * 32);
@@ -254,16 +267,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
             umma_bf16(tmem, smem_desc_sw128(xa + kk * 32), db, kIdesc, acc);
             if (two) umma_bf16(tmem + 256, smem_desc_sw128(xa + kXTileBytes + kk * 32), db, kIdesc, acc);
           }
-          umma_commit(empty(s));  // frees the stage when these MMAs have read it
+          umma_commit(empty_x(sx));  // both buffers are free once these MMAs have read them
+          umma_commit(empty_w(sw));
         }
-        umma_commit(acc_full);    // accumulators of this tile complete
+        umma_commit(acc_full);       // accumulators of this tile complete
       }
     done_mma:;
     }
   } else {
     // ---------------- decode + epilogue warps ----------------
     // thread d: weight row d % 256 of the tile, K half d / 256 of every 64-wide step
-    // (four 16-byte chunks).  Codes and norms are requested two steps ahead.
+    // (four 16-byte chunks of the swizzled weight tile).
     const int d = tid - 64;
     const int r = d & 255, kh = d >> 8;
     const uint32_t lane_base = lut_s + lane * 4;
@@ -271,7 +285,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
     const int grp = (warp - 2) >> 2;        // 0..3
     const int half = grp & 1;               // accumulator (token half) this warp drains
     const int chalf = grp >> 1;             // which 128 of its 256 columns
-    constexpr int CW = PACKED ? 1 : 2;      // 16-byte code loads per thread per step
+    const bool norm_vec = (p.ld_norms % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.norms) & 15) == 0);
+    const uint32_t wrow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+    const int sw7 = r & 7;
     int it = 0, tcount = 0;
     for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
       const int m0 = (tile % p.tiles_m) * kTileM;
@@ -280,77 +296,77 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
       int row = n0 + r;
       const bool row_ok = row < p.N;
       if (!row_ok) row = p.N - 1;
-      const uint8_t* crow = p.codes + (int64_t)row * p.ld_codes + kh * (PACKED ? 16 : 32);
-      const unsigned short* nrow = reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)row * p.ld_norms;
-      const uint32_t wrow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-      const int sw = r & 7;
+      const __half* nrow = p.norms + (int64_t)row * p.ld_norms;
       bool dead = false;
-      uint4 cq[2][CW];
-      unsigned short nq[2];
+      uint4 nq = make_uint4(0, 0, 0, 0);  // norms of eight consecutive blocks
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        const int blk = ks >> 1;
+        if ((ks & 15) == 0) {  // every 8 blocks
+          if (norm_vec && blk + 8 <= (p.K >> 7)) {
+            nq = __ldg(reinterpret_cast<const uint4*>(nrow + blk));
+          } else {
+            unsigned short t8[8];
 #pragma unroll
-      for (int pre = 0; pre < 2; ++pre) {
-        if (pre < ksteps) {
-#pragma unroll
-          for (int i = 0; i < CW; ++i) cq[pre][i] = ldg_stream(crow + pre * (PACKED ? 32 : 64) + 16 * i);
-          nq[pre] = __ldg(nrow + (pre >> 1));
-        }
-      }
-      for (int ks = 0; ks < ksteps; ks += 2) {
-#pragma unroll
-        for (int par = 0; par < 2; ++par) {
-          const int k1 = ks + par;
-          if (k1 < ksteps) {
-            const int s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1;
-            ++it;
-            uint4 c[CW];
-#pragma unroll
-            for (int i = 0; i < CW; ++i) c[i] = cq[par][i];
-            const float nf = row_ok ? __half2float(__ushort_as_half(nq[par])) : 0.f;
-            if (k1 + 2 < ksteps) {
-#pragma unroll
-              for (int i = 0; i < CW; ++i) cq[par][i] = ldg_stream(crow + (k1 + 2) * (PACKED ? 32 : 64) + 16 * i);
-              nq[par] = __ldg(nrow + ((k1 + 2) >> 1));
-            }
-            const uint32_t n2 = pack_bf16(nf, nf);
-            const bool ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 4, p.prof);
-            if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }  // leave together or not at all
-            uint8_t* wt = sm + s * kStageBytes + 2 * kXTileBytes + wrow;
-            if (PACKED) {
-              // one code byte -> two adjacent K elements; word j (4 bytes) -> chunk 4 kh + j (8 elements, 16 B)
-              const uint32_t wq[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint32_t w = wq[j];
-                uint4 o;
-                o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
-                o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
-                o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
-                o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
-                *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw) << 4)) = o;
-              }
-            } else {
-              // one code byte -> one K element; words 2j, 2j+1 -> chunk 4 kh + j
-              const uint4 c1 = c[CW - 1];
-              const uint32_t wq[8] = {c[0].x, c[0].y, c[0].z, c[0].w, c1.x, c1.y, c1.z, c1.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint32_t wa = wq[2 * j], wb = wq[2 * j + 1];
-                uint4 o;
-                o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
-                o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
-                o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
-                o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
-                *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw) << 4)) = o;
-              }
-            }
-        // make the generic-proxy stores visible to the tensor core, then one arrive per warp
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full_w(s));
+            for (int i = 0; i < 8; ++i)
+              t8[i] = blk + i < (p.K >> 7) ? __ldg(reinterpret_cast<const unsigned short*>(nrow) + blk + i) : (unsigned short)0;
+            nq = make_uint4(t8[0] | (t8[1] << 16), t8[2] | (t8[3] << 16), t8[4] | (t8[5] << 16), t8[6] | (t8[7] << 16));
           }
         }
-        if (dead) break;
+        const int b8 = blk & 7;
+        const uint32_t nword = b8 < 2 ? nq.x : (b8 < 4 ? nq.y : (b8 < 6 ? nq.z : nq.w));
+        const float nf = row_ok ? __half2float(__ushort_as_half((unsigned short)((b8 & 1) ? (nword >> 16) : (nword & 0xffff)))) : 0.f;
+        const uint32_t n2 = pack_bf16(nf, nf);
+        // this step's codes from the TMA-filled stage, then hand the stage back
+        const int sc = it % p.nc;
+        {
+          const bool ok = mbar_wait(full_c(sc), (it / p.nc) & 1, abort_flag, p.status, 7, p.prof);
+          if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }  // leave together or not at all
+        }
+        constexpr int CW = PACKED ? 1 : 2;
+        uint4 c[CW];
+        const uint8_t* csrc = sm + c_off + sc * kCodeStage + r * kCodeRow + kh * (kCodeRow / 2);
+#pragma unroll
+        for (int i = 0; i < CW; ++i) c[i] = *reinterpret_cast<const uint4*>(csrc + 16 * i);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_c(sc));
+        const int sw = it % kWStages;
+        {
+          const bool ok = mbar_wait(empty_w(sw), ((it / kWStages) & 1) ^ 1, abort_flag, p.status, 4, p.prof);
+          if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }
+        }
+        uint8_t* wt = sm + kWOff + sw * kWTileBytes + wrow;
+        if (PACKED) {
+          // one code byte -> two adjacent K elements; word j (4 bytes) -> chunk 4 kh + j (8 elements, 16 B)
+          const uint32_t wq[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t w = wq[j];
+            uint4 o;
+            o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
+            o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
+            o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
+            o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+            *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw7) << 4)) = o;
+          }
+        } else {
+          // one code byte -> one K element; words 2j, 2j+1 -> chunk 4 kh + j
+          const uint4 c1 = c[CW - 1];
+          const uint32_t wq[8] = {c[0].x, c[0].y, c[0].z, c[0].w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t wa = wq[2 * j], wb = wq[2 * j + 1];
+            uint4 o;
+            o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
+            o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
+            o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
+            o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
+            *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw7) << 4)) = o;
+          }
+        }
+        // make the generic-proxy stores visible to the tensor core, then one arrive per warp
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_w(sw));
       }
       if (dead) break;
       // ---------------- epilogue: TMEM -> registers -> global ----------------
@@ -364,8 +380,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
         const uint32_t trow = tmem + half * 256 + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
         for (int cc = chalf * 4; cc < chalf * 4 + 4; ++cc) {
-          uint32_t r[32];
-          tmem_ld32(trow + cc * 32, r);
+          uint32_t rr[32];
+          tmem_ld32(trow + cc * 32, rr);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           const int nb0 = n0 + cc * 32;
           if (m < p.M && nb0 < p.N) {
@@ -374,7 +390,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
               uint32_t o[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                float a = __uint_as_float(r[2 * j]), b = __uint_as_float(r[2 * j + 1]);
+                float a = __uint_as_float(rr[2 * j]), b = __uint_as_float(rr[2 * j + 1]);
                 if (p.bias) { a += __half2float(p.bias[nb0 + 2 * j]); b += __half2float(p.bias[nb0 + 2 * j + 1]); }
                 o[j] = p.y_dtype == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
               }
@@ -382,10 +398,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs p,
 #pragma unroll
               for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
             } else {
-              for (int j = 0; j < 32 && nb0 + j < p.N; ++j) {
-                float a = __uint_as_float(r[j]);
-                if (p.bias) a += __half2float(p.bias[nb0 + j]);
-                store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + nb0 + j, a);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (nb0 + j < p.N) {
+                  float a = __uint_as_float(rr[j]);
+                  if (p.bias) a += __half2float(p.bias[nb0 + j]);
+                  store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + nb0 + j, a);
+                }
               }
             }
           }
@@ -518,14 +537,31 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   a.tiles_n = (out_f + kTileN - 1) / kTileN;
   a.status = status;
   a.prof = g_gemm_prof;
+  a.lut_bytes = (packed ? 256 : n_levels) * 128;
+  const int code_row = packed ? 32 : 64;
+  const int code_stage = kTileN * code_row;
+  const unsigned fixed = kXStages * 2 * kXTileBytes + kWStages * kWTileBytes + a.lut_bytes + 256 + 1024;
+  a.nc = (fixed + 3 * code_stage <= 232448u) ? 3 : 2;
+  const unsigned smem_bytes = fixed + a.nc * code_stage;
+
+  // codes as a 2-D byte tensor (row stride ld_codes), boxes of 256 rows x one K step
+  CUtensorMap cmap;
+  const cuuint64_t cdims[2] = {(cuuint64_t)(packed ? in_f_padded / 2 : in_f_padded), (cuuint64_t)out_f};
+  const cuuint64_t cstrides[1] = {(cuuint64_t)ld_codes};
+  const cuuint32_t cbox[2] = {(cuuint32_t)code_row, (cuuint32_t)kTileN};
+  if (enc(&cmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(codes), cdims, cstrides, cbox, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return PE_ERR_CUDA;
+
   const int tiles = a.tiles_m * a.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
   if (packed) {
-    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
-    gemm_kernel<true><<<grid, kGemmThreads, kGemmSmem, st>>>(a, map);
+    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    gemm_kernel<true><<<grid, kGemmThreads, smem_bytes, st>>>(a, map, cmap);
   } else {
-    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
-    gemm_kernel<false><<<grid, kGemmThreads, kGemmSmem, st>>>(a, map);
+    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    gemm_kernel<false><<<grid, kGemmThreads, smem_bytes, st>>>(a, map, cmap);
   }
   PE_CUDA_TRY(cudaGetLastError());
   return PE_OK;
