@@ -121,6 +121,62 @@ def cpu_baseline(batch, budget_s=12.0):
             "sample": f"{n} decoder-layer passes (4 projections, batch {batch}) of the CPU oracle in {dt:.1f} s"}, dt / n
 
 
+def prefill_sweep(a, dev, rank, world):
+    """BASELINE configs[2]: M tokens x K into N, bf16 activations, Q4 nibble codes.  One step = the three layer
+    shapes once; value = TFLOP/s of 2*M*N*K (rotation and activation preparation included in the time)."""
+    from polarengine_vllm_b200 import kernels
+    shapes = [(4096, 4096), (12288, 4096), (4096, 12288)]
+    m = a.m
+    g = torch.Generator(device=dev).manual_seed(3)
+    data = []
+    for n, k in shapes:
+        w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        norms = (0.2 + 0.02 * torch.rand(n, k // 128, device=dev, generator=g)).half()
+        from polarengine_vllm_b200.utils import get_ct_scaled
+        x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+        data.append((w, norms, get_ct_scaled(4).to(dev), x, n, k))
+    def step():
+        for w, norms, ct, x, n, k in data:
+            kernels.quant_matmul(w, True, norms, ct, x, False, n, k, k, torch.float16)
+    if a.probe:
+        step(); torch.cuda.synchronize()
+        print(json.dumps({"probe": "prefill", "m": m}))
+        return
+    steps = max(3, min(a.steps, 50))
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    per = []
+    for w, norms, ct, x, n, k in data:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            kernels.quant_matmul(w, True, norms, ct, x, False, n, k, k, torch.float16)
+        e1.record(); torch.cuda.synchronize()
+        per.append(e0.elapsed_time(e1) / 1e3 / steps)
+    flops = [2.0 * m * n * k for n, k in shapes]
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    best = max(range(3), key=lambda i: flops[i] / per[i])
+    if rank == 0:
+        print(json.dumps({
+            "metric": "prefill quantized GEMM TFLOP/s", "unit": "TFLOP/s", "value": sum(flops) / sum(per) / 1e12,
+            "n_gpus": a.gpus, "steps": steps, "warmup": 3, "ms_per_step": sum(per) * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"prefill_gemm (BASELINE configs[2]) M={m}, Q4, (N,K) in {shapes}",
+                       "l2_defeat": "operands larger than L2 at M=4096 (x + y + codes > 126 MB for two of three shapes)"},
+            "per_shape_tflops": {f"{n}x{k}": flops[i] / per[i] / 1e12 for i, (n, k) in enumerate(shapes)},
+            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<packed> N=%d K=%d" % shapes[best],
+                         "achieved": flops[best] / per[best] / 1e12, "peak": peak,
+                         "peak_source": "measured burst (MEASURED_PEAKS.json)" if peaks else "fallback",
+                         "unit": "TFLOP/s", "frac": flops[best] / per[best] / 1e12 / peak, "traffic": None},
+            "gpu_launches": 2 * 3 * steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -129,6 +185,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: decoder-layer GEMV pass (default, the headline); prefill: Q4 GEMM sweep of BASELINE configs[2]")
+    ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
     ap.add_argument("--probe", default=None, metavar="PROJ",
                     help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
     a = ap.parse_args()
@@ -163,6 +222,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     from polarengine_vllm_b200 import kernels
     from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
+    if a.workload == "prefill":
+        return prefill_sweep(a, dev, rank, world)
 
     steps = max(RING, a.steps // RING * RING)
     warm = max(3, a.warmup)

@@ -58,7 +58,7 @@ __device__ __forceinline__ void store_from_float(void* base, int dtype, int64_t 
 }
 
 // 4 consecutive elements starting at a multiple of 4, zero beyond `limit`
-__device__ __forceinline__ void load4_as_float(const void* base, int dtype, int64_t row_off, int col,
+static __device__ __noinline__ void load4_as_float(const void* base, int dtype, int64_t row_off, int col,
                                                int limit, bool vec_ok, float v[4]) {
   if (vec_ok && col + 4 <= limit) {
     if (dtype == PE_F32) {

@@ -256,15 +256,23 @@ __device__ __forceinline__ void emit(const GemvArgs& p, int row, int m, float v)
   }
 }
 
-// End of a run of blocks [.., ..) of one 16-row tile: either the whole K was ours
-// (store), or leave a partial and, if we complete the tile, reduce all partials.
+// Hand-off of one 16-row tile at the end of this CTA's share of it.  Every CTA whose range
+// touches the tile's row-tile-of-256 leaves exactly one fp32 partial per warp lane-set
+// (zeros if none of the tile's steps fell to this warp), then bumps the tile's counter with
+// a release; the arrival that completes the count acquires, sums the partials in CTA order
+// (fixed, whatever the arrival order: bit-reproducible), adds the bias, converts, stores,
+// and returns the counter to zero.  A tile owned by a single CTA is stored directly.
 template <int NB>
-__device__ __noinline__ void flush(const GemvArgs& p, float acc[NB / 2], int rt256, int w, int nblk, int G,
-                                      int cta, int lane, int g, int t) {
+__device__ __noinline__ void flush(const GemvArgs& p, const float* acc, int rt256, int w, int G, int cta, int lane,
+                                   int g, int t) {
   const int rt16 = rt256 * 16 + w;
   const int row0 = rt16 * 16;
   if (rt16 >= p.n_rt16) return;
-  if (nblk == p.nb) {
+  const int span_lo = rt256 * p.nb * 16;
+  const int c_first = owner_of(p.S, G, span_lo);
+  const int c_last = owner_of(p.S, G, span_lo + p.nb * 16 - 1);
+  const int n_contrib = c_last - c_first + 1;
+  if (n_contrib == 1) {
 #pragma unroll
     for (int h = 0; h < NB / 8; ++h) {
       emit(p, row0 + g, 8 * h + 2 * t, acc[4 * h + 0]);
@@ -274,39 +282,28 @@ __device__ __noinline__ void flush(const GemvArgs& p, float acc[NB / 2], int rt2
     }
     return;
   }
-  const int span_lo = rt256 * p.nb * 16;
-  const int span_hi = span_lo + p.nb * 16;
-  const int c_first = owner_of(p.S, G, span_lo);
-  const int c_last = owner_of(p.S, G, span_hi - 1);
   const int tile_elems = 16 * p.batch;
-  float* mine = p.ws_part + ((int64_t)rt16 * p.max_slots + (cta - c_first)) * tile_elems;
+  float* tile_ws = p.ws_part + (int64_t)rt16 * p.max_slots * tile_elems;
+  float* mine = tile_ws + (cta - c_first) * tile_elems;
 #pragma unroll
   for (int h = 0; h < NB / 8; ++h) {
     const int m0 = 8 * h + 2 * t;
     if (m0 < p.batch) { mine[m0 * 16 + g] = acc[4 * h + 0]; mine[m0 * 16 + g + 8] = acc[4 * h + 2]; }
     if (m0 + 1 < p.batch) { mine[(m0 + 1) * 16 + g] = acc[4 * h + 1]; mine[(m0 + 1) * 16 + g + 8] = acc[4 * h + 3]; }
   }
-  __threadfence();
-  __syncwarp();
+  __syncwarp();  // orders the lanes' stores before lane 0's release
   unsigned old = 0;
-  if (lane == 0) old = atomicAdd(p.ws_cnt + rt16, (unsigned)nblk);
+  if (lane == 0)
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.ws_cnt + rt16) : "memory");
   old = __shfl_sync(0xffffffffu, old, 0);
-  if (old + (unsigned)nblk != (unsigned)p.nb) return;
-  __threadfence();
-  // this warp completed the tile: sum partials in CTA order (fixed, independent of arrival)
-  // (all loads of a group of eight partials are issued before the first add)
+  if ((int)old + 1 != n_contrib) return;
+  __syncwarp();  // lane 0's acquire happens before the other lanes' reads
   for (int e = lane; e < tile_elems; e += 32) {
     float s = 0.f;
-    for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+    for (int c0 = 0; c0 < n_contrib; c0 += 8) {  // eight loads in flight, then eight adds in slot order
       float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int c = c0 + u;
-        int qs = 0, qe = 0;
-        if (c <= c_last)
-          warp_q_range(range_start(p.S, G, c), range_start(p.S, G, c + 1), w, span_lo >> 4, span_hi >> 4, qs, qe);
-        v[u] = qe > qs ? __ldcg(p.ws_part + ((int64_t)rt16 * p.max_slots + (c - c_first)) * tile_elems + e) : 0.f;
-      }
+      for (int u = 0; u < 8; ++u) v[u] = c0 + u < n_contrib ? __ldcg(tile_ws + (c0 + u) * tile_elems + e) : 0.f;
 #pragma unroll
       for (int u = 0; u < 8; ++u) s += v[u];
     }
@@ -457,9 +454,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   // so they are requested right away; the activations and the scratch buffer belong to
   // the previous kernel until griddepcontrol.wait returns.
   asm volatile("griddepcontrol.launch_dependents;");
-  float ct_mine;
-  if (PACKED) ct_mine = (lane & 15) < p.n_levels ? __ldg(p.ct + (lane & 15)) : 0.f;
-  else ct_mine = (w + 16 * (lane & 15)) < p.n_levels ? __ldg(p.ct + w + 16 * (lane & 15)) : 0.f;
+  // (volatile asm loads: the compiler must not sink them to their first use, which is
+  // after the dependency wait)
+  float ct_mine = 0.f;
+  {
+    const int e = PACKED ? (lane & 15) : (w + 16 * (lane & 15));
+    if (e < p.n_levels) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(ct_mine) : "l"(p.ct + e));
+  }
 
   const int cnt0 = (Q1 - Q0) < p.cap ? (Q1 - Q0) : p.cap;
   // slot `lane` of the first phase
@@ -470,9 +471,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
 #pragma unroll
   for (int u = 0; u < NU; ++u) {
     const int grow = my_rt * kRowsPerCta + w + u * kWarps;
-    nv[u] = (lane < cnt0 && grow < p.N)
-                ? __ldg(reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)grow * p.ld_norms + my_blk)
-                : (unsigned short)0;
+    nv[u] = 0;
+    if (lane < cnt0 && grow < p.N)
+      asm volatile("ld.global.nc.u16 %0, [%1];"
+                   : "=h"(nv[u])
+                   : "l"(reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)grow * p.ld_norms + my_blk));
   }
   // first activation item of this warp (raw input): slot = item / batch, row = item % batch
   const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
@@ -550,6 +553,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
 #pragma unroll
   for (int i = 0; i < NB / 2; ++i) acc[i] = 0.f;
   int run = 0;  // blocks accumulated for the current row tile
+  float zeros[NB / 2];
+#pragma unroll
+  for (int i = 0; i < NB / 2; ++i) zeros[i] = 0.f;
+  const int span = p.nb * 16;
+  int next_flush = s_beg / span;                                      // first row-tile-of-256 the CTA touches
+  const int last_tile = s_end > s_beg ? (s_end - 1) / span : next_flush - 1;  // last one
 
   int q = q_lo;
   bool first_phase = true;
@@ -597,7 +606,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
           ++run;
           ++q;
           if (++b_c == p.nb) {  // row tile finished on our side
-            flush<NB>(p, acc, rt_c, w, run, G, cta, lane, g, t);
+            for (; next_flush < rt_c; ++next_flush) flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t);
+            flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t);
+            next_flush = rt_c + 1;
 #pragma unroll
             for (int i = 0; i < NB / 2; ++i) acc[i] = 0.f;
             run = 0;
@@ -609,7 +620,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
     }
   }
   PE_STAMP(5);
-  if (run > 0) flush<NB>(p, acc, rt_c, w, run, G, cta, lane, g, t);
+  // every row-tile-of-256 this CTA's range touches gets a hand-off from every warp
+  if (run > 0) {
+    for (; next_flush < rt_c; ++next_flush) flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t);
+    flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t);
+    next_flush = rt_c + 1;
+  }
+  for (; next_flush <= last_tile; ++next_flush) flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t);
   PE_STAMP(6);
 }
 
