@@ -177,6 +177,78 @@ def prefill_sweep(a, dev, rank, world):
             "gpu_launches": 2 * 3 * steps}))
 
 
+def model_decode(a, dev, rank, world):
+    """BASELINE configs[3]: prompt of random ids, then greedy decode; every projection, the embedding and the LM
+    head are quantized; tensor parallel over the ranks (column q/k/v/gate/up, row o/down + NCCL all-reduce).
+    The decode step is captured in a CUDA graph.  value = batch * new_tokens / time (tok/s), strong scaling."""
+    import torch.distributed as dist
+    from polarengine_vllm_b200.decoder import DecoderConfig, QuantDecoder
+    cfg = DecoderConfig(n_layers=a.layers)
+    b = a.batch
+    model = QuantDecoder(cfg, dev, rank, world, None, max_len=a.prompt + a.new_tokens + 8, batch=b)
+    g = torch.Generator(device=dev).manual_seed(17)
+    prompt = torch.randint(0, cfg.vocab, (b, a.prompt), device=dev, generator=g)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    nxt = model.forward(prompt, 0)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    ids_buf = nxt.view(b, 1).clone()
+    pos = torch.tensor(a.prompt, device=dev, dtype=torch.int64)
+    stream = torch.cuda.Stream(dev)
+    def step():
+        out = model.forward(ids_buf, pos, model.decode_mask(pos))
+        ids_buf.copy_(out.view(b, 1))
+        pos.add_(1)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        torch.cuda.synchronize()
+        pos.fill_(a.prompt)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(a.new_tokens):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        sampler.stop_flag = True
+        if world > 1:
+            dist.barrier()
+    el = e0.elapsed_time(e1) / 1e3
+    if world > 1:
+        t = torch.tensor([el], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        el = float(t)
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        wb = model.weight_bytes_per_step()
+        print(json.dumps({
+            "metric": "9B-class decode tok/s", "unit": "tok/s", "value": b * a.new_tokens / el, "n_gpus": a.gpus,
+            "steps": a.new_tokens, "warmup": 3, "ms_per_step": el / a.new_tokens * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers, hidden 4096, vocab 151936, "
+                                   f"prompt {a.prompt}, {a.new_tokens} new tokens", "batch": b,
+                       "parallelism": f"tp{world}", "l2_defeat": "weights per rank larger than L2"},
+            "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
+            "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
+            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (4 * a.layers + 2)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,8 +257,12 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: decoder-layer GEMV pass (default, the headline); prefill: Q4 GEMM sweep of BASELINE configs[2]")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
+                    help="decode: decoder-layer GEMV pass (default, the headline); prefill: Q4 GEMM sweep of BASELINE "
+                         "configs[2]; model: 36-layer 9B-class decode tok/s, tensor parallel over --gpus (configs[3])")
+    ap.add_argument("--layers", type=int, default=36, help="decoder layers for --workload model")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
     ap.add_argument("--probe", default=None, metavar="PROJ",
                     help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
@@ -224,6 +300,8 @@ def main():
     from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
     if a.workload == "prefill":
         return prefill_sweep(a, dev, rank, world)
+    if a.workload == "model":
+        return model_decode(a, dev, rank, world)
 
     steps = max(RING, a.steps // RING * RING)
     warm = max(3, a.warmup)
