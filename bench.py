@@ -204,9 +204,12 @@ def model_decode(a, dev, rank, world):
         for _ in range(3):
             step()
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step()
+        graph = None
+        if not a.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            # thread_local: the NCCL watchdog thread may query events while this thread captures
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                step()
         torch.cuda.synchronize()
         pos.fill_(a.prompt)
         if world > 1:
@@ -217,7 +220,10 @@ def model_decode(a, dev, rank, world):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(a.new_tokens):
-            graph.replay()
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
         e1.record(stream)
         torch.cuda.synchronize()
         sampler.stop_flag = True
@@ -241,12 +247,25 @@ def model_decode(a, dev, rank, world):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers, hidden 4096, vocab 151936, "
                                    f"prompt {a.prompt}, {a.new_tokens} new tokens", "batch": b,
-                       "parallelism": f"tp{world}", "l2_defeat": "weights per rank larger than L2"},
+                       "parallelism": f"tp{world}", "l2_defeat": "weights per rank larger than L2",
+                       "launch": "eager" if a.no_graph else "cuda graph"},
             "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
             "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
             "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (4 * a.layers + 2)}))
+    finish(world)
+
+
+def finish(world):
+    """Leave a multi-rank run.  Tearing down the NCCL communicator while captured graphs that contain its kernels are
+    alive can block forever; the ranks synchronise and exit without running the destructors instead."""
     if world > 1:
-        dist.destroy_process_group()
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -263,6 +282,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36, help="decoder layers for --workload model")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--no-graph", action="store_true", help="model workload: launch decode steps eagerly")
     ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
     ap.add_argument("--probe", default=None, metavar="PROJ",
                     help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
@@ -299,7 +319,8 @@ def main():
     from polarengine_vllm_b200 import kernels
     from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
     if a.workload == "prefill":
-        return prefill_sweep(a, dev, rank, world)
+        prefill_sweep(a, dev, rank, world)
+        return finish(world)
     if a.workload == "model":
         return model_decode(a, dev, rank, world)
 
@@ -437,8 +458,7 @@ def main():
         if not a.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline(a.batch)
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    finish(world)
 
 
 if __name__ == "__main__":
