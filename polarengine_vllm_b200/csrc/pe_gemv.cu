@@ -40,7 +40,8 @@ constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRowsPerCta = kWarps * 16;  // 256
 constexpr int kXRowBytes = 320;           // 256 B of activations + 64 B pad (bank spread)
-constexpr int kLutSpan = 65536;
+constexpr int kLutBytes = 32768;          // 256 entries x 32 lanes x 4 B (entry e of lane l at e*128 + l*4)
+constexpr int kRingPerWarp = 8192;        // bytes of code stream each warp keeps in flight
 
 struct GemvArgs {
   const uint8_t* codes; int64_t ld_codes;
@@ -54,7 +55,7 @@ struct GemvArgs {
   int S;             // total steps = n_rt256 * nb * 16 (S * grid < 2^31)
   int cap;           // activation slots resident in shared memory per phase
   int max_slots;     // scratch partials per 16-row tile
-  float* ws_part; unsigned* ws_cnt;
+  float* ws_part; unsigned* ws_cnt; int* ws_status;
   unsigned dyn_bytes;
   long long* prof;  // optional per-warp time stamps (developer builds with -DPE_PROFILE)
 };
@@ -72,7 +73,6 @@ __device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, u
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// A table address is {lane_base byte3, lane_base byte2, code byte, lane_base byte0}.
 // low half of a, high half of b
 __device__ __forceinline__ uint32_t lo_hi(uint32_t a, uint32_t b) {
   uint32_t r;
@@ -100,38 +100,74 @@ struct CodeRegs {
   uint4 a1, b1;  // second 16 B (byte codes only)
 };
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// Request one step's codes (rows g and g+8 of a 16-row tile, one 128-block) into this
+// lane's slots of a ring stage: 16-byte asynchronous copies, no registers held while the
+// data is in flight.  Stage layout: [piece 0..(1|3)][lane] x 16 B, so a warp reads it back
+// with conflict-free 128-bit loads.
 template <bool PACKED>
-__device__ __forceinline__ void fetch(CodeRegs<PACKED>& r, const GemvArgs& p, int rt256, int b, int w, int g, int t) {
+__device__ __forceinline__ void fetch(uint32_t stage, const GemvArgs& p, int rt256, int b, int w, int g, int t, int lane) {
   int rowA = rt256 * kRowsPerCta + w * 16 + g;
   int rowB = rowA + 8;
   rowA = rowA < p.N ? rowA : p.N - 1;
   rowB = rowB < p.N ? rowB : p.N - 1;
+  const uint32_t dst = stage + lane * 16;
   if (PACKED) {
-    const uint8_t* pa = p.codes + (int64_t)rowA * p.ld_codes + b * 64 + t * 16;
-    const uint8_t* pb = p.codes + (int64_t)rowB * p.ld_codes + b * 64 + t * 16;
-    r.a0 = ldg_stream(pa);
-    r.b0 = ldg_stream(pb);
+    cp_async16(dst, p.codes + (int64_t)rowA * p.ld_codes + b * 64 + t * 16);
+    cp_async16(dst + 512, p.codes + (int64_t)rowB * p.ld_codes + b * 64 + t * 16);
   } else {
     const uint8_t* pa = p.codes + (int64_t)rowA * p.ld_codes + b * 128 + t * 32;
     const uint8_t* pb = p.codes + (int64_t)rowB * p.ld_codes + b * 128 + t * 32;
-    r.a0 = ldg_stream(pa);
-    r.a1 = ldg_stream(pa + 16);
-    r.b0 = ldg_stream(pb);
-    r.b1 = ldg_stream(pb + 16);
+    cp_async16(dst, pa);
+    cp_async16(dst + 512, pb);
+    cp_async16(dst + 1024, pa + 16);
+    cp_async16(dst + 1536, pb + 16);
   }
 }
 
-// table address of byte BYTE of a code word (see lut_ld)
+template <bool PACKED>
+__device__ __forceinline__ void read_stage(CodeRegs<PACKED>& r, const uint8_t* stage, int lane) {
+  const uint4* s4 = reinterpret_cast<const uint4*>(stage) + lane;
+  r.a0 = s4[0];
+  r.b0 = s4[32];
+  if (!PACKED) { r.a1 = s4[64]; r.b1 = s4[96]; }
+}
+
+// table address of byte BYTE of a code word: table + byte * 128 + lane * 4
 template <int BYTE>
 __device__ __forceinline__ uint32_t lut_addr(uint32_t word, uint32_t lane_base) {
-  uint32_t addr;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(word), "r"(lane_base), "n"(0x7604 | (BYTE << 4)));
-  return addr;
+  uint32_t bt;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(bt) : "r"(word), "r"(0), "n"(0x4440 | BYTE));
+  return bt * 128u + lane_base;
 }
 __device__ __forceinline__ uint32_t lut_ld(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
+}
+
+// Register-resident centroid table for layers with at most 8 levels (3-bit codes stored in
+// nibbles): the low and the high byte of the eight fp16 centroids sit in two register
+// pairs, and one byte-permute looks four codes up at once -- a nibble 0..7 IS a valid
+// permute selector.  Two more permutes interleave low and high bytes into the fp16 pairs
+// (ct[lo nibble], ct[hi nibble]) the MMA wants.  No shared-memory traffic at all, which is
+// what bounds the table-lookup path.
+struct RegTable { uint32_t lo0, lo1, hi0, hi1; };
+
+// word (4 code bytes) -> the four A registers of its bytes 0..3
+__device__ __forceinline__ void reg_decode(uint32_t w, const RegTable& tb, uint32_t out[4]) {
+  uint32_t L, H, w2 = w >> 16;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(L) : "r"(tb.lo0), "r"(tb.lo1), "r"(w));
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(H) : "r"(tb.hi0), "r"(tb.hi1), "r"(w));
+  asm("prmt.b32 %0, %1, %2, 0x5140;" : "=r"(out[0]) : "r"(L), "r"(H));
+  asm("prmt.b32 %0, %1, %2, 0x7362;" : "=r"(out[1]) : "r"(L), "r"(H));
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(L) : "r"(tb.lo0), "r"(tb.lo1), "r"(w2));
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(H) : "r"(tb.hi0), "r"(tb.hi1), "r"(w2));
+  asm("prmt.b32 %0, %1, %2, 0x5140;" : "=r"(out[2]) : "r"(L), "r"(H));
+  asm("prmt.b32 %0, %1, %2, 0x7362;" : "=r"(out[3]) : "r"(L), "r"(H));
 }
 
 // Four MMAs (16 rows x 64 k) from two code words of row g (wa) and of row g+8 (wb).
@@ -140,12 +176,28 @@ __device__ __forceinline__ uint32_t lut_ld(uint32_t addr) {
 // predecessor.
 //  PACKED: word i holds bytes for MMAs 2i (bytes 0,1) and 2i+1 (bytes 2,3).
 //  !PACKED: the caller passes four words per row; word i is MMA i (codes 0,1 | 2,3).
-template <bool PACKED, int NB>
+template <bool PACKED, int NB, bool REGTAB>
 __device__ __forceinline__ void quad_mma(float d0[NB / 2], float d1[NB / 2], const uint32_t* wa, const uint32_t* wb,
-                                         uint32_t lane_base, const uint4& xa, const uint4& xb, const uint4& ya,
-                                         const uint4& yb) {
+                                         uint32_t lane_base, const RegTable& tb, const uint4& xa, const uint4& xb,
+                                         const uint4& ya, const uint4& yb) {
   uint32_t ad[16], v[16];
-  if (PACKED) {
+  if (PACKED && REGTAB) {
+    uint32_t a0[4], b0[4], a1[4], b1[4];  // bytes 0..3 of wa[0], wb[0], wa[1], wb[1]
+    reg_decode(wa[0], tb, a0);
+    reg_decode(wb[0], tb, b0);
+    reg_decode(wa[1], tb, a1);
+    reg_decode(wb[1], tb, b1);
+    mma16816(d0, a0[0], b0[0], a0[1], b0[1], xa.x, xa.y);
+    mma16816(d1, a0[2], b0[2], a0[3], b0[3], xa.z, xa.w);
+    mma16816(d0, a1[0], b1[0], a1[1], b1[1], xb.x, xb.y);
+    mma16816(d1, a1[2], b1[2], a1[3], b1[3], xb.z, xb.w);
+    if (NB == 16) {
+      mma16816(d0 + 4, a0[0], b0[0], a0[1], b0[1], ya.x, ya.y);
+      mma16816(d1 + 4, a0[2], b0[2], a0[3], b0[3], ya.z, ya.w);
+      mma16816(d0 + 4, a1[0], b1[0], a1[1], b1[1], yb.x, yb.y);
+      mma16816(d1 + 4, a1[2], b1[2], a1[3], b1[3], yb.z, yb.w);
+    }
+  } else if (PACKED) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       ad[8 * i + 0] = lut_addr<0>(wa[i], lane_base);
@@ -201,9 +253,10 @@ __device__ __forceinline__ void quad_mma(float d0[NB / 2], float d1[NB / 2], con
   }
 }
 
-template <bool PACKED, int NB>
+template <bool PACKED, int NB, bool REGTAB>
 __device__ __forceinline__ void step_math(float acc[NB / 2], const CodeRegs<PACKED>& r, uint32_t lane_base,
-                                          const uint8_t* xslot, float nA, float nB, int g, int t, int batch) {
+                                          const RegTable& tb, const uint8_t* xslot, float nA, float nB, int g, int t,
+                                          int batch) {
   // activation fragments of this block: 4 x 16 B per 8 rows of batch.  Lanes whose batch
   // row does not exist skip the load (their MMA columns are never read), which also
   // shrinks the shared-memory transaction to the quarter-warps that hold live rows.
@@ -228,13 +281,13 @@ __device__ __forceinline__ void step_math(float acc[NB / 2], const CodeRegs<PACK
   if (PACKED) {
     const uint32_t wa[4] = {r.a0.x, r.a0.y, r.a0.z, r.a0.w};
     const uint32_t wb[4] = {r.b0.x, r.b0.y, r.b0.z, r.b0.w};
-    quad_mma<true, NB>(d0, d1, wa, wb, lane_base, xf[0], xf[1], yf[0], yf[1]);
-    quad_mma<true, NB>(d0, d1, wa + 2, wb + 2, lane_base, xf[2], xf[3], yf[2], yf[3]);
+    quad_mma<true, NB, REGTAB>(d0, d1, wa, wb, lane_base, tb, xf[0], xf[1], yf[0], yf[1]);
+    quad_mma<true, NB, REGTAB>(d0, d1, wa + 2, wb + 2, lane_base, tb, xf[2], xf[3], yf[2], yf[3]);
   } else {
     const uint32_t wa[8] = {r.a0.x, r.a0.y, r.a0.z, r.a0.w, r.a1.x, r.a1.y, r.a1.z, r.a1.w};
     const uint32_t wb[8] = {r.b0.x, r.b0.y, r.b0.z, r.b0.w, r.b1.x, r.b1.y, r.b1.z, r.b1.w};
-    quad_mma<false, NB>(d0, d1, wa, wb, lane_base, xf[0], xf[1], yf[0], yf[1]);
-    quad_mma<false, NB>(d0, d1, wa + 4, wb + 4, lane_base, xf[2], xf[3], yf[2], yf[3]);
+    quad_mma<false, NB, false>(d0, d1, wa, wb, lane_base, tb, xf[0], xf[1], yf[0], yf[1]);
+    quad_mma<false, NB, false>(d0, d1, wa + 4, wb + 4, lane_base, tb, xf[2], xf[3], yf[2], yf[3]);
   }
   acc[0] = fmaf(nA, d0[0] + d1[0], acc[0]);
   acc[1] = fmaf(nA, d0[1] + d1[1], acc[1]);
@@ -257,22 +310,23 @@ __device__ __forceinline__ void emit(const GemvArgs& p, int row, int m, float v)
 }
 
 // Hand-off of one 16-row tile at the end of this CTA's share of it.  Every CTA whose range
-// touches the tile's row-tile-of-256 leaves exactly one fp32 partial per warp lane-set
-// (zeros if none of the tile's steps fell to this warp), then bumps the tile's counter with
-// a release; the arrival that completes the count acquires, sums the partials in CTA order
-// (fixed, whatever the arrival order: bit-reproducible), adds the bias, converts, stores,
-// and returns the counter to zero.  A tile owned by a single CTA is stored directly.
+// touches the tile's row-tile-of-256 leaves exactly one fp32 partial per warp (zeros if none
+// of the tile's steps fell to this warp) and bumps the tile's counter with a release --
+// fire and forget, nobody waits here.  The CTA that owns the tile's LAST step is its
+// reducer: at the very end of the kernel (reduce_tile) it waits, bounded, for the count,
+// sums the partials in CTA order (fixed, whatever the arrival order: bit-reproducible),
+// adds the bias, converts, stores, and returns the counter to zero.  A tile owned by a
+// single CTA is stored directly.  Returns true if this warp must reduce the tile later.
 template <int NB>
-__device__ __noinline__ void flush(const GemvArgs& p, const float* acc, int rt256, int w, int G, int cta, int lane,
+__device__ __noinline__ bool flush(const GemvArgs& p, const float* acc, int rt256, int w, int G, int cta, int lane,
                                    int g, int t) {
   const int rt16 = rt256 * 16 + w;
   const int row0 = rt16 * 16;
-  if (rt16 >= p.n_rt16) return;
+  if (rt16 >= p.n_rt16) return false;
   const int span_lo = rt256 * p.nb * 16;
   const int c_first = owner_of(p.S, G, span_lo);
   const int c_last = owner_of(p.S, G, span_lo + p.nb * 16 - 1);
-  const int n_contrib = c_last - c_first + 1;
-  if (n_contrib == 1) {
+  if (c_last == c_first) {
 #pragma unroll
     for (int h = 0; h < NB / 8; ++h) {
       emit(p, row0 + g, 8 * h + 2 * t, acc[4 * h + 0]);
@@ -280,11 +334,10 @@ __device__ __noinline__ void flush(const GemvArgs& p, const float* acc, int rt25
       emit(p, row0 + g + 8, 8 * h + 2 * t, acc[4 * h + 2]);
       emit(p, row0 + g + 8, 8 * h + 2 * t + 1, acc[4 * h + 3]);
     }
-    return;
+    return false;
   }
   const int tile_elems = 16 * p.batch;
-  float* tile_ws = p.ws_part + (int64_t)rt16 * p.max_slots * tile_elems;
-  float* mine = tile_ws + (cta - c_first) * tile_elems;
+  float* mine = p.ws_part + ((int64_t)rt16 * p.max_slots + (cta - c_first)) * tile_elems;
 #pragma unroll
   for (int h = 0; h < NB / 8; ++h) {
     const int m0 = 8 * h + 2 * t;
@@ -292,11 +345,35 @@ __device__ __noinline__ void flush(const GemvArgs& p, const float* acc, int rt25
     if (m0 + 1 < p.batch) { mine[(m0 + 1) * 16 + g] = acc[4 * h + 1]; mine[(m0 + 1) * 16 + g + 8] = acc[4 * h + 3]; }
   }
   __syncwarp();  // orders the lanes' stores before lane 0's release
-  unsigned old = 0;
-  if (lane == 0)
-    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.ws_cnt + rt16) : "memory");
-  old = __shfl_sync(0xffffffffu, old, 0);
-  if ((int)old + 1 != n_contrib) return;
+  if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ws_cnt + rt16) : "memory");
+  return cta == c_last;
+}
+
+// The reducer's half of the hand-off (see flush).  The wait is bounded: if the count does
+// not arrive the tile is left unwritten and the scratch's status word is set.
+__device__ __noinline__ void reduce_tile(const GemvArgs& p, int rt256, int w, int G, int lane) {
+  const int rt16 = rt256 * 16 + w;
+  const int row0 = rt16 * 16;
+  const int span_lo = rt256 * p.nb * 16;
+  const int c_first = owner_of(p.S, G, span_lo);
+  const int n_contrib = owner_of(p.S, G, span_lo + p.nb * 16 - 1) - c_first + 1;
+  const int tile_elems = 16 * p.batch;
+  const float* tile_ws = p.ws_part + (int64_t)rt16 * p.max_slots * tile_elems;
+  int ok = 1;
+  if (lane == 0) {
+    unsigned seen = 0;
+    const long long t0 = clock64();
+    for (;;) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.ws_cnt + rt16) : "memory");
+      if ((int)seen >= n_contrib) break;
+      if (clock64() - t0 > (1ll << 30)) { ok = 0; break; }  // ~0.5 s: something is badly wrong
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (!ok) {
+    if (lane == 0) atomicExch(p.ws_status, 1);
+    return;
+  }
   __syncwarp();  // lane 0's acquire happens before the other lanes' reads
   for (int e = lane; e < tile_elems; e += 32) {
     float s = 0.f;
@@ -336,7 +413,7 @@ __device__ __forceinline__ void place_block(uint8_t* row, const float v[4], int 
 // that a warp pays one memory latency per group, not one per item.
 template <bool PACKED>
 __device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* slot_blk, int cnt, int warp, int lane) {
-  const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
+  const int slot_bytes = p.batch * kXRowBytes;
   const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
   const int items = cnt * p.batch;
   if (p.x_kind == PE_X_RAW) {
@@ -428,7 +505,7 @@ __device__ __noinline__ void stage_norms(const GemvArgs& p, __half* ns, int nstr
   }
 }
 
-template <bool PACKED, int NB, int DEPTH>
+template <bool PACKED, int NB, int DEPTH, bool REGTAB>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int slot_rt[32], slot_blk[32];
@@ -446,9 +523,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   // ---- everything the prologue needs from memory is requested here, before any of it
   // is used, so that the prologue costs one memory latency: codes, centroids, norms and
   // the first group of activations.
-  CodeRegs<PACKED> ring[DEPTH];
   int rt_c = q_lo / p.nb, b_c = q_lo - rt_c * p.nb;  // compute cursor
-  int rt_f = rt_c, b_f = b_c;                        // fetch cursor
+  int rt_f = rt_c, b_f = b_c, q_f = q_lo;            // fetch cursor (runs kDepth-1 steps ahead)
   // Programmatic dependent launch: this grid may have been started while the previous
   // kernel in the stream was still draining.  Weights, norms and centroids never change,
   // so they are requested right away; the activations and the scratch buffer belong to
@@ -478,7 +554,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
                    : "l"(reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)grow * p.ld_norms + my_blk));
   }
   // first activation item of this warp (raw input): slot = item / batch, row = item % batch
-  const int slot_bytes = ((p.batch + 7) & ~7) * kXRowBytes;
+  const int slot_bytes = p.batch * kXRowBytes;
   const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
   const int items0 = cnt0 * p.batch;
   float xv[4];
@@ -492,42 +568,63 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
     load4_as_float(p.x, p.x_dtype, (int64_t)x_m * p.ld_x, (qq % p.nb) * kBlock + lane * 4, on ? p.in_f : 0, vec_ok, xv);
   }
 
+  // ---- shared memory: [table 32 KB][activation slots][norms][code ring 16 x 8 KB]
+  uint8_t* lut_g = smem;
+  const uint32_t lut_s = smem_u32(smem);
+  uint8_t* xs = lut_g + kLutBytes;
+  const int nstr = p.cap + 2;
+  __half* ns = reinterpret_cast<__half*>(xs + (size_t)p.cap * slot_bytes);
+  constexpr int kStage = PACKED ? 1024 : 2048;      // bytes of one step's codes per warp
+  constexpr int kDepth = DEPTH;                     // ring stages per warp
+  uint8_t* ring_g = reinterpret_cast<uint8_t*>(ns) + ((kRowsPerCta * nstr * 2 + 15) & ~15) + w * (kDepth * kStage);
+  const uint32_t ring_s = smem_u32(ring_g);
   // the code stream goes last: it is the bulk, and whatever is requested after it
-  // would queue behind megabytes of it in the memory system
+  // would queue behind megabytes of it in the memory system.  The ring is filled and
+  // refilled kBatch steps at a time: consecutive steps of a warp are consecutive 64-byte
+  // (128-byte) pieces of the same 16 rows, so requesting them together gives the DRAM
+  // controller 256 contiguous bytes per row instead of one burst per row activation.
+  constexpr int kBatch = 1;  // steps per refill (larger batches measured slower: fewer bytes in flight)
 #pragma unroll
-  for (int d = 0; d < DEPTH; ++d) {
-    if (q_lo + d < q_hi) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
-    if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+  for (int d = 0; d < kDepth; ++d) {
+    if (q_f < q_hi) {
+      fetch<PACKED>(ring_s + (q_f % kDepth) * kStage, p, rt_f, b_f, w, g, t, lane);
+      if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+      ++q_f;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   }
 
   PE_STAMP(7);
-  // ---- shared memory carve-up: [pad][table 64 KB-aligned][activation slots][norms]
-  const uint32_t s0 = smem_u32(smem);
-  // The table always owns a full 64 KB so that any code byte, valid or not, stays inside it.
-  const uint32_t lut_s = (s0 + kLutSpan - 1) & ~(uint32_t)(kLutSpan - 1);
-  uint8_t* lut_g = smem + (lut_s - s0);
-  uint8_t* xs = lut_g + kLutSpan;
-  const int nstr = p.cap + 2;
-  __half* ns = reinterpret_cast<__half*>(xs + (size_t)p.cap * slot_bytes);
   if (lane < cnt0 && w == 0) { slot_rt[lane] = my_rt; slot_blk[lane] = my_blk; }
 
   // ---- centroid table, replicated per lane.  Warp w writes entries w, w+16, ...; the
   // levels came with one load per lane and travel by shuffle.
-  if (PACKED) {
+  if (PACKED && REGTAB) {
+    // no shared table: the centroids live in registers (below)
+  } else if (PACKED) {
     const float lo = __shfl_sync(0xffffffffu, ct_mine, w);  // entry e = w + 16 i: low nibble w, high nibble i
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float hi = __shfl_sync(0xffffffffu, ct_mine, i);
-      *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 256 + lane * 4) = pack_half2(lo, hi);
+      *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 128 + lane * 4) = pack_half2(lo, hi);
     }
   } else {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float c = __shfl_sync(0xffffffffu, ct_mine, i);
-      if (w + 16 * i < p.n_levels) *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 256 + lane * 4) = pack_half2(c, c);
+      if (w + 16 * i < p.n_levels) *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 128 + lane * 4) = pack_half2(c, c);
     }
   }
   const uint32_t lane_base = lut_s + lane * 4;
+  RegTable tb = {0, 0, 0, 0};
+  if (PACKED && REGTAB) {  // fp16 bits of ct[0..7], split into low-byte and high-byte tables
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t hb = __half_as_ushort(__float2half_rn(__shfl_sync(0xffffffffu, ct_mine, i)));
+      if (i < 4) { tb.lo0 |= (hb & 0xff) << (8 * i); tb.hi0 |= (hb >> 8) << (8 * i); }
+      else { tb.lo1 |= (hb & 0xff) << (8 * (i - 4)); tb.hi1 |= (hb >> 8) << (8 * (i - 4)); }
+    }
+  }
   PE_STAMP(1);
   if (lane < cnt0) {
 #pragma unroll
@@ -557,11 +654,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
 #pragma unroll
   for (int i = 0; i < NB / 2; ++i) zeros[i] = 0.f;
   const int span = p.nb * 16;
+  int pending = -1;                                                   // tile this warp must reduce at the end
   int next_flush = s_beg / span;                                      // first row-tile-of-256 the CTA touches
   const int last_tile = s_end > s_beg ? (s_end - 1) / span : next_flush - 1;  // last one
 
   int q = q_lo;
   bool first_phase = true;
+  __syncwarp();
   for (int ph = Q0; ph < Q1; ph += p.cap) {
     const int cnt = (Q1 - ph) < p.cap ? (Q1 - ph) : p.cap;
     const int ph_end = ph + cnt;
@@ -578,36 +677,45 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
     }
     __syncthreads();
     PE_STAMP(4);
-    if (!first_phase) {
-      // refill the ring after a phase break
-      rt_f = rt_c; b_f = b_c;
-#pragma unroll
-      for (int d = 0; d < DEPTH; ++d) {
-        if (q + d < q_hi) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
-        if (++b_f == p.nb) { b_f = 0; ++rt_f; }
-      }
-    }
     first_phase = false;
     const int q_stop = q_hi < ph_end ? q_hi : ph_end;
-    const bool last_phase = ph_end >= Q1;
     while (q < q_stop) {
-#pragma unroll
-      for (int d = 0; d < DEPTH; ++d) {
-        if (q < q_stop) {
-          const CodeRegs<PACKED> cur = ring[d];
-          // keep the ring full, but never past this phase when another one follows
-          // (the ring is refilled after the barrier)
-          if (q + DEPTH < q_hi && (last_phase || q + DEPTH < ph_end)) fetch<PACKED>(ring[d], p, rt_f, b_f, w, g, t);
-          if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+      {
+        {
+          // Groups are committed one per step, kDepth up front and kBatch more after every
+          // kBatch-th step, so step i's group is complete once at most
+          // kDepth - 1 - (i % kBatch) younger groups are pending.
+          const int i_step = q - q_lo;
+          switch (i_step % kBatch) {
+            case 0: asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory"); break;
+            case 1: asm volatile("cp.async.wait_group %0;" ::"n"(kDepth > 2 ? kDepth - 2 : 0) : "memory"); break;
+            case 2: asm volatile("cp.async.wait_group %0;" ::"n"(kDepth > 3 ? kDepth - 3 : 0) : "memory"); break;
+            default: asm volatile("cp.async.wait_group %0;" ::"n"(kDepth > 4 ? kDepth - 4 : 0) : "memory"); break;
+          }
+          CodeRegs<PACKED> cur;
+          read_stage<PACKED>(cur, ring_g + (q % kDepth) * kStage, lane);
           const int slot = q - ph;
           const float nA = __half2float(ns[(w * 16 + g) * nstr + slot]);
           const float nB = __half2float(ns[(w * 16 + g + 8) * nstr + slot]);
-          step_math<PACKED, NB>(acc, cur, lane_base, xs + slot * slot_bytes, nA, nB, g, t, p.batch);
+          step_math<PACKED, NB, REGTAB>(acc, cur, lane_base, tb, xs + slot * slot_bytes, nA, nB, g, t, p.batch);
           ++run;
           ++q;
+          if (i_step % kBatch == kBatch - 1) {
+            // the kBatch stages just consumed are free (their reads fed the math above)
+#pragma unroll
+            for (int d = 0; d < kBatch; ++d) {
+              if (q_f < q_hi) {
+                fetch<PACKED>(ring_s + (q_f % kDepth) * kStage, p, rt_f, b_f, w, g, t, lane);
+                if (++b_f == p.nb) { b_f = 0; ++rt_f; }
+                ++q_f;
+              }
+              asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+          }
           if (++b_c == p.nb) {  // row tile finished on our side
-            for (; next_flush < rt_c; ++next_flush) flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t);
-            flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t);
+            for (; next_flush < rt_c; ++next_flush)
+              if (flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t)) pending = next_flush;
+            if (flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t)) pending = rt_c;
             next_flush = rt_c + 1;
 #pragma unroll
             for (int i = 0; i < NB / 2; ++i) acc[i] = 0.f;
@@ -622,30 +730,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   PE_STAMP(5);
   // every row-tile-of-256 this CTA's range touches gets a hand-off from every warp
   if (run > 0) {
-    for (; next_flush < rt_c; ++next_flush) flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t);
-    flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t);
+    for (; next_flush < rt_c; ++next_flush)
+      if (flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t)) pending = next_flush;
+    if (flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t)) pending = rt_c;
     next_flush = rt_c + 1;
   }
-  for (; next_flush <= last_tile; ++next_flush) flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t);
+  for (; next_flush <= last_tile; ++next_flush)
+    if (flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t)) pending = next_flush;
+  // A CTA owns the last step of at most one shared tile (only the first tile of its range
+  // can have started in an earlier CTA and end here; later shared tiles end further on).
+  if (pending >= 0) reduce_tile(p, pending, w, G, lane);
   PE_STAMP(6);
 }
 
 // ---- host side -----------------------------------------------------------------
 
-static int pick_cap(int batch) { return batch <= 8 ? 32 : 16; }
+static int pick_cap(int batch) { return batch <= 8 ? 32 : 16; }  // activation slots resident per phase (<= 80 KB)
 
 // Scratch layout: [tile counters, fixed 256 KB][fp32 partials].  The counter region has
 // the same size for every shape so that partials of one call can never land where a
 // later call of another shape keeps its counters (counters must read zero on entry and
 // are returned to zero; partials need no initial value).
 constexpr size_t kCounterBytes = 262144;
-constexpr int kMaxRowTiles = (int)(kCounterBytes / sizeof(unsigned));
+constexpr int kMaxRowTiles = (int)(kCounterBytes / sizeof(unsigned)) - 1;  // last word: status (0 = ok)
 
 struct Plan {
   int n_rt16, n_rt256, nb, G, cap, max_slots;
   long long S;
   size_t part_bytes, cnt_bytes;
-  unsigned dyn_bytes;
+  unsigned fixed_bytes;  // shared memory besides the code ring
 };
 
 static Plan make_plan(int batch, int N, int K, int sms) {
@@ -663,8 +776,8 @@ static Plan make_plan(int batch, int N, int K, int sms) {
   if (pl.max_slots > pl.G) pl.max_slots = pl.G;
   pl.part_bytes = (size_t)pl.n_rt16 * pl.max_slots * 16 * batch * sizeof(float);
   pl.cnt_bytes = kCounterBytes;
-  const unsigned slot_bytes = ((batch + 7) & ~7) * kXRowBytes;
-  pl.dyn_bytes = kLutSpan /*worst-case alignment pad*/ + kLutSpan + pl.cap * slot_bytes + kRowsPerCta * (pl.cap + 2) * 2 + 64;
+  const unsigned slot_bytes = batch * kXRowBytes;
+  pl.fixed_bytes = kLutBytes + pl.cap * slot_bytes + ((kRowsPerCta * (pl.cap + 2) * 2 + 15) & ~15) + 64;
   return pl;
 }
 
@@ -692,9 +805,12 @@ extern "C" size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded)
   return best;
 }
 
-template <bool PACKED, int NB, int DEPTH>
-static int launch(const GemvArgs& a, int G, cudaStream_t st) {
-  auto kfn = gemv_kernel<PACKED, NB, DEPTH>;
+template <bool PACKED, int NB, int DEPTH, bool REGTAB>
+static int launch(GemvArgs a, const Plan& pl, cudaStream_t st) {
+  const int G = pl.G;
+  a.dyn_bytes = pl.fixed_bytes + kWarps * DEPTH * (PACKED ? 1024 : 2048);
+  if (a.dyn_bytes > 231424u) return PE_ERR_LIMIT;
+  auto kfn = gemv_kernel<PACKED, NB, DEPTH, REGTAB>;
   static thread_local unsigned configured[16] = {0};
   int dev = 0;
   PE_CUDA_TRY(cudaGetDevice(&dev));
@@ -750,12 +866,24 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
   a.batch = batch; a.N = out_f; a.K = in_f_padded; a.nb = pl.nb;
   a.n_rt16 = pl.n_rt16; a.n_rt256 = pl.n_rt256; a.S = (int)pl.S; a.cap = pl.cap; a.max_slots = pl.max_slots;
   a.ws_cnt = static_cast<unsigned*>(workspace);
+  a.ws_status = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kCounterBytes - 4);
   a.ws_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.cnt_bytes);
-  a.dyn_bytes = pl.dyn_bytes;
+  // the deepest code ring that fits beside table, activation slots and norms
+  const unsigned room = 231000u - pl.fixed_bytes;
+  const bool deep = room >= (unsigned)kWarps * kRingPerWarp;
   a.prof = g_prof;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (packed) return batch <= 8 ? launch<true, 8, 4>(a, pl.G, st) : launch<true, 16, 3>(a, pl.G, st);
-  return batch <= 8 ? launch<false, 8, 3>(a, pl.G, st) : launch<false, 16, 2>(a, pl.G, st);
+  // DEPTH = ring stages per warp (1 KB nibble / 2 KB byte stages): 8 KB per warp when it fits, else 6 / 4 KB
+  if (packed && n_levels <= 8) {  // 2- and 3-bit layers: centroid table in registers
+    if (batch <= 8) return deep ? launch<true, 8, 8, true>(a, pl, st) : launch<true, 8, 6, true>(a, pl, st);
+    return launch<true, 16, 6, true>(a, pl, st);
+  }
+  if (packed) {
+    if (batch <= 8) return deep ? launch<true, 8, 8, false>(a, pl, st) : launch<true, 8, 6, false>(a, pl, st);
+    return launch<true, 16, 6, false>(a, pl, st);
+  }
+  if (batch <= 8) return deep ? launch<false, 8, 4, false>(a, pl, st) : launch<false, 8, 2, false>(a, pl, st);
+  return launch<false, 16, 2, false>(a, pl, st);
 }
 
 // ---- entry point for callers that cannot allocate device memory -------------------
