@@ -112,6 +112,22 @@ int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, 
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
             int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- tiled weight layout for the decode kernel -----------------------------------
+ * pe_retile rewrites a layer (codes + norms, the reference's row-major layouts) into the
+ * layout the decode kernel streams best: for every 16-row tile and every 128-block, the
+ * 16 x 64 B (nibble) or 16 x 128 B (byte) codes followed by the 16 fp16 block norms, tiles
+ * of a row tile stored one after the other.  A warp then reads one contiguous region
+ * with 512-byte requests instead of sixteen 64-byte row pieces, and the norms travel with
+ * the codes.  pe_retile_bytes gives the size of the tiled buffer (rows padded to 16).
+ * Done once after loading, next to pack_codes_int4 (linear_method.py:228-258); it has no
+ * counterpart in the reference.  pe_gemv_tiled = pe_gemv on such a buffer. */
+size_t pe_retile_bytes(int packed, int64_t out_f, int64_t in_f_padded);
+int pe_retile(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms, void* tiles,
+              int64_t out_f, int64_t in_f_padded, void* stream);
+int pe_gemv_tiled(const void* tiles, int packed, const float* ct_scaled, int n_levels, const void* x, int x_kind,
+                  int x_dtype, int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch,
+                  int out_f, int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- prefill-size matmul (any number of rows; meant for m > 16) -------------------
  * Same result as pe_gemv with the arguments in the same order; the contraction runs on
  * tcgen05 tensor cores in bf16 with fp32 accumulation (activations and dequantised

@@ -33,6 +33,9 @@ SIGNATURES = {
     "pe_gemv_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                      _vp, _sz, _vp]),
+    "pe_retile_bytes": (_sz, [_i, _i64, _i64]),
+    "pe_retile": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i64, _i64, _vp]),
+    "pe_gemv_tiled": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "pe_gemm_workspace_bytes": (_sz, [_i, _i]),
     "pe_gemm": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                      _vp, _sz, _vp]),

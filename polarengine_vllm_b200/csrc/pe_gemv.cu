@@ -44,8 +44,9 @@ constexpr int kLutBytes = 32768;          // 256 entries x 32 lanes x 4 B (entry
 constexpr int kRingPerWarp = 8192;        // bytes of code stream each warp keeps in flight
 
 struct GemvArgs {
-  const uint8_t* codes; int64_t ld_codes;
+  const uint8_t* codes; int64_t ld_codes;   // row-major layout (the reference's)
   const __half* norms; int64_t ld_norms;
+  const uint8_t* tiles;                     // tiled layout (pe_retile), used when TILED
   const float* ct; int n_levels;
   const void* x; int x_kind; int x_dtype; int64_t ld_x; int in_f;
   void* y; int y_dtype; int64_t ld_y;
@@ -104,12 +105,31 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
+// Tiled layout (pe_retile): the codes of one step -- 16 rows x one 128-block -- are 1 KB
+// (2 KB for byte codes) of contiguous memory followed by the 16 fp16 block norms, and the
+// steps of a row tile follow each other, so a warp streams one contiguous region.
+template <bool PACKED> struct TileGeom {
+  static constexpr int kCodeBytes = PACKED ? 1024 : 2048;
+  static constexpr int kTileBytes = kCodeBytes + 32;            // + 16 norms
+  static constexpr int kStageBytes = (kTileBytes + 63) & ~63;   // ring stage stride
+};
+
 // Request one step's codes (rows g and g+8 of a 16-row tile, one 128-block) into this
-// lane's slots of a ring stage: 16-byte asynchronous copies, no registers held while the
-// data is in flight.  Stage layout: [piece 0..(1|3)][lane] x 16 B, so a warp reads it back
-// with conflict-free 128-bit loads.
-template <bool PACKED>
+// warp's ring stage: 16-byte asynchronous copies, no registers held while the data is in
+// flight.  Row-major source: stage layout [piece 0..(1|3)][lane] x 16 B (lane (g,t) copies
+// its own 16-byte pieces of rows g and g+8).  Tiled source: the stage is a copy of the tile.
+template <bool PACKED, bool TILED>
 __device__ __forceinline__ void fetch(uint32_t stage, const GemvArgs& p, int rt256, int b, int w, int g, int t, int lane) {
+  if (TILED) {
+    int rt16 = rt256 * 16 + w;
+    rt16 = rt16 < p.n_rt16 ? rt16 : p.n_rt16 - 1;
+    const uint8_t* src = p.tiles + ((int64_t)rt16 * p.nb + b) * TileGeom<PACKED>::kTileBytes + lane * 16;
+    const uint32_t dst = stage + lane * 16;
+#pragma unroll
+    for (int i = 0; i < TileGeom<PACKED>::kCodeBytes / 512; ++i) cp_async16(dst + 512 * i, src + 512 * i);
+    if (lane < 2) cp_async16(dst + TileGeom<PACKED>::kCodeBytes, src + TileGeom<PACKED>::kCodeBytes);  // norms
+    return;
+  }
   int rowA = rt256 * kRowsPerCta + w * 16 + g;
   int rowB = rowA + 8;
   rowA = rowA < p.N ? rowA : p.N - 1;
@@ -128,9 +148,16 @@ __device__ __forceinline__ void fetch(uint32_t stage, const GemvArgs& p, int rt2
   }
 }
 
-template <bool PACKED>
-__device__ __forceinline__ void read_stage(CodeRegs<PACKED>& r, const uint8_t* stage, int lane) {
-  const uint4* s4 = reinterpret_cast<const uint4*>(stage) + lane;
+template <bool PACKED, bool TILED>
+__device__ __forceinline__ void read_stage(CodeRegs<PACKED>& r, const uint8_t* stage, int lane, int g, int t) {
+  if (TILED && !PACKED) {  // rows of 128 B: lane (g,t) owns bytes [32 t, 32 t + 32) of rows g and g+8
+    const uint4* ra = reinterpret_cast<const uint4*>(stage + g * 128 + t * 32);
+    const uint4* rb = reinterpret_cast<const uint4*>(stage + (g + 8) * 128 + t * 32);
+    r.a0 = ra[0]; r.a1 = ra[1];
+    r.b0 = rb[0]; r.b1 = rb[1];
+    return;
+  }
+  const uint4* s4 = reinterpret_cast<const uint4*>(stage) + lane;  // tiled nibble rows are 64 B: same addresses
   r.a0 = s4[0];
   r.b0 = s4[32];
   if (!PACKED) { r.a1 = s4[64]; r.b1 = s4[96]; }
@@ -298,6 +325,116 @@ __device__ __forceinline__ void step_math(float acc[NB / 2], const CodeRegs<PACK
     acc[5] = fmaf(nA, d0[5] + d1[5], acc[5]);
     acc[6] = fmaf(nB, d0[6] + d1[6], acc[6]);
     acc[7] = fmaf(nB, d0[7] + d1[7], acc[7]);
+  }
+}
+
+// ---- one or two activation rows: no tensor cores --------------------------------
+// With a single activation row seven eighths of every m16n8k16 MMA is padding, and the
+// legacy mma.sync path retires only one such MMA per 8 cycles per scheduler: at eight
+// MMAs per step it, not memory, bounds the stream.  For batch <= 2 the products go through
+// the fp16x2 FMA pipe instead: a lane keeps the dot products of ITS 32 (64) weights of rows
+// g and g+8 against its own slice of the activations -- two fp16x2 chains of 8 per row and
+// block, widened to fp32 and scaled by the block norm -- and the four lanes of a row are
+// summed once per tile, at hand-off time.
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ float h2sum(uint32_t h) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+  return f.x + f.y;
+}
+
+// A registers (fp16 pairs in activation order) of chunk j (16 bytes of activations) for rows g (a) and g+8 (b)
+template <bool PACKED, bool REGTAB>
+__device__ __forceinline__ void decode_chunk(const CodeRegs<PACKED>& r, int j, uint32_t lane_base, const RegTable& tb,
+                                             uint32_t a[4], uint32_t b[4]) {
+  if (PACKED) {
+    const uint32_t wa = j == 0 ? r.a0.x : (j == 1 ? r.a0.y : (j == 2 ? r.a0.z : r.a0.w));
+    const uint32_t wb = j == 0 ? r.b0.x : (j == 1 ? r.b0.y : (j == 2 ? r.b0.z : r.b0.w));
+    if (REGTAB) {
+      reg_decode(wa, tb, a);
+      reg_decode(wb, tb, b);
+    } else {
+      const uint32_t ad[8] = {lut_addr<0>(wa, lane_base), lut_addr<1>(wa, lane_base), lut_addr<2>(wa, lane_base),
+                              lut_addr<3>(wa, lane_base), lut_addr<0>(wb, lane_base), lut_addr<1>(wb, lane_base),
+                              lut_addr<2>(wb, lane_base), lut_addr<3>(wb, lane_base)};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { a[k] = lut_ld(ad[k]); b[k] = lut_ld(ad[4 + k]); }
+    }
+  } else {
+    const uint4 qa = j < 2 ? r.a0 : r.a1, qb = j < 2 ? r.b0 : r.b1;
+    const uint32_t wa0 = (j & 1) ? qa.z : qa.x, wa1 = (j & 1) ? qa.w : qa.y;
+    const uint32_t wb0 = (j & 1) ? qb.z : qb.x, wb1 = (j & 1) ? qb.w : qb.y;
+    uint32_t ad[16], v[16];
+    ad[0] = lut_addr<0>(wa0, lane_base); ad[1] = lut_addr<1>(wa0, lane_base);
+    ad[2] = lut_addr<2>(wa0, lane_base); ad[3] = lut_addr<3>(wa0, lane_base);
+    ad[4] = lut_addr<0>(wa1, lane_base); ad[5] = lut_addr<1>(wa1, lane_base);
+    ad[6] = lut_addr<2>(wa1, lane_base); ad[7] = lut_addr<3>(wa1, lane_base);
+    ad[8] = lut_addr<0>(wb0, lane_base); ad[9] = lut_addr<1>(wb0, lane_base);
+    ad[10] = lut_addr<2>(wb0, lane_base); ad[11] = lut_addr<3>(wb0, lane_base);
+    ad[12] = lut_addr<0>(wb1, lane_base); ad[13] = lut_addr<1>(wb1, lane_base);
+    ad[14] = lut_addr<2>(wb1, lane_base); ad[15] = lut_addr<3>(wb1, lane_base);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v[k] = lut_ld(ad[k]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { a[k] = lo_hi(v[2 * k], v[2 * k + 1]); b[k] = lo_hi(v[8 + 2 * k], v[9 + 2 * k]); }
+  }
+}
+
+// acc[0] row g batch 0, acc[1] row g batch 1, acc[2] row g+8 batch 0, acc[3] row g+8 batch 1: per-lane partials
+template <bool PACKED, bool REGTAB>
+__device__ __forceinline__ void step_fma(float acc[4], const CodeRegs<PACKED>& r, uint32_t lane_base, const RegTable& tb,
+                                         const uint8_t* xslot, float nA, float nB, int t, int batch) {
+  uint4 x0[4], x1[4];
+  const uint8_t* xrow = xslot + t * 16;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    x0[j] = *reinterpret_cast<const uint4*>(xrow + j * 64);
+    x1[j] = make_uint4(0, 0, 0, 0);
+  }
+  if (batch > 1) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x1[j] = *reinterpret_cast<const uint4*>(xrow + kXRowBytes + j * 64);
+  }
+  uint32_t cA0[2] = {0, 0}, cB0[2] = {0, 0}, cA1[2] = {0, 0}, cB1[2] = {0, 0};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t a[4], b[4];
+    decode_chunk<PACKED, REGTAB>(r, j, lane_base, tb, a, b);
+    const uint32_t xx[4] = {x0[j].x, x0[j].y, x0[j].z, x0[j].w};
+    const uint32_t yy[4] = {x1[j].x, x1[j].y, x1[j].z, x1[j].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      cA0[j & 1] = hfma2_u(a[k], xx[k], cA0[j & 1]);
+      cB0[j & 1] = hfma2_u(b[k], xx[k], cB0[j & 1]);
+    }
+    if (batch > 1) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        cA1[j & 1] = hfma2_u(a[k], yy[k], cA1[j & 1]);
+        cB1[j & 1] = hfma2_u(b[k], yy[k], cB1[j & 1]);
+      }
+    }
+  }
+  acc[0] = fmaf(nA, h2sum(cA0[0]) + h2sum(cA0[1]), acc[0]);
+  acc[2] = fmaf(nB, h2sum(cB0[0]) + h2sum(cB0[1]), acc[2]);
+  if (batch > 1) {
+    acc[1] = fmaf(nA, h2sum(cA1[0]) + h2sum(cA1[1]), acc[1]);
+    acc[3] = fmaf(nB, h2sum(cB1[0]) + h2sum(cB1[1]), acc[3]);
+  }
+}
+
+// sum the four lanes (t = 0..3) that share a weight row; afterwards every lane holds the
+// totals in the accumulator layout the hand-off expects from lanes with t == 0
+__device__ __forceinline__ void quad_reduce(const float in[4], float out[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float v = in[i];
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    out[i] = v;
   }
 }
 
@@ -505,7 +642,7 @@ __device__ __noinline__ void stage_norms(const GemvArgs& p, __half* ns, int nstr
   }
 }
 
-template <bool PACKED, int NB, int DEPTH, bool REGTAB>
+template <bool PACKED, int NB, int DEPTH, bool REGTAB, bool FMA, bool TILED>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int slot_rt[32], slot_blk[32];
@@ -548,7 +685,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   for (int u = 0; u < NU; ++u) {
     const int grow = my_rt * kRowsPerCta + w + u * kWarps;
     nv[u] = 0;
-    if (lane < cnt0 && grow < p.N)
+    if (!TILED && lane < cnt0 && grow < p.N)
       asm volatile("ld.global.nc.u16 %0, [%1];"
                    : "=h"(nv[u])
                    : "l"(reinterpret_cast<const unsigned short*>(p.norms) + (int64_t)grow * p.ld_norms + my_blk));
@@ -574,10 +711,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   uint8_t* xs = lut_g + kLutBytes;
   const int nstr = p.cap + 2;
   __half* ns = reinterpret_cast<__half*>(xs + (size_t)p.cap * slot_bytes);
-  constexpr int kStage = PACKED ? 1024 : 2048;      // bytes of one step's codes per warp
+  constexpr int kCodeBytes = PACKED ? 1024 : 2048;  // bytes of one step's codes per warp
+  constexpr int kStage = TILED ? TileGeom<PACKED>::kStageBytes : kCodeBytes;
   constexpr int kDepth = DEPTH;                     // ring stages per warp
-  uint8_t* ring_g = reinterpret_cast<uint8_t*>(ns) + ((kRowsPerCta * nstr * 2 + 15) & ~15) + w * (kDepth * kStage);
+  uint8_t* ring_g = reinterpret_cast<uint8_t*>(ns) + (TILED ? 0 : ((kRowsPerCta * nstr * 2 + 15) & ~15)) + w * (kDepth * kStage);
   const uint32_t ring_s = smem_u32(ring_g);
+  int i_f = 0;  // steps requested so far
   // the code stream goes last: it is the bulk, and whatever is requested after it
   // would queue behind megabytes of it in the memory system.  The ring is filled and
   // refilled kBatch steps at a time: consecutive steps of a warp are consecutive 64-byte
@@ -587,9 +726,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
 #pragma unroll
   for (int d = 0; d < kDepth; ++d) {
     if (q_f < q_hi) {
-      fetch<PACKED>(ring_s + (q_f % kDepth) * kStage, p, rt_f, b_f, w, g, t, lane);
+      fetch<PACKED, TILED>(ring_s + (i_f % kDepth) * kStage, p, rt_f, b_f, w, g, t, lane);
       if (++b_f == p.nb) { b_f = 0; ++rt_f; }
       ++q_f;
+      ++i_f;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
@@ -626,7 +766,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
     }
   }
   PE_STAMP(1);
-  if (lane < cnt0) {
+  if (!TILED && lane < cnt0) {
 #pragma unroll
     for (int u = 0; u < NU; ++u) reinterpret_cast<unsigned short*>(ns)[(w + u * kWarps) * nstr + lane] = nv[u];
   }
@@ -672,7 +812,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
         slot_blk[tid] = qq - r * p.nb;
       }
       __syncthreads();
-      stage_norms(p, ns, nstr, slot_rt, slot_blk, cnt, tid);
+      if (!TILED) stage_norms(p, ns, nstr, slot_rt, slot_blk, cnt, tid);
       stage_x<PACKED>(p, xs, slot_blk, cnt, w, lane);
     }
     __syncthreads();
@@ -693,11 +833,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
             default: asm volatile("cp.async.wait_group %0;" ::"n"(kDepth > 4 ? kDepth - 4 : 0) : "memory"); break;
           }
           CodeRegs<PACKED> cur;
-          read_stage<PACKED>(cur, ring_g + (q % kDepth) * kStage, lane);
+          const uint8_t* stage_g = ring_g + (i_step % kDepth) * kStage;
+          read_stage<PACKED, TILED>(cur, stage_g, lane, g, t);
+          float nA, nB;
+          if (TILED) {  // the norms travelled with the codes
+            nA = __half2float(*reinterpret_cast<const __half*>(stage_g + kCodeBytes + 2 * g));
+            nB = __half2float(*reinterpret_cast<const __half*>(stage_g + kCodeBytes + 2 * g + 16));
+          }
           const int slot = q - ph;
-          const float nA = __half2float(ns[(w * 16 + g) * nstr + slot]);
-          const float nB = __half2float(ns[(w * 16 + g + 8) * nstr + slot]);
-          step_math<PACKED, NB, REGTAB>(acc, cur, lane_base, tb, xs + slot * slot_bytes, nA, nB, g, t, p.batch);
+          if (!TILED) {
+            nA = __half2float(ns[(w * 16 + g) * nstr + slot]);
+            nB = __half2float(ns[(w * 16 + g + 8) * nstr + slot]);
+          }
+#ifdef PE_NO_MATH  // developer experiment: stream the codes, skip the arithmetic
+          acc[0] += __uint_as_float(cur.a0.x ^ cur.b0.w) * nA * nB;
+#else
+          if (FMA) step_fma<PACKED, REGTAB>(acc, cur, lane_base, tb, xs + slot * slot_bytes, nA, nB, t, p.batch);
+          else step_math<PACKED, NB, REGTAB>(acc, cur, lane_base, tb, xs + slot * slot_bytes, nA, nB, g, t, p.batch);
+#endif
           ++run;
           ++q;
           if (i_step % kBatch == kBatch - 1) {
@@ -705,9 +858,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
 #pragma unroll
             for (int d = 0; d < kBatch; ++d) {
               if (q_f < q_hi) {
-                fetch<PACKED>(ring_s + (q_f % kDepth) * kStage, p, rt_f, b_f, w, g, t, lane);
+                fetch<PACKED, TILED>(ring_s + (i_f % kDepth) * kStage, p, rt_f, b_f, w, g, t, lane);
                 if (++b_f == p.nb) { b_f = 0; ++rt_f; }
                 ++q_f;
+                ++i_f;
               }
               asm volatile("cp.async.commit_group;" ::: "memory");
             }
@@ -715,7 +869,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
           if (++b_c == p.nb) {  // row tile finished on our side
             for (; next_flush < rt_c; ++next_flush)
               if (flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t)) pending = next_flush;
-            if (flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t)) pending = rt_c;
+            if (FMA) {
+              float red[NB / 2];
+              quad_reduce(acc, red);
+              if (flush<NB>(p, red, rt_c, w, G, cta, lane, g, t)) pending = rt_c;
+            } else if (flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t)) {
+              pending = rt_c;
+            }
             next_flush = rt_c + 1;
 #pragma unroll
             for (int i = 0; i < NB / 2; ++i) acc[i] = 0.f;
@@ -732,7 +892,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   if (run > 0) {
     for (; next_flush < rt_c; ++next_flush)
       if (flush<NB>(p, zeros, next_flush, w, G, cta, lane, g, t)) pending = next_flush;
-    if (flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t)) pending = rt_c;
+    if (FMA) {
+      float red[NB / 2];
+      quad_reduce(acc, red);
+      if (flush<NB>(p, red, rt_c, w, G, cta, lane, g, t)) pending = rt_c;
+    } else if (flush<NB>(p, acc, rt_c, w, G, cta, lane, g, t)) {
+      pending = rt_c;
+    }
     next_flush = rt_c + 1;
   }
   for (; next_flush <= last_tile; ++next_flush)
@@ -758,7 +924,8 @@ struct Plan {
   int n_rt16, n_rt256, nb, G, cap, max_slots;
   long long S;
   size_t part_bytes, cnt_bytes;
-  unsigned fixed_bytes;  // shared memory besides the code ring
+  unsigned fixed_bytes;        // shared memory besides the code ring
+  unsigned fixed_bytes_tiled;  // same without the norm staging area
 };
 
 static Plan make_plan(int batch, int N, int K, int sms) {
@@ -778,6 +945,7 @@ static Plan make_plan(int batch, int N, int K, int sms) {
   pl.cnt_bytes = kCounterBytes;
   const unsigned slot_bytes = batch * kXRowBytes;
   pl.fixed_bytes = kLutBytes + pl.cap * slot_bytes + ((kRowsPerCta * (pl.cap + 2) * 2 + 15) & ~15) + 64;
+  pl.fixed_bytes_tiled = kLutBytes + pl.cap * slot_bytes + 64;
   return pl;
 }
 
@@ -805,12 +973,13 @@ extern "C" size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded)
   return best;
 }
 
-template <bool PACKED, int NB, int DEPTH, bool REGTAB>
-static int launch(GemvArgs a, const Plan& pl, cudaStream_t st) {
+template <bool PACKED, int NB, int DEPTH, bool REGTAB, bool FMA, bool TILED>
+static int launch_t(GemvArgs a, const Plan& pl, cudaStream_t st) {
   const int G = pl.G;
-  a.dyn_bytes = pl.fixed_bytes + kWarps * DEPTH * (PACKED ? 1024 : 2048);
-  if (a.dyn_bytes > 231424u) return PE_ERR_LIMIT;
-  auto kfn = gemv_kernel<PACKED, NB, DEPTH, REGTAB>;
+  a.dyn_bytes = (TILED ? pl.fixed_bytes_tiled : pl.fixed_bytes) +
+                kWarps * DEPTH * (TILED ? TileGeom<PACKED>::kStageBytes : (PACKED ? 1024 : 2048));
+  if (a.dyn_bytes > 231424u) return PE_ERR_LIMIT;  // 227 KB minus the 1 KB of static shared memory
+  auto kfn = gemv_kernel<PACKED, NB, DEPTH, REGTAB, FMA, TILED>;
   static thread_local unsigned configured[16] = {0};
   int dev = 0;
   PE_CUDA_TRY(cudaGetDevice(&dev));
@@ -834,18 +1003,30 @@ static int launch(GemvArgs a, const Plan& pl, cudaStream_t st) {
   return PE_OK;
 }
 
-extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
-                       const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
-                       int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
-                       int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!codes || !norms || !ct_scaled || !x || !y || !workspace) return PE_ERR_ARG;
+template <bool PACKED, int NB, int DEPTH, bool REGTAB, bool FMA = false>
+static int launch(const GemvArgs& a, const Plan& pl, cudaStream_t st) {
+  return a.tiles ? launch_t<PACKED, NB, DEPTH, REGTAB, FMA, true>(a, pl, st)
+                 : launch_t<PACKED, NB, DEPTH, REGTAB, FMA, false>(a, pl, st);
+}
+
+// Shared by pe_gemv (row-major codes + norms) and pe_gemv_tiled (tiles != nullptr).
+static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                    const void* tiles, const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype,
+                    int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+                    int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!ct_scaled || !x || !y || !workspace) return PE_ERR_ARG;
+  if (!tiles && (!codes || !norms)) return PE_ERR_ARG;
   if (batch < 1 || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
   if (x_kind != PE_X_ROTATED && x_kind != PE_X_RAW) return PE_ERR_ARG;
   if (x_dtype < PE_F32 || x_dtype > PE_BF16 || y_dtype < PE_F32 || y_dtype > PE_BF16) return PE_ERR_ARG;
   if (n_levels < 2 || n_levels > 256 || (packed && n_levels > 16)) return PE_ERR_ARG;
   if (batch > 16 || in_f_padded % kBlock) return PE_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15)) return PE_ERR_ALIGN;
-  if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  if (tiles) {
+    if (reinterpret_cast<uintptr_t>(tiles) & 15) return PE_ERR_ALIGN;
+  } else {
+    if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15)) return PE_ERR_ALIGN;
+    if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  }
   if (ld_x < (x_kind == PE_X_RAW ? in_f : in_f_padded) || ld_y < out_f) return PE_ERR_ARG;
 
   const int sms = sm_count();
@@ -859,6 +1040,7 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
   GemvArgs a;
   a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
   a.norms = static_cast<const __half*>(norms); a.ld_norms = ld_norms;
+  a.tiles = static_cast<const uint8_t*>(tiles);
   a.ct = ct_scaled; a.n_levels = n_levels;
   a.x = x; a.x_kind = x_kind; a.x_dtype = x_dtype; a.ld_x = ld_x; a.in_f = in_f;
   a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
@@ -869,11 +1051,16 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
   a.ws_status = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kCounterBytes - 4);
   a.ws_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.cnt_bytes);
   // the deepest code ring that fits beside table, activation slots and norms
-  const unsigned room = 231000u - pl.fixed_bytes;
-  const bool deep = room >= (unsigned)kWarps * kRingPerWarp;
+  const unsigned ring_need = kWarps * 8u * (tiles ? (unsigned)TileGeom<true>::kStageBytes : 1024u);
+  const bool deep = (tiles ? pl.fixed_bytes_tiled : pl.fixed_bytes) + ring_need <= 231424u;
   a.prof = g_prof;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // DEPTH = ring stages per warp (1 KB nibble / 2 KB byte stages): 8 KB per warp when it fits, else 6 / 4 KB
+  if (batch <= 2) {  // one or two activation rows: fp16x2 FMA path, no tensor cores (always fits the deep ring)
+    if (packed && n_levels <= 8) return launch<true, 8, 8, true, true>(a, pl, st);
+    if (packed) return launch<true, 8, 8, false, true>(a, pl, st);
+    return launch<false, 8, 4, false, true>(a, pl, st);
+  }
   if (packed && n_levels <= 8) {  // 2- and 3-bit layers: centroid table in registers
     if (batch <= 8) return deep ? launch<true, 8, 8, true>(a, pl, st) : launch<true, 8, 6, true>(a, pl, st);
     return launch<true, 16, 6, true>(a, pl, st);
@@ -884,6 +1071,82 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
   }
   if (batch <= 8) return deep ? launch<false, 8, 4, false>(a, pl, st) : launch<false, 8, 2, false>(a, pl, st);
   return launch<false, 16, 2, false>(a, pl, st);
+}
+
+extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                       const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
+                       int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+                       int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
+  return gemv_run(codes, packed, ld_codes, norms, ld_norms, nullptr, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
+                  y_dtype, ld_y, bias, batch, out_f, in_f_padded, workspace, workspace_bytes, stream);
+}
+
+// ---- tiled weight layout ---------------------------------------------------------
+namespace pe {
+// one thread per 16-byte piece of the output
+template <bool PACKED>
+__global__ void __launch_bounds__(256) retile_kernel(const uint8_t* codes, int64_t ld_codes, const __half* norms,
+                                                     int64_t ld_norms, uint8_t* out, int N, int nb, int64_t n_pieces) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pieces) return;
+  constexpr int kPieces = TileGeom<PACKED>::kTileBytes / 16;   // 66 or 130
+  constexpr int kRowBytes = PACKED ? 64 : 128;
+  const int64_t tile = i / kPieces;
+  const int piece = (int)(i - tile * kPieces);
+  const int rt16 = (int)(tile / nb), b = (int)(tile - (int64_t)rt16 * nb);
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (piece < TileGeom<PACKED>::kCodeBytes / 16) {
+    const int r = piece / (kRowBytes / 16), c = piece % (kRowBytes / 16);
+    const int row = rt16 * 16 + r;
+    if (row < N) v = *reinterpret_cast<const uint4*>(codes + (int64_t)row * ld_codes + b * kRowBytes + c * 16);
+  } else {  // norms: rows 0..7 in the first piece, 8..15 in the second
+    const int r0 = (piece - TileGeom<PACKED>::kCodeBytes / 16) * 8;
+    unsigned short h[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int row = rt16 * 16 + r0 + k;
+      h[k] = row < N ? __half_as_ushort(norms[(int64_t)row * ld_norms + b]) : (unsigned short)0;
+    }
+    v = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+  }
+  *reinterpret_cast<uint4*>(out + i * 16) = v;
+}
+}  // namespace pe
+
+extern "C" size_t pe_retile_bytes(int packed, int64_t out_f, int64_t in_f_padded) {
+  if (out_f < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
+  const size_t tile = packed ? TileGeom<true>::kTileBytes : TileGeom<false>::kTileBytes;
+  return (size_t)((out_f + 15) / 16) * (size_t)(in_f_padded / kBlock) * tile;
+}
+
+extern "C" int pe_retile(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms, void* tiles,
+                         int64_t out_f, int64_t in_f_padded, void* stream) {
+  if (!codes || !norms || !tiles || out_f < 1 || out_f > 0x7fffffff) return PE_ERR_ARG;
+  if (in_f_padded < kBlock || in_f_padded % kBlock) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15) || (reinterpret_cast<uintptr_t>(tiles) & 15)) return PE_ERR_ALIGN;
+  const int nb = (int)(in_f_padded / kBlock);
+  const int64_t n_pieces = (int64_t)pe_retile_bytes(packed, out_f, in_f_padded) / 16;
+  const int64_t blocks = (n_pieces + 255) / 256;
+  if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (packed)
+    retile_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint8_t*>(codes), ld_codes,
+                                                         static_cast<const __half*>(norms), ld_norms,
+                                                         static_cast<uint8_t*>(tiles), (int)out_f, nb, n_pieces);
+  else
+    retile_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint8_t*>(codes), ld_codes,
+                                                          static_cast<const __half*>(norms), ld_norms,
+                                                          static_cast<uint8_t*>(tiles), (int)out_f, nb, n_pieces);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
+
+extern "C" int pe_gemv_tiled(const void* tiles, int packed, const float* ct_scaled, int n_levels, const void* x, int x_kind,
+                             int x_dtype, int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias,
+                             int batch, int out_f, int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!tiles) return PE_ERR_ARG;
+  return gemv_run(nullptr, packed, 0, nullptr, 0, tiles, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y, y_dtype, ld_y,
+                  bias, batch, out_f, in_f_padded, workspace, workspace_bytes, stream);
 }
 
 // ---- entry point for callers that cannot allocate device memory -------------------

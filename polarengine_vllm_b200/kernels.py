@@ -22,11 +22,28 @@ def pack_codes_int4(codes: torch.Tensor, block_size: int = 128) -> torch.Tensor:
     return pack_codes_half_block(codes, block_size)
 
 
+def retile(codes: torch.Tensor, packed: bool, norms: torch.Tensor) -> torch.Tensor:
+    """Layer in the decode kernel's tiled layout (``pe_retile``): a flat uint8 buffer."""
+    dev = nv.require_cuda(codes, norms)
+    out_f = codes.shape[0]
+    kp = norms.shape[-1] * 128
+    if norms.dtype != torch.float16 or norms.stride(-1) != 1:
+        norms = norms.to(torch.float16).contiguous()
+    if codes.stride(-1) != 1:
+        codes = codes.contiguous()
+    l = nv.lib()
+    out = torch.empty(l.pe_retile_bytes(int(packed), out_f, kp), dtype=torch.uint8, device=dev)
+    nv.check(l.pe_retile(codes.data_ptr(), int(packed), codes.stride(0) * codes.element_size(), norms.data_ptr(),
+                         norms.stride(0), out.data_ptr(), out_f, kp, nv.stream_ptr(dev)), "pe_retile")
+    return out
+
+
 def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scaled: torch.Tensor, x: torch.Tensor,
                  rotated: bool, out_f: int, in_f: int, in_f_padded: int, out_dtype: torch.dtype = torch.float32,
-                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 bias: Optional[torch.Tensor] = None, tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y (batch, out_f) for x (batch, in_f or in_f_padded); the single entry to the
-    native kernels used by everything else in the package."""
+    native kernels used by everything else in the package.  ``tiles`` (from
+    :func:`retile`) lets batches of up to 16 rows stream the tiled copy of the layer."""
     dev = nv.require_cuda(codes, norms, ct_scaled, x)
     nv.ensure_init(dev)
     if x.dim() != 2 or x.stride(1) != 1:
@@ -53,6 +70,13 @@ def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scal
         for m0 in range(0, batch, GEMV_MAX_BATCH):
             m1 = min(batch, m0 + GEMV_MAX_BATCH)
             xs, ys = x[m0:m1], y[m0:m1]
+            if tiles is not None:
+                nv.check(l.pe_gemv_tiled(tiles.data_ptr(), int(packed), ct.data_ptr(), ct.numel(), xs.data_ptr(),
+                                         nv.PE_X_ROTATED if rotated else nv.PE_X_RAW, nv.dtype_code(xs), xs.stride(0),
+                                         in_f, ys.data_ptr(), nv.dtype_code(ys), ys.stride(0),
+                                         bias.data_ptr() if bias is not None else None, m1 - m0, out_f, in_f_padded,
+                                         ws.data_ptr(), ws.numel(), st), "pe_gemv_tiled")
+                continue
             nv.check(l.pe_gemv(codes.data_ptr(), int(packed), codes.stride(0) * codes.element_size(),
                                norms.data_ptr(), norms.stride(0), ct.data_ptr(), ct.numel(),
                                xs.data_ptr(), nv.PE_X_ROTATED if rotated else nv.PE_X_RAW, nv.dtype_code(xs),

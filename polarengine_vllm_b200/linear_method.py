@@ -23,7 +23,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from .fwht import FWHTCache
-from .kernels import pack_codes_int4, quant_matmul
+from .kernels import pack_codes_int4, quant_matmul, retile
 from .utils import get_ct_scaled
 
 try:  # vLLM is optional: the class must stay importable for offline tooling
@@ -45,6 +45,7 @@ class PolarQuantLinearMethod(_Base):
         self.block_size = block_size
         self.bits = bits
         self.layer_meta = layer_meta or {}
+        self.decode_tiled = True
         self._fwht_cache = FWHTCache()
 
     # ------------------------------------------------------------------ weights
@@ -87,6 +88,11 @@ class PolarQuantLinearMethod(_Base):
             layer.codes_packed = packed
             layer.in_f_half = layer.n_blocks * (layer.block_size // 2)
             layer.packed = True
+        if self.decode_tiled:
+            # second copy of the layer in the decode kernel's streaming layout (codes + norms
+            # interleaved per 16-row x 128-column tile); the row-major copy feeds the prefill kernel
+            w = layer.codes_packed if layer.packed else layer.codes
+            layer.codes_tiled = retile(w.data, layer.packed, layer.norms.data)
 
     # ------------------------------------------------------------------ forward
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -97,7 +103,7 @@ class PolarQuantLinearMethod(_Base):
         # one native entry for every batch size: <= 16 rows run the fused decode kernel,
         # more rows the tensor-core kernel (rotation is done by its preparation launch)
         y = quant_matmul(w, packed, layer.norms, layer.ct_scaled, x2, False, layer.out_f, layer.in_f,
-                         layer.in_f_padded, torch.float16, bias)
+                         layer.in_f_padded, torch.float16, bias, tiles=getattr(layer, "codes_tiled", None))
         return y.view(*lead, layer.out_f)
 
 

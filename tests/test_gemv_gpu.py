@@ -115,7 +115,7 @@ def test_polar_matmul_reference_signature():
     pk = kernels.pack_codes_int4(cd)
     y1 = kernels.polar_matmul(None, xd, nd, ctd, n, k, k // 128, 128, True, pk, k // 2)
     assert y0.shape == (n,) and y0.dtype == torch.float32
-    assert (y0 - y1).abs().max() <= 1e-4 * y0.abs().max()
+    assert (y0 - y1).abs().max() <= 2e-3 * y0.abs().max()  # batch 1 runs the fp16x2 path: two different code layouts, same values
     y2 = kernels.polar_gemv_packed(pk, xd, nd, ctd, n, k // 2, k // 128)
     assert torch.equal(y1, y2)
     yb = kernels.polar_matmul(cd, xd.reshape(1, -1), nd, ctd, n, k, k // 128)
@@ -146,3 +146,23 @@ def test_apply_matches_oracle_forward():
         # against the un-quantized weight the error is the quantizer's, not the kernel's
         dense = x.float().reshape(-1, in_f) @ w.T + bias.float()
         assert max_rel(y.reshape(-1, n), dense) < 0.25
+
+
+@pytest.mark.parametrize("batch", [1, 2, 3, 8, 16])
+@pytest.mark.parametrize("bits,n,k,in_f", [(3, 12288, 4096, 4096), (4, 4096, 12288, 12288), (5, 6144, 4096, 4096),
+                                           (6, 1000, 1920, 1856), (4, 130, 384, 300), (8, 144, 256, 200)])
+def test_gemv_tiled_layout_is_bit_identical(batch, bits, n, k, in_f):
+    """The tiled copy of a layer (pe_retile) gives the same bits as the row-major layout."""
+    from polarengine_vllm_b200 import kernels, packing
+    codes, norms, cts = rand_layer(n, k, bits, seed=7 * bits + n)
+    x = rand_x(batch, in_f, seed=batch + 1).cuda()
+    packed = bits <= 4
+    cd = codes.cuda()
+    w = packing.pack_codes_half_block(cd) if packed else cd
+    nd, ctd = norms.cuda(), cts.cuda()
+    tiles = kernels.retile(w, packed, nd)
+    y0 = kernels.quant_matmul(w, packed, nd, ctd, x, False, n, in_f, k, torch.float32)
+    y1 = kernels.quant_matmul(w, packed, nd, ctd, x, False, n, in_f, k, torch.float32, tiles=tiles)
+    assert torch.equal(y0, y1)
+    ref = oracle.linear_dequant(x.cpu(), codes, norms, cts, in_f=in_f)
+    assert max_rel(y1, ref) <= TOL
