@@ -54,6 +54,7 @@ def make_layer(dev, seed):
     distribution the quantizer produces for Gaussian weights), norms ~ 0.02*sqrt(128)."""
     from polarengine_vllm_b200.utils import get_centroids, get_ct_scaled
     from polarengine_vllm_b200.packing import pack_codes_half_block
+    from polarengine_vllm_b200.kernels import retile
     g = torch.Generator(device=dev).manual_seed(seed)
     out = {}
     for name, n, k, bits in PROJ:
@@ -63,7 +64,8 @@ def make_layer(dev, seed):
         del r
         norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(n, k // 128, device=dev, generator=g))).half()
         w = pack_codes_half_block(codes) if bits <= 4 else codes
-        out[name] = (w, bits <= 4, norms, get_ct_scaled(bits).to(dev), n, k)
+        # the decode kernel streams the tiled copy (what process_weights_after_loading builds)
+        out[name] = (w, bits <= 4, norms, get_ct_scaled(bits).to(dev), n, k, retile(w, bits <= 4, norms))
     return out
 
 
@@ -333,8 +335,9 @@ def main():
     outs = {name: torch.empty(a.batch, n, dtype=torch.float16, device=dev) for name, n, _, _ in PROJ}
 
     def launch(layer, name):
-        w, packed, norms, ct, n, k = layer[name]
-        return kernels.quant_matmul(w, packed, norms, ct, xh if k == HIDDEN else xi, False, n, k, k, torch.float16)
+        w, packed, norms, ct, n, k, tiles = layer[name]
+        return kernels.quant_matmul(w, packed, norms, ct, xh if k == HIDDEN else xi, False, n, k, k, torch.float16,
+                                    tiles=tiles)
 
     def ring_pass(names):
         for layer in layers:
@@ -392,7 +395,7 @@ def main():
     for name, n, k, bits in PROJ:
         m = PolarQuantLinearMethod(128, bits)
         mod = torch.nn.Module()
-        w, packed, norms, ct, _, _ = layers[0][name]
+        w, packed, norms, ct, _, _, tiles = layers[0][name]
         mod.in_f, mod.out_f, mod.in_f_padded, mod.n_blocks, mod.bits, mod.block_size = k, n, k, k // 128, bits, 128
         mod.packed, mod.norms, mod.ct_scaled = packed, norms, ct
         if packed:
@@ -402,7 +405,246 @@ def main():
         method[name], mods[name] = m, mod
     hx = {k: torch.randn(a.batch, k).half().pin_memory() for k in (HIDDEN, INTER)}
     hy = torch.empty(a.batch, HIDDEN, dtype=torch.float16).pin_memory()
-    e2e_steps = min(steps, 200)
+    e2e_steps = min(steps, 1000)
+
+    def e2e_body(i, dx):
+        layer = layers[i % RING]
+        y = None
+        for name, n, k, bits in PROJ:
+            mod = mods[name]
+            w, packed, norms, ct, _, _, tiles = layer[name]
+            mod.norms = norms
+            mod.codes_tiled = tiles
+            if packed:
+                mod.codes_packed = w
+            else:
+                mod.codes = w
+            y = method[name].apply(mod, dx[k])
+        return y
+
+    def e2e_step_eager(i):
+        dx = {k: v.to(dev, non_blocking=True) for k, v in hx.items()}
+        hy.copy_(e2e_body(i, dx), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    # The way a serving engine drives decode: the step (host->device copies of the pinned
+    # inputs, the four apply() calls, device->host copy of the result) is captured once per
+    # ring layer in a CUDA graph and replayed; every replay is followed by a host wait.
+    dx_static = {k: torch.empty(a.batch, k, dtype=torch.float16, device=dev) for k in hx}
+    graphs = []
+    with torch.cuda.stream(stream):
+        for i in range(RING):
+            for k in hx:
+                dx_static[k].copy_(hx[k], non_blocking=True)
+            hy.copy_(e2e_body(i, dx_static), non_blocking=True)  # warm the allocator
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                for k in hx:
+                    dx_static[k].copy_(hx[k], non_blocking=True)
+                hy.copy_(e2e_body(i, dx_static), non_blocking=True)
+            graphs.append(g)
+
+    def e2e_step_graph(i):
+        graphs[i % RING].replay()
+        stream.synchronize()
+
+    def time_e2e(step_fn):
+        with torch.cuda.stream(stream):
+            for i in range(2 * RING):
+                step_fn(i)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            for i in range(e2e_steps):
+                step_fn(i)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t)
+        return step_bytes(a.batch) * e2e_steps * world / dt / 1e9
+
+    e2e_graph = time_e2e(e2e_step_graph)
+    e2e_eager = time_e2e(e2e_step_eager)
+    e2e = {"value": e2e_graph, "unit": "GB/s",
+           "h2d_bytes_per_step": a.batch * (HIDDEN + INTER) * 2, "d2h_bytes_per_step": a.batch * HIDDEN * 2,
+           "steps": e2e_steps, "eager_value": e2e_eager,
+           "api": "PolarQuantLinearMethod.apply x4 per step with pinned host in/out copies, the step captured in a "
+                  "CUDA graph and waited on by the host after every replay; eager_value = same step without the graph"}
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        wb = model.weight_bytes_per_step()
+        print(json.dumps({
+            "metric": "9B-class decode tok/s", "unit": "tok/s", "value": b * a.new_tokens / el, "n_gpus": a.gpus,
+            "steps": a.new_tokens, "warmup": 3, "ms_per_step": el / a.new_tokens * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers, hidden 4096, vocab 151936, "
+                                   f"prompt {a.prompt}, {a.new_tokens} new tokens", "batch": b,
+                       "parallelism": f"tp{world}", "l2_defeat": "weights per rank larger than L2",
+                       "launch": "eager" if a.no_graph else "cuda graph"},
+            "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
+            "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
+            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (4 * a.layers + 2)}))
+    finish(world)
+
+
+def finish(world):
+    """Leave a multi-rank run.  Tearing down the NCCL communicator while captured graphs that contain its kernels are
+    alive can block forever; the ranks synchronise and exit without running the destructors instead."""
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--warmup", type=int, default=40)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
+                    help="decode: decoder-layer GEMV pass (default, the headline); prefill: Q4 GEMM sweep of BASELINE "
+                         "configs[2]; model: 36-layer 9B-class decode tok/s, tensor parallel over --gpus (configs[3])")
+    ap.add_argument("--layers", type=int, default=36, help="decoder layers for --workload model")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--no-graph", action="store_true", help="model workload: launch decode steps eagerly")
+    ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
+    ap.add_argument("--probe", default=None, metavar="PROJ",
+                    help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": "decoder_layer_gemv (BASELINE configs[1]): q/k/v Q5 fused, o Q6, gate/up Q3 fused, down Q4; "
+                          "hidden 4096, intermediate 12288", "batch": a.batch, "ring_layers": RING,
+              "l2_defeat": "inputs larger than L2 (ring of 8 layers = 964 MB of codes)",
+              "parallelism": f"replicas x{a.gpus}: each rank streams its own layers, no collective"}
+    base = {"metric": "quantized GEMV HBM GB/s", "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": config}
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        # The reference has no CPU implementation of apply() (its Triton wrappers need a GPU);
+        # its CPU-runnable path is the torch math its kernels are tested against = the oracle.
+        cb, per_step = cpu_baseline(a.batch, budget_s=max(5.0, min(60.0, 0.3 * (a.steps + a.warmup))))
+        line = dict(base, impl="reference", value=cb["value"], ms_per_step=per_step * 1e3, cpu_baseline=cb, gpu_launches=0,
+                    e2e={"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from polarengine_vllm_b200 import kernels
+    from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
+    if a.workload == "prefill":
+        prefill_sweep(a, dev, rank, world)
+        return finish(world)
+    if a.workload == "model":
+        return model_decode(a, dev, rank, world)
+
+    steps = max(RING, a.steps // RING * RING)
+    warm = max(3, a.warmup)
+    layers = [make_layer(dev, 1000 + 16 * i + 97 * rank) for i in range(RING)]
+    g = torch.Generator(device=dev).manual_seed(7)
+    xh = torch.randn(a.batch, HIDDEN, device=dev, generator=g).half()
+    xi = torch.randn(a.batch, INTER, device=dev, generator=g).half()
+    outs = {name: torch.empty(a.batch, n, dtype=torch.float16, device=dev) for name, n, _, _ in PROJ}
+
+    def launch(layer, name):
+        w, packed, norms, ct, n, k, tiles = layer[name]
+        return kernels.quant_matmul(w, packed, norms, ct, xh if k == HIDDEN else xi, False, n, k, k, torch.float16,
+                                    tiles=tiles)
+
+    def ring_pass(names):
+        for layer in layers:
+            for name in names:
+                launch(layer, name)
+
+    all_names = [p[0] for p in PROJ]
+    if a.probe:
+        ring_pass([a.probe])
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": a.probe, "launches": RING, "batch": a.batch}))
+        return
+    stream = torch.cuda.Stream(dev)
+
+    def timed_graph(names, reps, warm_reps):
+        """Capture one ring pass (RING steps) as a CUDA graph and time `reps` replays."""
+        with torch.cuda.stream(stream):
+            ring_pass(names)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                ring_pass(names)
+            for _ in range(warm_reps):
+                graph.replay()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            return e0.elapsed_time(e1) / 1e3
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    elapsed = timed_graph(all_names, steps // RING, max(1, math.ceil(warm / RING)))
+    # dominant kernel alone: the nibble-code GEMV on the 4096x12288 Q4 layer (down_proj)
+    dom = ["down_proj"]
+    dom_elapsed = timed_graph(dom, steps // RING, 1)
+    sampler.stop_flag = True
+    if world > 1:
+        t = torch.tensor([elapsed], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed = float(t)
+    value = step_bytes(a.batch) * steps * world / elapsed / 1e9
+
+    # ---- end to end through the plugin surface with host buffers
+    method = {}
+    mods = {}
+    for name, n, k, bits in PROJ:
+        m = PolarQuantLinearMethod(128, bits)
+        mod = torch.nn.Module()
+        w, packed, norms, ct, _, _, tiles = layers[0][name]
+        mod.in_f, mod.out_f, mod.in_f_padded, mod.n_blocks, mod.bits, mod.block_size = k, n, k, k // 128, bits, 128
+        mod.packed, mod.norms, mod.ct_scaled = packed, norms, ct
+        if packed:
+            mod.codes_packed, mod.in_f_half = w, k // 2
+        else:
+            mod.codes = w
+        method[name], mods[name] = m, mod
+    hx = {k: torch.randn(a.batch, k).half().pin_memory() for k in (HIDDEN, INTER)}
+    hy = torch.empty(a.batch, HIDDEN, dtype=torch.float16).pin_memory()
+    e2e_steps = min(steps, 1000)
 
     def e2e_step(i):
         layer = layers[i % RING]
@@ -410,8 +652,9 @@ def main():
         y = None
         for name, n, k, bits in PROJ:
             mod = mods[name]
-            w, packed, norms, ct, _, _ = layer[name]
+            w, packed, norms, ct, _, _, tiles = layer[name]
             mod.norms = norms
+            mod.codes_tiled = tiles
             if packed:
                 mod.codes_packed = w
             else:

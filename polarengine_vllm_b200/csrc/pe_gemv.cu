@@ -845,12 +845,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
             nA = __half2float(ns[(w * 16 + g) * nstr + slot]);
             nB = __half2float(ns[(w * 16 + g + 8) * nstr + slot]);
           }
-#ifdef PE_NO_MATH  // developer experiment: stream the codes, skip the arithmetic
-          acc[0] += __uint_as_float(cur.a0.x ^ cur.b0.w) * nA * nB;
-#else
           if (FMA) step_fma<PACKED, REGTAB>(acc, cur, lane_base, tb, xs + slot * slot_bytes, nA, nB, t, p.batch);
           else step_math<PACKED, NB, REGTAB>(acc, cur, lane_base, tb, xs + slot * slot_bytes, nA, nB, g, t, p.batch);
-#endif
           ++run;
           ++q;
           if (i_step % kBatch == kBatch - 1) {

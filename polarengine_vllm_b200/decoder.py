@@ -22,7 +22,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .kernels import quant_embedding, quant_matmul
+from .kernels import quant_embedding, quant_matmul, retile
 from .packing import pack_codes_half_block
 from .utils import get_centroids, get_ct_scaled
 
@@ -61,10 +61,12 @@ class QWeight:
         self.codes = pack_codes_half_block(codes) if self.packed else codes
         self.norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(out_f, in_f // 128, device=dev, generator=gen))).half()
         self.ct = get_ct_scaled(bits).to(dev)
+        self.tiles = retile(self.codes, self.packed, self.norms)  # streaming copy for decode-size batches
         self.out_f, self.in_f = out_f, in_f
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
-        return quant_matmul(self.codes, self.packed, self.norms, self.ct, x, False, self.out_f, self.in_f, self.in_f, out_dtype)
+        return quant_matmul(self.codes, self.packed, self.norms, self.ct, x, False, self.out_f, self.in_f, self.in_f, out_dtype,
+                            tiles=self.tiles)
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
