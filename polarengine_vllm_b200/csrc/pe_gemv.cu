@@ -32,7 +32,7 @@
 //    completes the tile (a counter per 16-row tile) sums the partials in CTA order,
 //    adds the bias, converts and stores.  No float atomics: results are bit-identical
 //    from run to run.  The counters return to zero, so the scratch is reusable.
-#include "pe_common.cuh"
+#include "pe_gemv_decode.cuh"
 
 namespace pe {
 
@@ -40,7 +40,6 @@ constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRowsPerCta = kWarps * 16;  // 256
 constexpr int kXRowBytes = 320;           // 256 B of activations + 64 B pad (bank spread)
-constexpr int kLutBytes = 32768;          // 256 entries x 32 lanes x 4 B (entry e of lane l at e*128 + l*4)
 constexpr int kRingPerWarp = 8192;        // bytes of code stream each warp keeps in flight
 
 struct GemvArgs {
@@ -74,13 +73,6 @@ __device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, u
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// low half of a, high half of b
-__device__ __forceinline__ uint32_t lo_hi(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, 0x7610;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-
 // Step-line arithmetic.  The host guarantees S * G < 2^31, so 32-bit division is exact.
 __device__ __forceinline__ int range_start(int S, int G, int c) { return (int)((unsigned)S * (unsigned)c / (unsigned)G); }
 __device__ __forceinline__ int owner_of(int S, int G, int idx) { return (int)(((unsigned)(idx + 1) * (unsigned)G - 1u) / (unsigned)S); }
@@ -100,10 +92,6 @@ struct CodeRegs {
   uint4 a0, b0;  // rows g and g+8
   uint4 a1, b1;  // second 16 B (byte codes only)
 };
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
 
 // Tiled layout (pe_retile): the codes of one step -- 16 rows x one 128-block -- are 1 KB
 // (2 KB for byte codes) of contiguous memory followed by the 16 fp16 block norms, and the
@@ -161,40 +149,6 @@ __device__ __forceinline__ void read_stage(CodeRegs<PACKED>& r, const uint8_t* s
   r.a0 = s4[0];
   r.b0 = s4[32];
   if (!PACKED) { r.a1 = s4[64]; r.b1 = s4[96]; }
-}
-
-// table address of byte BYTE of a code word: table + byte * 128 + lane * 4
-template <int BYTE>
-__device__ __forceinline__ uint32_t lut_addr(uint32_t word, uint32_t lane_base) {
-  uint32_t bt;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(bt) : "r"(word), "r"(0), "n"(0x4440 | BYTE));
-  return bt * 128u + lane_base;
-}
-__device__ __forceinline__ uint32_t lut_ld(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-
-// Register-resident centroid table for layers with at most 8 levels (3-bit codes stored in
-// nibbles): the low and the high byte of the eight fp16 centroids sit in two register
-// pairs, and one byte-permute looks four codes up at once -- a nibble 0..7 IS a valid
-// permute selector.  Two more permutes interleave low and high bytes into the fp16 pairs
-// (ct[lo nibble], ct[hi nibble]) the MMA wants.  No shared-memory traffic at all, which is
-// what bounds the table-lookup path.
-struct RegTable { uint32_t lo0, lo1, hi0, hi1; };
-
-// word (4 code bytes) -> the four A registers of its bytes 0..3
-__device__ __forceinline__ void reg_decode(uint32_t w, const RegTable& tb, uint32_t out[4]) {
-  uint32_t L, H, w2 = w >> 16;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(L) : "r"(tb.lo0), "r"(tb.lo1), "r"(w));
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(H) : "r"(tb.hi0), "r"(tb.hi1), "r"(w));
-  asm("prmt.b32 %0, %1, %2, 0x5140;" : "=r"(out[0]) : "r"(L), "r"(H));
-  asm("prmt.b32 %0, %1, %2, 0x7362;" : "=r"(out[1]) : "r"(L), "r"(H));
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(L) : "r"(tb.lo0), "r"(tb.lo1), "r"(w2));
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(H) : "r"(tb.hi0), "r"(tb.hi1), "r"(w2));
-  asm("prmt.b32 %0, %1, %2, 0x5140;" : "=r"(out[2]) : "r"(L), "r"(H));
-  asm("prmt.b32 %0, %1, %2, 0x7362;" : "=r"(out[3]) : "r"(L), "r"(H));
 }
 
 // Four MMAs (16 rows x 64 k) from two code words of row g (wa) and of row g+8 (wb).
@@ -336,16 +290,6 @@ __device__ __forceinline__ void step_math(float acc[NB / 2], const CodeRegs<PACK
 // g and g+8 against its own slice of the activations -- two fp16x2 chains of 8 per row and
 // block, widened to fp32 and scaled by the block norm -- and the four lanes of a row are
 // summed once per tile, at hand-off time.
-__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ float h2sum(uint32_t h) {
-  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
-  return f.x + f.y;
-}
-
 // A registers (fp16 pairs in activation order) of chunk j (16 bytes of activations) for rows g (a) and g+8 (b)
 template <bool PACKED, bool REGTAB>
 __device__ __forceinline__ void decode_chunk(const CodeRegs<PACKED>& r, int j, uint32_t lane_base, const RegTable& tb,
@@ -1025,6 +969,11 @@ static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void*
   }
   if (ld_x < (x_kind == PE_X_RAW ? in_f : in_f_padded) || ld_y < out_f) return PE_ERR_ARG;
 
+  if (!tiles) {  // one or two activation rows over whole-row items: the row-owner kernel, no scratch
+    const int r = gemv_rows_try(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
+                                y_dtype, ld_y, bias, batch, out_f, in_f_padded, static_cast<cudaStream_t>(stream));
+    if (r <= 0) return r;
+  }
   const int sms = sm_count();
   if (sms <= 0) return PE_ERR_CUDA;
   if (sms > kMaxSms || (out_f + 15) / 16 > kMaxRowTiles) return PE_ERR_LIMIT;

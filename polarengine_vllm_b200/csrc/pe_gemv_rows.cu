@@ -1,0 +1,398 @@
+// Row-owner matmul for one or two activation rows (the batch-1 / batch-2 decode step).
+//
+//   y[m, r] = sum_blk norm[r, blk] * sum_k ct[code[r, blk, k]] * xt[m, blk, k]   (+ bias[r])
+//
+// The tile kernel in pe_gemv.cu cuts a layer into equal byte ranges whatever its shape,
+// which splits weight rows between CTAs and ends every launch with a hand-off through
+// global memory (partials, a release/acquire pair, a second pass by the reducing CTA).
+// At 1..2 activation rows that tail is a fifth of the launch.  Here a CTA owns whole
+// weight rows instead, so nothing ever crosses CTAs:
+//
+//  * CTA c owns rows [c N / G, (c+1) N / G): one contiguous region of the row-major code
+//    array (the reference's layout, unchanged) and of the norm array.  No scratch memory.
+//  * The region is a line of 512-byte "items" (one weight row x 8 nibble blocks or 4 byte
+//    blocks); warp w of 16 takes a contiguous 1/16 of the line.  An item is one 16-byte
+//    asynchronous copy per lane into a lane-private ring in shared memory (12 items per
+//    warp in flight, ~100 KB per SM) plus one 16/8-byte copy of the item's block norms.
+//  * The activations are rotated once per CTA (zero-pad, FWHT-128 in registers and
+//    shuffles) and staged in shared memory as fp16, laid out so that the four 16-byte
+//    pieces a lane needs for an item are conflict-free 128-bit loads.
+//  * A lane multiplies its 32 (16) weights of the item with fp16x2 FMAs -- four short
+//    chains, widened to fp32 and scaled by the block norm -- and keeps a per-row fp32
+//    partial.  When a row ends the 32 lanes are summed by shuffles.  A row that lies
+//    inside one warp is stored directly; a row shared by neighbouring warps leaves one
+//    partial per warp in shared memory and is summed in warp order after the loop, so the
+//    result is bit-identical from run to run.
+//  * Centroid lookup as in the tile kernel: register table (byte permutes) for layers
+//    with at most eight levels, lane-replicated shared-memory table otherwise.
+#include "pe_gemv_decode.cuh"
+
+namespace pe {
+
+constexpr int kRowWarps = 16;
+constexpr int kRowThreads = kRowWarps * 32;
+constexpr int kItemBytes = 512;
+constexpr int kRowStage = kItemBytes + 16;  // codes + the item's norms
+
+struct RowArgs {
+  const uint8_t* codes;  // rows of cpr * 512 bytes, contiguous
+  const uint8_t* norms;  // fp16, rows of nb, contiguous
+  const float* ct; int n_levels;
+  const void* x; int x_kind; int x_dtype; int64_t ld_x; int in_f;
+  void* y; int y_dtype; int64_t ld_y;
+  const __half* bias;
+  int batch, N, K, nb, cpr;
+};
+
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// fp16 pairs of one code word, in the order the staged activations have them.
+//  PACKED: the four bytes' pairs (ct[low nibble], ct[high nibble]) = weights (k, k+64)
+//  !PACKED: two pairs (ct[c0], ct[c1]), (ct[c2], ct[c3]) = consecutive weights
+template <bool PACKED, bool REGTAB>
+__device__ __forceinline__ void decode_word(uint32_t w, uint32_t lane_base, const RegTable& tb, uint32_t a[4]) {
+  if (PACKED && REGTAB) {
+    reg_decode(w, tb, a);
+  } else {
+    const uint32_t ad0 = lut_addr<0>(w, lane_base), ad1 = lut_addr<1>(w, lane_base), ad2 = lut_addr<2>(w, lane_base),
+                   ad3 = lut_addr<3>(w, lane_base);
+    const uint32_t v0 = lut_ld(ad0), v1 = lut_ld(ad1), v2 = lut_ld(ad2), v3 = lut_ld(ad3);
+    if (PACKED) {
+      a[0] = v0; a[1] = v1; a[2] = v2; a[3] = v3;
+    } else {
+      a[0] = lo_hi(v0, v1);
+      a[1] = lo_hi(v2, v3);
+    }
+  }
+}
+
+// dot product of one lane's 16 bytes of codes with its slice of one activation row
+template <bool PACKED, bool REGTAB>
+__device__ __forceinline__ float item_dot(const uint32_t a[4][4], uint32_t xp) {
+  if (PACKED) {
+    const uint4 x0 = lds128(xp), x1 = lds128(xp + 512), x2 = lds128(xp + 1024), x3 = lds128(xp + 1536);
+    uint32_t c0 = hmul2_u(a[0][0], x0.x), c1 = hmul2_u(a[1][0], x1.x), c2 = hmul2_u(a[2][0], x2.x), c3 = hmul2_u(a[3][0], x3.x);
+    c0 = hfma2_u(a[0][1], x0.y, c0); c1 = hfma2_u(a[1][1], x1.y, c1); c2 = hfma2_u(a[2][1], x2.y, c2); c3 = hfma2_u(a[3][1], x3.y, c3);
+    c0 = hfma2_u(a[0][2], x0.z, c0); c1 = hfma2_u(a[1][2], x1.z, c1); c2 = hfma2_u(a[2][2], x2.z, c2); c3 = hfma2_u(a[3][2], x3.z, c3);
+    c0 = hfma2_u(a[0][3], x0.w, c0); c1 = hfma2_u(a[1][3], x1.w, c1); c2 = hfma2_u(a[2][3], x2.w, c2); c3 = hfma2_u(a[3][3], x3.w, c3);
+    return h2sum(hadd2_u(c0, c1)) + h2sum(hadd2_u(c2, c3));
+  } else {
+    const uint4 x0 = lds128(xp), x1 = lds128(xp + 512);
+    uint32_t c0 = hmul2_u(a[0][0], x0.x), c1 = hmul2_u(a[1][0], x0.z), c2 = hmul2_u(a[2][0], x1.x), c3 = hmul2_u(a[3][0], x1.z);
+    c0 = hfma2_u(a[0][1], x0.y, c0); c1 = hfma2_u(a[1][1], x0.w, c1); c2 = hfma2_u(a[2][1], x1.y, c2); c3 = hfma2_u(a[3][1], x1.w, c3);
+    return h2sum(hadd2_u(c0, c1)) + h2sum(hadd2_u(c2, c3));
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+
+__device__ __forceinline__ void emit_row(const RowArgs& p, int row, int m, float v) {
+  if (p.bias) v += __half2float(p.bias[row]);
+  store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + row, v);
+}
+
+// Where the rotated block `b` of an activation row goes: lane l holds elements 4l..4l+3.
+template <bool PACKED>
+__device__ __forceinline__ void place_row_block(uint8_t* xrow, int b, const float v[4], int lane) {
+  if (PACKED) {  // pairs (k, k+64); reader lane (b%8)*4 + k/16 takes piece (k%16)/4 of its item
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[i], 16);
+    if (lane < 16) {
+      const uint4 u = make_uint4(pack_half2(v[0], o[0]), pack_half2(v[1], o[1]), pack_half2(v[2], o[2]), pack_half2(v[3], o[3]));
+      *reinterpret_cast<uint4*>(xrow + (b >> 3) * 2048 + (lane & 3) * 512 + ((b & 7) * 4 + (lane >> 2)) * 16) = u;
+    }
+  } else {  // natural order; reader lane (b%4)*8 + k/16 takes piece (k%16)/8
+    const uint2 u = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+    *reinterpret_cast<uint2*>(xrow + (b >> 2) * 1024 + ((lane & 3) >> 1) * 512 + ((b & 3) * 8 + (lane >> 2)) * 16 + (lane & 1) * 8) = u;
+  }
+}
+
+template <bool PACKED, bool REGTAB, int NBATCH, int DEPTH>
+__global__ void __launch_bounds__(kRowThreads, 1) gemv_rows_kernel(const RowArgs p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ int ent_row[2 * kRowWarps];
+  __shared__ float ent_val[2 * kRowWarps][2];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int G = gridDim.x, cta = blockIdx.x;
+  constexpr int kNormBytes = PACKED ? 16 : 8;   // norms of one item
+  constexpr int kChunkX = PACKED ? 2048 : 1024;  // staged activation bytes one item reads from
+
+  const int r_beg = (int)((long long)p.N * cta / G), r_end = (int)((long long)p.N * (cta + 1) / G);
+  const int items = (r_end - r_beg) * p.cpr;
+  const int i0 = (int)((long long)items * w / kRowWarps), i1 = (int)((long long)items * (w + 1) / kRowWarps);
+
+  // Programmatic dependent launch: codes, norms and centroids never change, so they are
+  // requested before the previous kernel in the stream has finished; activations and the
+  // output belong to it until griddepcontrol.wait returns.
+  asm volatile("griddepcontrol.launch_dependents;");
+  float ct_mine = 0.f;
+  {
+    const int e = PACKED ? (lane & 15) : (w + 16 * (lane & 15));
+    if (e < p.n_levels) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(ct_mine) : "l"(p.ct + e));
+  }
+
+  // shared memory: [table 32 KB unless REGTAB][activations NBATCH x K fp16][ring]
+  uint8_t* lut_g = smem;
+  uint8_t* xs = smem + (REGTAB ? 0 : kLutBytes);
+  const int x_row_bytes = p.K * 2;
+  uint8_t* ring_g = xs + (size_t)NBATCH * x_row_bytes + (size_t)w * (DEPTH * kRowStage);
+  const uint32_t st_base = smem_u32(ring_g), st_end = st_base + DEPTH * kRowStage;
+
+  const int64_t gi0 = (int64_t)r_beg * p.cpr + i0;  // first item of this warp on the layer's item line
+  const uint8_t* cptr = p.codes + gi0 * kItemBytes + lane * 16;
+  const uint8_t* nptr = p.norms + gi0 * kNormBytes;
+  int n_fetch = i0;
+  {
+    uint32_t st = st_base;
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (n_fetch < i1) {
+        cp_async16(st + lane * 16, cptr);
+        if (lane == 0) {
+          if (PACKED) cp_async16(st + kItemBytes, nptr);
+          else cp_async8(st + kItemBytes, nptr);
+        }
+        cptr += kItemBytes;
+        nptr += kNormBytes;
+        ++n_fetch;
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      st += kRowStage;
+    }
+  }
+
+  // ---- centroid table
+  RegTable tb = {0, 0, 0, 0};
+  if (PACKED && REGTAB) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t hb = __half_as_ushort(__float2half_rn(__shfl_sync(0xffffffffu, ct_mine, i)));
+      if (i < 4) { tb.lo0 |= (hb & 0xff) << (8 * i); tb.hi0 |= (hb >> 8) << (8 * i); }
+      else { tb.lo1 |= (hb & 0xff) << (8 * (i - 4)); tb.hi1 |= (hb >> 8) << (8 * (i - 4)); }
+    }
+  } else if (PACKED) {
+    const float lo = __shfl_sync(0xffffffffu, ct_mine, w);  // entry w + 16 i: low nibble w, high nibble i
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float hi = __shfl_sync(0xffffffffu, ct_mine, i);
+      *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 128 + lane * 4) = pack_half2(lo, hi);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float c = __shfl_sync(0xffffffffu, ct_mine, i);
+      if (w + 16 * i < p.n_levels) *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 128 + lane * 4) = pack_half2(c, c);
+    }
+  }
+  const uint32_t lane_base = smem_u32(lut_g) + lane * 4;
+  if (lane == 0) { ent_row[2 * w] = -1; ent_row[2 * w + 1] = -1; }
+
+  // ---- activations: every (row, block) pair is one warp job; loads of a group go out
+  // together so that a warp pays one memory latency per group
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  {
+    const bool raw = p.x_kind == PE_X_RAW;
+    const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+    const int limit = raw ? p.in_f : p.K;
+    const int jobs = p.nb * NBATCH;
+    constexpr int U = 6;
+    for (int base = w; base < jobs; base += kRowWarps * U) {
+      float v[U][4];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int job = base + u * kRowWarps;
+        const bool on = job < jobs;
+        const int m = (NBATCH > 1 && job >= p.nb) ? 1 : 0;
+        const int b = job - m * p.nb;
+        load4_as_float(p.x, p.x_dtype, (int64_t)m * p.ld_x, (on ? b : 0) * kBlock + lane * 4, on ? limit : 0, vec_ok, v[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int job = base + u * kRowWarps;
+        if (job < jobs) {  // warp-uniform
+          const int m = (NBATCH > 1 && job >= p.nb) ? 1 : 0;
+          if (raw) warp_fwht128(v[u], lane);
+          place_row_block<PACKED>(xs + m * x_row_bytes, job - m * p.nb, v[u], lane);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- the item line
+  int ch = i0 % p.cpr;
+  int row = r_beg + i0 / p.cpr;
+  bool started_here = ch == 0;
+  int n_ent = 0;
+  float acc0 = 0.f, acc1 = 0.f;
+  const uint32_t xs_s = smem_u32(xs) + lane * 16;
+  uint32_t xp = xs_s + ch * kChunkX;
+  uint32_t st = st_base;
+  const uint32_t norm_off = kItemBytes + (PACKED ? (lane >> 2) : (lane >> 3)) * 2;
+  for (int i = i0; i < i1; ++i) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+    const uint4 q = lds128(st + lane * 16);
+    unsigned short nh;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh) : "r"(st + norm_off));
+    const float nrm = __half2float(__ushort_as_half(nh));
+    uint32_t a[4][4];
+    decode_word<PACKED, REGTAB>(q.x, lane_base, tb, a[0]);
+    decode_word<PACKED, REGTAB>(q.y, lane_base, tb, a[1]);
+    decode_word<PACKED, REGTAB>(q.z, lane_base, tb, a[2]);
+    decode_word<PACKED, REGTAB>(q.w, lane_base, tb, a[3]);
+    acc0 = fmaf(nrm, item_dot<PACKED, REGTAB>(a, xp), acc0);
+    if (NBATCH > 1) acc1 = fmaf(nrm, item_dot<PACKED, REGTAB>(a, xp + x_row_bytes), acc1);
+    __syncwarp();  // every lane has read the stage (codes and norms) before it is refilled
+    if (n_fetch < i1) {
+      cp_async16(st + lane * 16, cptr);
+      if (lane == 0) {
+        if (PACKED) cp_async16(st + kItemBytes, nptr);
+        else cp_async8(st + kItemBytes, nptr);
+      }
+      cptr += kItemBytes;
+      nptr += kNormBytes;
+      ++n_fetch;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    st += kRowStage;
+    if (st == st_end) st = st_base;
+    xp += kChunkX;
+    ++ch;
+    if (ch == p.cpr || i == i1 - 1) {  // the row ends, or this warp's share of it does
+      const float t0 = warp_sum(acc0);
+      const float t1 = NBATCH > 1 ? warp_sum(acc1) : 0.f;
+      if (started_here && ch == p.cpr) {
+        if (lane == 0) {
+          emit_row(p, row, 0, t0);
+          if (NBATCH > 1) emit_row(p, row, 1, t1);
+        }
+      } else {
+        if (lane == 0) {
+          ent_row[2 * w + n_ent] = row;
+          ent_val[2 * w + n_ent][0] = t0;
+          ent_val[2 * w + n_ent][1] = t1;
+        }
+        ++n_ent;
+      }
+      acc0 = acc1 = 0.f;
+      ch = 0;
+      xp = xs_s;
+      ++row;
+      started_here = true;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // ---- rows shared by neighbouring warps: the first entry of a row sums the row's
+  // entries in warp order (entries are in row order; unused slots hold -1)
+  __syncthreads();
+  if (tid < 2 * kRowWarps) {
+    const int r = ent_row[tid];
+    if (r >= 0) {
+      int prev = tid - 1;
+      while (prev >= 0 && ent_row[prev] < 0) --prev;
+      if (prev < 0 || ent_row[prev] != r) {
+        float s0 = 0.f, s1 = 0.f;
+        for (int f = tid; f < 2 * kRowWarps; ++f) {
+          const int rr = ent_row[f];
+          if (rr == r) { s0 += ent_val[f][0]; s1 += ent_val[f][1]; }
+          else if (rr >= 0) break;
+        }
+        emit_row(p, r, 0, s0);
+        if (NBATCH > 1) emit_row(p, r, 1, s1);
+      }
+    }
+  }
+}
+
+template <bool PACKED, bool REGTAB, int NBATCH, int DEPTH>
+static int launch_rows(const RowArgs& a, int G, unsigned dyn_bytes, cudaStream_t st) {
+  auto kfn = gemv_rows_kernel<PACKED, REGTAB, NBATCH, DEPTH>;
+  static thread_local unsigned configured[16] = {0};
+  int dev = 0;
+  PE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 16 || configured[dev] < dyn_bytes) {
+    PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_bytes));
+    if (dev < 16) configured[dev] = dyn_bytes;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(G);
+  cfg.blockDim = dim3(kRowThreads);
+  cfg.dynamicSmemBytes = dyn_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, a));
+  return PE_OK;
+}
+
+template <bool PACKED, bool REGTAB, int NBATCH>
+static int launch_rows_depth(const RowArgs& a, int G, unsigned fixed, cudaStream_t st) {
+  const unsigned deep = fixed + kRowWarps * 12u * kRowStage, shallow = fixed + kRowWarps * 8u * kRowStage;
+  if (deep <= 231424u) return launch_rows<PACKED, REGTAB, NBATCH, 12>(a, G, deep, st);
+  if (shallow <= 231424u) return launch_rows<PACKED, REGTAB, NBATCH, 8>(a, G, shallow, st);
+  return 1;
+}
+
+int gemv_rows_try(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                  const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f,
+                  void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f, int in_f_padded,
+                  cudaStream_t stream) {
+  if (batch > 2 || !codes || !norms) return 1;
+  const int K = in_f_padded, nb = K / kBlock;
+  const int64_t row_bytes = packed ? K / 2 : K;
+  if (row_bytes % kItemBytes || ld_codes != row_bytes || ld_norms != nb) return 1;
+  if (reinterpret_cast<uintptr_t>(norms) & 15) return 1;
+  const int sms = sm_count();
+  if (sms <= 0) return PE_ERR_CUDA;
+  const int cpr = (int)(row_bytes / kItemBytes);
+  const int G = out_f < sms ? out_f : sms;
+  if ((long long)out_f * cpr < (long long)G * kRowWarps * 4) return 1;  // too little work per warp: tile kernel
+  if ((long long)out_f * cpr >= (1ll << 31)) return 1;
+
+  RowArgs a;
+  a.codes = static_cast<const uint8_t*>(codes);
+  a.norms = static_cast<const uint8_t*>(norms);
+  a.ct = ct_scaled; a.n_levels = n_levels;
+  a.x = x; a.x_kind = x_kind; a.x_dtype = x_dtype; a.ld_x = ld_x; a.in_f = in_f;
+  a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  a.bias = static_cast<const __half*>(bias);
+  a.batch = batch; a.N = out_f; a.K = K; a.nb = nb; a.cpr = cpr;
+  const bool regtab = packed && n_levels <= 8;
+  const unsigned fixed = (regtab ? 0u : (unsigned)kLutBytes) + (unsigned)batch * (unsigned)K * 2u;
+  if (packed) {
+    if (regtab) return batch == 1 ? launch_rows_depth<true, true, 1>(a, G, fixed, stream)
+                                  : launch_rows_depth<true, true, 2>(a, G, fixed, stream);
+    return batch == 1 ? launch_rows_depth<true, false, 1>(a, G, fixed, stream)
+                      : launch_rows_depth<true, false, 2>(a, G, fixed, stream);
+  }
+  return batch == 1 ? launch_rows_depth<false, false, 1>(a, G, fixed, stream)
+                    : launch_rows_depth<false, false, 2>(a, G, fixed, stream);
+}
+
+}  // namespace pe

@@ -43,7 +43,8 @@ def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scal
                  bias: Optional[torch.Tensor] = None, tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y (batch, out_f) for x (batch, in_f or in_f_padded); the single entry to the
     native kernels used by everything else in the package.  ``tiles`` (from
-    :func:`retile`) lets batches of up to 16 rows stream the tiled copy of the layer."""
+    :func:`retile`) lets batches of 3..16 rows stream the tiled copy of the layer; one or
+    two rows read the row-major arrays (whole weight rows per CTA, no scratch traffic)."""
     dev = nv.require_cuda(codes, norms, ct_scaled, x)
     nv.ensure_init(dev)
     if x.dim() != 2 or x.stride(1) != 1:
@@ -70,7 +71,7 @@ def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scal
         for m0 in range(0, batch, GEMV_MAX_BATCH):
             m1 = min(batch, m0 + GEMV_MAX_BATCH)
             xs, ys = x[m0:m1], y[m0:m1]
-            if tiles is not None:
+            if tiles is not None and batch > 2:
                 nv.check(l.pe_gemv_tiled(tiles.data_ptr(), int(packed), ct.data_ptr(), ct.numel(), xs.data_ptr(),
                                          nv.PE_X_ROTATED if rotated else nv.PE_X_RAW, nv.dtype_code(xs), xs.stride(0),
                                          in_f, ys.data_ptr(), nv.dtype_code(ys), ys.stride(0),
