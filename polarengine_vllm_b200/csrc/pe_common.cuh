@@ -90,11 +90,11 @@ __device__ __forceinline__ void warp_fwht128(float v[4], int lane) {
   v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
 #pragma unroll
   for (int m = 1; m <= 16; m <<= 1) {
-    const bool upper = (lane & m) != 0;
+    const float sgn = (lane & m) ? -1.f : 1.f;  // upper half of the pair: partner - own (one FMA, exact)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float o = __shfl_xor_sync(0xffffffffu, v[i], m);
-      v[i] = upper ? (o - v[i]) : (v[i] + o);
+      v[i] = fmaf(sgn, v[i], o);
     }
   }
   const float s = 0.08838834764831845f;  // 1/sqrt(128)

@@ -327,6 +327,314 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_rows_kernel(const RowArgs
   }
 }
 
+// ---- one activation row: activations in registers -----------------------------------
+//
+// With a single activation row the loop above is bound by shared-memory bandwidth: every
+// 512 bytes of codes drag 2 KB of staged activations through the same port as the ring
+// and the table.  Here an item is FOUR weight rows x 128 bytes (8 lanes x 16 B per row)
+// and warp w owns the 128-byte column chunks w, w+16, ... of the CTA's rows, so a lane
+// meets the same few activation slices over and over and keeps them in registers (16
+// fp16 pairs per chunk, at most CPW chunks).  The price is a reduction per item -- three
+// shuffles over the 8 lanes of a row, once per row group and warp -- and a sum over the
+// 16 warps' column partials through shared memory, in warp order (bit-reproducible),
+// after every pass of 256 rows.  Each warp rotates only the blocks it owns.
+constexpr int kPassRows = 256;
+constexpr int kPartStride = kRowWarps + 1;  // floats per row in the partial array (bank spread)
+
+struct ColArgs {
+  const uint8_t* codes; int64_t ld_codes;  // bytes
+  const uint8_t* norms; int64_t ld_norms;  // bytes between rows of fp16 norms
+  const float* ct; int n_levels;
+  const void* x; int x_kind; int x_dtype; int in_f;
+  void* y; int y_dtype;
+  const __half* bias;
+  int N, K, n_chunks;
+};
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
+template <bool PACKED, bool REGTAB, int CPW, int DEPTH>
+__global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs p) {
+  static_assert(DEPTH % CPW == 0, "the ring holds whole row groups");
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int rs = lane >> 3, pc = lane & 7;  // row of the group, 16-byte piece of the chunk
+  const int G = gridDim.x, cta = blockIdx.x;
+  constexpr int kXPerChunk = PACKED ? 16 : 8;  // fp16 pairs a lane keeps per chunk
+  constexpr int kRgDepth = DEPTH / CPW;        // row groups in flight per warp
+  constexpr int kNormStep = PACKED ? 64 : 32;  // norm bytes between this warp's chunks
+
+  const int r_beg = (int)((long long)p.N * cta / G), r_end = (int)((long long)p.N * (cta + 1) / G);
+  const int n_rg = (r_end - r_beg + 3) >> 2;
+  int cnt = (p.n_chunks - w + kRowWarps - 1) / kRowWarps;  // chunks w, w+16, ... of this warp
+  cnt = cnt < 0 ? 0 : (cnt > CPW ? CPW : cnt);
+
+  asm volatile("griddepcontrol.launch_dependents;");
+  float ct_mine = 0.f;
+  {
+    const int e = PACKED ? (lane & 15) : (w + 16 * (lane & 15));
+    if (e < p.n_levels) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(ct_mine) : "l"(p.ct + e));
+  }
+
+  // shared memory: [table 32 KB unless REGTAB][rotation scratch][partials][ring]
+  uint8_t* lut_g = smem;
+  uint8_t* xw = smem + (REGTAB ? 0 : kLutBytes) + (size_t)w * (CPW * 512);
+  float* part = reinterpret_cast<float*>(smem + (REGTAB ? 0 : kLutBytes) + (size_t)kRowWarps * CPW * 512);
+  uint8_t* ring_g = reinterpret_cast<uint8_t*>(part) + kPassRows * kPartStride * 4 + (size_t)w * (DEPTH * kRowStage);
+  const uint32_t st_base = smem_u32(ring_g), st_end = st_base + DEPTH * kRowStage;
+
+  // ---- code stream.  The ring slot of item (row group rg, chunk slot j) is
+  // (rg % kRgDepth) * CPW + j, so the refill issued after item (rg, j) is item
+  // (rg + kRgDepth, j): same slot, same j, and the source is a running pointer plus a
+  // compile-time offset.  One copy group per slot, empty for slots the warp does not
+  // have, so the group count the math waits on is a constant.  Rows past the end of
+  // the matrix are not fetched (their sums are never stored).
+  const uint8_t* cptr_f = p.codes + (int64_t)(r_beg + rs) * p.ld_codes + (size_t)w * 128 + pc * 16;
+  const uint8_t* nptr_f = p.norms + (int64_t)(r_beg + (lane & 3)) * p.ld_norms + (PACKED ? (size_t)w * 4 : (size_t)(w & ~1) * 2);
+  const int64_t cstep = 4 * p.ld_codes, nstep = 4 * p.ld_norms;
+  int rg_f = 0;
+  bool row_ok = r_beg + rs < p.N, nrow_ok = lane < 4 && r_beg + lane < p.N;
+  auto fetch_group = [&](uint32_t st_rg) {  // all chunk slots of row group rg_f
+#pragma unroll
+    for (int j = 0; j < CPW; ++j) {
+      if (j < cnt && rg_f < n_rg) {
+        if (row_ok) cp_async16(st_rg + j * kRowStage + lane * 16, cptr_f + j * 2048);
+        if (nrow_ok) cp_async4(st_rg + j * kRowStage + kItemBytes + lane * 4, nptr_f + j * kNormStep);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+  };
+  auto advance_fetch = [&]() {
+    ++rg_f;
+    cptr_f += cstep;
+    nptr_f += nstep;
+    row_ok = r_beg + 4 * rg_f + rs < p.N;
+    nrow_ok = lane < 4 && r_beg + 4 * rg_f + lane < p.N;
+  };
+#pragma unroll
+  for (int d = 0; d < kRgDepth; ++d) {
+    fetch_group(st_base + d * (CPW * kRowStage));
+    advance_fetch();
+  }
+
+  // ---- centroid table
+  RegTable tb = {0, 0, 0, 0};
+  if (PACKED && REGTAB) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t hb = __half_as_ushort(__float2half_rn(__shfl_sync(0xffffffffu, ct_mine, i)));
+      if (i < 4) { tb.lo0 |= (hb & 0xff) << (8 * i); tb.hi0 |= (hb >> 8) << (8 * i); }
+      else { tb.lo1 |= (hb & 0xff) << (8 * (i - 4)); tb.hi1 |= (hb >> 8) << (8 * (i - 4)); }
+    }
+  } else if (PACKED) {
+    const float lo = __shfl_sync(0xffffffffu, ct_mine, w);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float hi = __shfl_sync(0xffffffffu, ct_mine, i);
+      *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 128 + lane * 4) = pack_half2(lo, hi);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float c = __shfl_sync(0xffffffffu, ct_mine, i);
+      if (w + 16 * i < p.n_levels) *reinterpret_cast<uint32_t*>(lut_g + (w + 16 * i) * 128 + lane * 4) = pack_half2(c, c);
+    }
+  }
+  const uint32_t lane_base = smem_u32(lut_g) + lane * 4;
+
+  // ---- this warp's activation slices: load, rotate, bounce through the warp's scratch
+  // into the item layout, keep in registers
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  uint32_t xr[CPW][kXPerChunk];
+  {
+    const bool raw = p.x_kind == PE_X_RAW;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+    const bool fast = vec_ok && p.x_dtype == PE_F16;
+    const int limit = raw ? p.in_f : p.K;
+    constexpr int BPC = PACKED ? 2 : 1;  // quantization blocks per chunk
+    float v[CPW * BPC][4];
+#pragma unroll
+    for (int u = 0; u < CPW * BPC; ++u) {
+      const bool on = u / BPC < cnt;
+      const int col = (on ? (w + 16 * (u / BPC)) * BPC + (u % BPC) : 0) * kBlock + lane * 4;
+      if (fast && on && col + 4 <= limit) {  // the common case inline: four fp16 values, one 8-byte load
+        uint2 h;
+        asm volatile("ld.global.v2.u32 {%0,%1}, [%2];" : "=r"(h.x), "=r"(h.y) : "l"(reinterpret_cast<const __half*>(p.x) + col));
+        const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h.x)), f1 = __half22float2(*reinterpret_cast<__half2*>(&h.y));
+        v[u][0] = f0.x; v[u][1] = f0.y; v[u][2] = f1.x; v[u][3] = f1.y;
+      } else {
+        load4_as_float(p.x, p.x_dtype, 0, col, on ? limit : 0, vec_ok, v[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < CPW * BPC; ++u) {
+      if (u / BPC < cnt) {  // warp-uniform
+        if (raw) warp_fwht128(v[u], lane);
+        uint8_t* dst = xw + (u / BPC) * 512 + (u % BPC) * 256;
+        if (PACKED) {  // pairs (k, k+64), in pair order
+          float o[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[u][i], 16);
+          if (lane < 16)
+            *reinterpret_cast<uint4*>(dst + lane * 16) = make_uint4(pack_half2(v[u][0], o[0]), pack_half2(v[u][1], o[1]),
+                                                                    pack_half2(v[u][2], o[2]), pack_half2(v[u][3], o[3]));
+        } else {
+          *reinterpret_cast<uint2*>(dst + lane * 8) = make_uint2(pack_half2(v[u][0], v[u][1]), pack_half2(v[u][2], v[u][3]));
+        }
+      }
+    }
+    __syncwarp();
+    const uint32_t xw_s = smem_u32(xw) + (PACKED ? (pc >> 2) * 256 + (pc & 3) * 64 : pc * 32);
+#pragma unroll
+    for (int j = 0; j < CPW; ++j) {
+#pragma unroll
+      for (int i = 0; i < kXPerChunk / 4; ++i) {
+        uint4 t = make_uint4(0, 0, 0, 0);
+        if (j < cnt) t = lds128(xw_s + j * 512 + i * 16);
+        xr[j][4 * i + 0] = t.x; xr[j][4 * i + 1] = t.y; xr[j][4 * i + 2] = t.z; xr[j][4 * i + 3] = t.w;
+      }
+    }
+  }
+
+  if (!REGTAB) __syncthreads();  // the shared table has entries from every warp
+
+  // ---- the item line, in passes of kPassRows rows
+  const int n_warps_used = p.n_chunks < kRowWarps ? p.n_chunks : kRowWarps;
+  const uint32_t q_off = lane * 16;
+  const uint32_t norm_off = kItemBytes + rs * 4 + (PACKED ? (pc >> 2) * 2 : (w & 1) * 2);
+  uint32_t st_rg = st_base;
+  for (int rg0 = 0; rg0 < n_rg; rg0 += kPassRows / 4) {
+    const int rg1 = n_rg < rg0 + kPassRows / 4 ? n_rg : rg0 + kPassRows / 4;
+    if (cnt > 0) {
+      uint32_t part_s = smem_u32(part) + (rs * kPartStride + w) * 4;
+      for (int rg = rg0; rg < rg1; ++rg) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) {
+          asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+          if (j < cnt) {
+            const uint32_t st = st_rg + j * kRowStage;
+            const uint4 q = lds128(st + q_off);
+            unsigned short nh;
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh) : "r"(st + norm_off));
+            uint32_t a[4][4];
+            decode_word<PACKED, REGTAB>(q.x, lane_base, tb, a[0]);
+            decode_word<PACKED, REGTAB>(q.y, lane_base, tb, a[1]);
+            decode_word<PACKED, REGTAB>(q.z, lane_base, tb, a[2]);
+            decode_word<PACKED, REGTAB>(q.w, lane_base, tb, a[3]);
+            uint32_t c0, c1, c2, c3;
+            if (PACKED) {
+              c0 = hmul2_u(a[0][0], xr[j][0]); c1 = hmul2_u(a[1][0], xr[j][4]); c2 = hmul2_u(a[2][0], xr[j][8]); c3 = hmul2_u(a[3][0], xr[j][12]);
+#pragma unroll
+              for (int i = 1; i < 4; ++i) {
+                c0 = hfma2_u(a[0][i], xr[j][i], c0); c1 = hfma2_u(a[1][i], xr[j][4 + i], c1);
+                c2 = hfma2_u(a[2][i], xr[j][8 + i], c2); c3 = hfma2_u(a[3][i], xr[j][12 + i], c3);
+              }
+            } else {
+              c0 = hmul2_u(a[0][0], xr[j][0]); c1 = hmul2_u(a[1][0], xr[j][2]); c2 = hmul2_u(a[2][0], xr[j][4]); c3 = hmul2_u(a[3][0], xr[j][6]);
+              c0 = hfma2_u(a[0][1], xr[j][1], c0); c1 = hfma2_u(a[1][1], xr[j][3], c1);
+              c2 = hfma2_u(a[2][1], xr[j][5], c2); c3 = hfma2_u(a[3][1], xr[j][7], c3);
+            }
+            const float s = h2sum(hadd2_u(c0, c1)) + h2sum(hadd2_u(c2, c3));
+            acc = fmaf(__half2float(__ushort_as_half(nh)), s, acc);
+          }
+          __syncwarp();  // every lane has read the slot before it is refilled
+          if (j < cnt && rg_f < n_rg) {
+            if (row_ok) cp_async16(st_rg + j * kRowStage + q_off, cptr_f + j * 2048);
+            if (nrow_ok) cp_async4(st_rg + j * kRowStage + kItemBytes + lane * 4, nptr_f + j * kNormStep);
+          }
+          asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        advance_fetch();
+        st_rg += CPW * kRowStage;
+        if (st_rg == st_end) st_rg = st_base;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        if (pc == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_s), "f"(acc) : "memory");
+        part_s += 4 * kPartStride * 4;
+      }
+    }
+    __syncthreads();
+    for (int r = tid; r < 4 * (rg1 - rg0); r += kRowThreads) {
+      const int row = r_beg + 4 * rg0 + r;
+      if (row < r_end) {
+        float s = 0.f;
+        for (int ww = 0; ww < n_warps_used; ++ww) s += part[r * kPartStride + ww];
+        if (p.bias) s += __half2float(p.bias[row]);
+        store_from_float(p.y, p.y_dtype, row, s);
+      }
+    }
+    if (rg1 < n_rg) __syncthreads();
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+template <bool PACKED, bool REGTAB, int CPW>
+static int launch_cols(const ColArgs& a, int G, cudaStream_t st) {
+  constexpr int DEPTH = 12;
+  const unsigned dyn_bytes = (REGTAB ? 0u : (unsigned)kLutBytes) + kRowWarps * CPW * 512u + kPassRows * kPartStride * 4u +
+                             kRowWarps * DEPTH * (unsigned)kRowStage;
+  auto kfn = gemv_cols_kernel<PACKED, REGTAB, CPW, DEPTH>;
+  static thread_local bool configured[16] = {false};
+  int dev = 0;
+  PE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 16 || !configured[dev]) {
+    PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_bytes));
+    if (dev < 16) configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(G);
+  cfg.blockDim = dim3(kRowThreads);
+  cfg.dynamicSmemBytes = dyn_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, a));
+  return PE_OK;
+}
+
+template <bool PACKED, bool REGTAB>
+static int launch_cols_cpw(const ColArgs& a, int cpw, int G, cudaStream_t st) {
+  switch (cpw) {
+    case 1: return launch_cols<PACKED, REGTAB, 1>(a, G, st);
+    case 2: return launch_cols<PACKED, REGTAB, 2>(a, G, st);
+    case 3: return launch_cols<PACKED, REGTAB, 3>(a, G, st);
+    case 4: return launch_cols<PACKED, REGTAB, 4>(a, G, st);
+    default: return 1;
+  }
+}
+
+// batch 1: returns 1 if the shape is not this kernel's kind
+static int gemv_cols_try(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                         const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int in_f, void* y,
+                         int y_dtype, const void* bias, int out_f, int K, int sms, cudaStream_t stream) {
+  const int64_t row_bytes = packed ? K / 2 : K;
+  // norms are copied 4 bytes (two blocks) at a time: rows of norms must start 4-byte aligned and hold an even count
+  if (row_bytes % 128 || (ld_norms & 1) || ((K / kBlock) & 1) || (reinterpret_cast<uintptr_t>(norms) & 3)) return 1;
+  const int n_chunks = (int)(row_bytes / 128);
+  const int cpw = (n_chunks + kRowWarps - 1) / kRowWarps;
+  if (cpw > 4) return 1;
+  const int G = out_f / 8 < sms ? out_f / 8 : sms;  // at least two row groups per CTA
+  if (G < 1 || (long long)out_f * n_chunks < (long long)G * kRowWarps * 16) return 1;
+  ColArgs a;
+  a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
+  a.norms = static_cast<const uint8_t*>(norms); a.ld_norms = ld_norms * 2;
+  a.ct = ct_scaled; a.n_levels = n_levels;
+  a.x = x; a.x_kind = x_kind; a.x_dtype = x_dtype; a.in_f = in_f;
+  a.y = y; a.y_dtype = y_dtype;
+  a.bias = static_cast<const __half*>(bias);
+  a.N = out_f; a.K = K; a.n_chunks = n_chunks;
+  if (packed && n_levels <= 8) return launch_cols_cpw<true, true>(a, cpw, G, stream);
+  if (packed) return launch_cols_cpw<true, false>(a, cpw, G, stream);
+  return launch_cols_cpw<false, false>(a, cpw, G, stream);
+}
+
 template <bool PACKED, bool REGTAB, int NBATCH, int DEPTH>
 static int launch_rows(const RowArgs& a, int G, unsigned dyn_bytes, cudaStream_t st) {
   auto kfn = gemv_rows_kernel<PACKED, REGTAB, NBATCH, DEPTH>;
@@ -365,6 +673,13 @@ int gemv_rows_try(const void* codes, int packed, int64_t ld_codes, const void* n
                   cudaStream_t stream) {
   if (batch > 2 || !codes || !norms) return 1;
   const int K = in_f_padded, nb = K / kBlock;
+  if (batch == 1) {
+    const int n_sms = sm_count();
+    if (n_sms <= 0) return PE_ERR_CUDA;
+    const int r = gemv_cols_try(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, in_f, y,
+                                y_dtype, bias, out_f, K, n_sms, stream);
+    if (r <= 0) return r;
+  }
   const int64_t row_bytes = packed ? K / 2 : K;
   if (row_bytes % kItemBytes || ld_codes != row_bytes || ld_norms != nb) return 1;
   if (reinterpret_cast<uintptr_t>(norms) & 15) return 1;
