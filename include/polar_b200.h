@@ -78,6 +78,27 @@ int pe_embedding(const void* codes, int packed, int64_t ld_codes, const void* no
                  const float* ct_scaled, int n_levels, const int64_t* ids, int64_t vocab, void* out, int out_dtype,
                  int64_t ld_out, int tokens, int hidden, int hidden_padded, void* stream);
 
+/* ---- decoder-layer glue ops (no reference counterpart) -----------------------
+ * The reference leaves these to the serving framework (vLLM's fused RMSNorm, rotary and
+ * activation ops); they are here so that an end-to-end decode step can be timed without
+ * dozens of small framework kernels between the quantized projections.  fp16 tensors.
+ *
+ * pe_add_rmsnorm: x (rows, hidden) is the residual stream, updated in place with
+ *   x += fp16(delta) when delta (fp16 or fp32, same shape, may be NULL) is given;
+ *   out = fp16(x * rsqrt(mean(x^2) + eps)) * weight.  hidden % 8 == 0, hidden <= 16384.
+ * pe_rope_cache: qkv (batch*t, (hq + 2 hkv) * head_dim), row stride ld_qkv.  Token i of a
+ *   sequence sits at position base + i, base = *pos_dev if pos_dev is not NULL (a device
+ *   scalar, for graph replay) else pos_host.  Rotate-half rotary embedding of the query and
+ *   key heads (frequencies theta^(-2j/d)); queries go to q_out (batch, hq, t, head_dim),
+ *   rotated keys and the values into the caches (batch, hkv, max_len, head_dim) at their
+ *   positions (positions outside [0, max_len) are dropped).
+ * pe_silu_mul: out[r, i] = fp16(silu(gate_up[r, i])) * gate_up[r, inter + i]. */
+int pe_add_rmsnorm(void* x, const void* delta, int delta_dtype, const void* weight, void* out, int rows, int hidden,
+                   float eps, void* stream);
+int pe_rope_cache(const void* qkv, int64_t ld_qkv, const int64_t* pos_dev, int64_t pos_host, void* q_out, void* k_cache,
+                  void* v_cache, int batch, int t, int hq, int hkv, int head_dim, int max_len, float theta, void* stream);
+int pe_silu_mul(const void* gate_up, int64_t ld_gu, void* out, int64_t ld_out, int rows, int inter, void* stream);
+
 /* ---- nibble packing ---------------------------------------------------------
  * int8 codes (out_f, in_f_padded) -> uint8 (out_f, in_f_padded/2), byte i of each
  * 128-block = code[64+i] << 4 | code[i].  Replaces pack_codes_int4

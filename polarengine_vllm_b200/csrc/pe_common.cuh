@@ -57,29 +57,58 @@ __device__ __forceinline__ void store_from_float(void* base, int dtype, int64_t 
   else reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
 }
 
-// 4 consecutive elements starting at a multiple of 4, zero beyond `limit`
-static __device__ __noinline__ void load4_as_float(const void* base, int dtype, int64_t row_off, int col,
-                                               int limit, bool vec_ok, float v[4]) {
+// 4 consecutive elements starting at a multiple of 4, zero beyond `limit`, in two steps so
+// that a caller can issue the loads of several items before converting any of them (the
+// hardware issues in program order: a conversion right behind its load makes the next load
+// wait a full memory round trip).
+struct Raw4 { uint32_t w[4]; };  // fp32: four words; fp16 / bf16: two words
+
+__device__ __forceinline__ Raw4 load4_raw(const void* base, int dtype, int64_t row_off, int col, int limit, bool vec_ok) {
+  Raw4 r = {{0u, 0u, 0u, 0u}};
   if (vec_ok && col + 4 <= limit) {
     if (dtype == PE_F32) {
-      float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + row_off + col);
-      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+      asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3])
+                   : "l"(reinterpret_cast<const float*>(base) + row_off + col));
     } else {
-      uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + row_off + col);
-      if (dtype == PE_F16) {
-        float2 a = __half22float2(*reinterpret_cast<__half2*>(&u.x));
-        float2 b = __half22float2(*reinterpret_cast<__half2*>(&u.y));
-        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-      } else {
-        float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
-        float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
-        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+      asm volatile("ld.global.v2.u32 {%0,%1}, [%2];"
+                   : "=r"(r.w[0]), "=r"(r.w[1])
+                   : "l"(reinterpret_cast<const uint16_t*>(base) + row_off + col));
+    }
+  } else {  // ragged edge or unaligned rows: element loads
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (col + i < limit) {
+        if (dtype == PE_F32) {
+          r.w[i] = reinterpret_cast<const uint32_t*>(base)[row_off + col + i];
+        } else {
+          const uint32_t h = reinterpret_cast<const uint16_t*>(base)[row_off + col + i];
+          r.w[i >> 1] |= h << (16 * (i & 1));
+        }
       }
     }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = (col + i < limit) ? load_as_float(base, dtype, row_off + col + i) : 0.f;
   }
+  return r;
+}
+
+__device__ __forceinline__ void cvt4(const Raw4& r, int dtype, float v[4]) {
+  if (dtype == PE_F32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r.w[i]);
+  } else if (dtype == PE_F16) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.w[0]));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&r.w[1]));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  } else {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.w[0]));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.w[1]));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+}
+
+__device__ __forceinline__ void load4_as_float(const void* base, int dtype, int64_t row_off, int col, int limit,
+                                               bool vec_ok, float v[4]) {
+  cvt4(load4_raw(base, dtype, row_off, col, limit, vec_ok), dtype, v);
 }
 
 // FWHT-128 across one warp.  Lane l holds elements 4l..4l+3 of the block on entry and

@@ -40,7 +40,6 @@ constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRowsPerCta = kWarps * 16;  // 256
 constexpr int kXRowBytes = 320;           // 256 B of activations + 64 B pad (bank spread)
-constexpr int kRingPerWarp = 8192;        // bytes of code stream each warp keeps in flight
 
 struct GemvArgs {
   const uint8_t* codes; int64_t ld_codes;   // row-major layout (the reference's)
@@ -502,6 +501,7 @@ __device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* 
     constexpr int U = 4;
     for (int base = warp; base < items; base += kWarps * U) {
       float v[U][4];
+      Raw4 raw4[U];
       int sl[U], mm[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -509,9 +509,10 @@ __device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* 
         const bool on = item < items;
         sl[u] = on ? item / p.batch : 0;
         mm[u] = on ? item - sl[u] * p.batch : 0;
-        load4_as_float(p.x, p.x_dtype, (int64_t)mm[u] * p.ld_x, slot_blk[sl[u]] * kBlock + lane * 4,
-                       on ? p.in_f : 0, vec_ok, v[u]);
+        raw4[u] = load4_raw(p.x, p.x_dtype, (int64_t)mm[u] * p.ld_x, slot_blk[sl[u]] * kBlock + lane * 4, on ? p.in_f : 0, vec_ok);
       }
+#pragma unroll
+      for (int u = 0; u < U; ++u) cvt4(raw4[u], p.x_dtype, v[u]);
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (base + u * kWarps < items) {  // warp-uniform
@@ -526,6 +527,7 @@ __device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* 
     constexpr int U = 2;
     for (int base = warp * 32 + lane; base < total; base += kThreads * U) {
       float a[U][4], b[U][4];
+      Raw4 ra[U], rb[U];
       int dst[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -538,13 +540,18 @@ __device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* 
         const int64_t row_off = (int64_t)m * p.ld_x;
         const int lim = on ? p.K : 0;
         if (PACKED) {
-          load4_as_float(p.x, p.x_dtype, row_off, col + 4 * c, lim, vec_ok, a[u]);
-          load4_as_float(p.x, p.x_dtype, row_off, col + 64 + 4 * c, lim, vec_ok, b[u]);
+          ra[u] = load4_raw(p.x, p.x_dtype, row_off, col + 4 * c, lim, vec_ok);
+          rb[u] = load4_raw(p.x, p.x_dtype, row_off, col + 64 + 4 * c, lim, vec_ok);
         } else {
-          load4_as_float(p.x, p.x_dtype, row_off, col + 8 * c, lim, vec_ok, a[u]);
-          load4_as_float(p.x, p.x_dtype, row_off, col + 8 * c + 4, lim, vec_ok, b[u]);
+          ra[u] = load4_raw(p.x, p.x_dtype, row_off, col + 8 * c, lim, vec_ok);
+          rb[u] = load4_raw(p.x, p.x_dtype, row_off, col + 8 * c + 4, lim, vec_ok);
         }
         dst[u] = on ? sl * slot_bytes + m * kXRowBytes + ((c & 3) * 4 + (c >> 2)) * 16 : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        cvt4(ra[u], p.x_dtype, a[u]);
+        cvt4(rb[u], p.x_dtype, b[u]);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -639,6 +646,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   const bool vec_ok = (p.ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
   const int items0 = cnt0 * p.batch;
   float xv[4];
+  Raw4 xraw = {{0u, 0u, 0u, 0u}};
   int x_sl = 0, x_m = 0;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (p.x_kind == PE_X_RAW) {
@@ -646,7 +654,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
     x_sl = on ? w / p.batch : 0;
     x_m = on ? w - x_sl * p.batch : 0;
     const int qq = Q0 + x_sl;
-    load4_as_float(p.x, p.x_dtype, (int64_t)x_m * p.ld_x, (qq % p.nb) * kBlock + lane * 4, on ? p.in_f : 0, vec_ok, xv);
+    xraw = load4_raw(p.x, p.x_dtype, (int64_t)x_m * p.ld_x, (qq % p.nb) * kBlock + lane * 4, on ? p.in_f : 0, vec_ok);
   }
 
   // ---- shared memory: [table 32 KB][activation slots][norms][code ring 16 x 8 KB]
@@ -717,6 +725,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
   PE_STAMP(2);
   if (p.x_kind == PE_X_RAW) {
     if (w < items0) {
+      cvt4(xraw, p.x_dtype, xv);
       warp_fwht128(xv, lane);
       place_block<PACKED>(xs + x_sl * slot_bytes + x_m * kXRowBytes, xv, lane);
     }

@@ -220,14 +220,17 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_rows_kernel(const RowArgs
     constexpr int U = 6;
     for (int base = w; base < jobs; base += kRowWarps * U) {
       float v[U][4];
+      Raw4 raw4[U];  // loads first, conversions after: one memory round trip per group
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int job = base + u * kRowWarps;
         const bool on = job < jobs;
         const int m = (NBATCH > 1 && job >= p.nb) ? 1 : 0;
         const int b = job - m * p.nb;
-        load4_as_float(p.x, p.x_dtype, (int64_t)m * p.ld_x, (on ? b : 0) * kBlock + lane * 4, on ? limit : 0, vec_ok, v[u]);
+        raw4[u] = load4_raw(p.x, p.x_dtype, (int64_t)m * p.ld_x, (on ? b : 0) * kBlock + lane * 4, on ? limit : 0, vec_ok);
       }
+#pragma unroll
+      for (int u = 0; u < U; ++u) cvt4(raw4[u], p.x_dtype, v[u]);
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int job = base + u * kRowWarps;
@@ -331,13 +334,14 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_rows_kernel(const RowArgs
 //
 // With a single activation row the loop above is bound by shared-memory bandwidth: every
 // 512 bytes of codes drag 2 KB of staged activations through the same port as the ring
-// and the table.  Here an item is FOUR weight rows x 128 bytes (8 lanes x 16 B per row)
-// and warp w owns the 128-byte column chunks w, w+16, ... of the CTA's rows, so a lane
-// meets the same few activation slices over and over and keeps them in registers (16
-// fp16 pairs per chunk, at most CPW chunks).  The price is a reduction per item -- three
-// shuffles over the 8 lanes of a row, once per row group and warp -- and a sum over the
-// 16 warps' column partials through shared memory, in warp order (bit-reproducible),
-// after every pass of 256 rows.  Each warp rotates only the blocks it owns.
+// and the table.  Here an item is EIGHT weight rows x 128 bytes (8 lanes x 16 B per row,
+// two rows per lane) and warp w owns the 128-byte column chunks w, w+16, ... of the CTA's
+// rows, so a lane meets the same few activation slices over and over and keeps them in
+// registers (16 fp16 pairs per chunk, at most CPW chunks), and the two rows of a lane give
+// the scheduler two independent dependency chains.  The price is a reduction per row
+// group -- three shuffles over the 8 lanes of a row -- and a sum over the 16 warps' column
+// partials through shared memory, in warp order (bit-reproducible), after every pass of
+// 256 rows.  Each warp rotates only the blocks it owns.
 constexpr int kPassRows = 256;
 constexpr int kPartStride = kRowWarps + 1;  // floats per row in the partial array (bank spread)
 
@@ -355,19 +359,45 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
+constexpr int kColStage = 2 * kItemBytes + 32;  // two 4-row sub-items + the norms of 8 rows
+
+// dot product of one lane's 16 bytes of codes with its activation registers
+template <bool PACKED, bool REGTAB, int NX>
+__device__ __forceinline__ float reg_dot(const uint4& q, uint32_t lane_base, const RegTable& tb, const uint32_t (&x)[NX]) {
+  uint32_t a[4][4];
+  decode_word<PACKED, REGTAB>(q.x, lane_base, tb, a[0]);
+  decode_word<PACKED, REGTAB>(q.y, lane_base, tb, a[1]);
+  decode_word<PACKED, REGTAB>(q.z, lane_base, tb, a[2]);
+  decode_word<PACKED, REGTAB>(q.w, lane_base, tb, a[3]);
+  uint32_t c0, c1, c2, c3;
+  if (PACKED) {
+    c0 = hmul2_u(a[0][0], x[0]); c1 = hmul2_u(a[1][0], x[4]); c2 = hmul2_u(a[2][0], x[8]); c3 = hmul2_u(a[3][0], x[12]);
+#pragma unroll
+    for (int i = 1; i < 4; ++i) {
+      c0 = hfma2_u(a[0][i], x[i], c0); c1 = hfma2_u(a[1][i], x[4 + i], c1);
+      c2 = hfma2_u(a[2][i], x[8 + i], c2); c3 = hfma2_u(a[3][i], x[12 + i], c3);
+    }
+  } else {
+    c0 = hmul2_u(a[0][0], x[0]); c1 = hmul2_u(a[1][0], x[2]); c2 = hmul2_u(a[2][0], x[4]); c3 = hmul2_u(a[3][0], x[6]);
+    c0 = hfma2_u(a[0][1], x[1], c0); c1 = hfma2_u(a[1][1], x[3], c1);
+    c2 = hfma2_u(a[2][1], x[5], c2); c3 = hfma2_u(a[3][1], x[7], c3);
+  }
+  return h2sum(hadd2_u(hadd2_u(c0, c1), hadd2_u(c2, c3)));
+}
+
 template <bool PACKED, bool REGTAB, int CPW, int DEPTH>
 __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs p) {
   static_assert(DEPTH % CPW == 0, "the ring holds whole row groups");
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-  const int rs = lane >> 3, pc = lane & 7;  // row of the group, 16-byte piece of the chunk
+  const int rs = lane >> 3, pc = lane & 7;  // row of the sub-item, 16-byte piece of the chunk
   const int G = gridDim.x, cta = blockIdx.x;
   constexpr int kXPerChunk = PACKED ? 16 : 8;  // fp16 pairs a lane keeps per chunk
-  constexpr int kRgDepth = DEPTH / CPW;        // row groups in flight per warp
+  constexpr int kRgDepth = DEPTH / CPW;        // row groups (8 rows) in flight per warp
   constexpr int kNormStep = PACKED ? 64 : 32;  // norm bytes between this warp's chunks
 
   const int r_beg = (int)((long long)p.N * cta / G), r_end = (int)((long long)p.N * (cta + 1) / G);
-  const int n_rg = (r_end - r_beg + 3) >> 2;
+  const int n_rg = (r_end - r_beg + 7) >> 3;
   int cnt = (p.n_chunks - w + kRowWarps - 1) / kRowWarps;  // chunks w, w+16, ... of this warp
   cnt = cnt < 0 ? 0 : (cnt > CPW ? CPW : cnt);
 
@@ -382,44 +412,48 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
   uint8_t* lut_g = smem;
   uint8_t* xw = smem + (REGTAB ? 0 : kLutBytes) + (size_t)w * (CPW * 512);
   float* part = reinterpret_cast<float*>(smem + (REGTAB ? 0 : kLutBytes) + (size_t)kRowWarps * CPW * 512);
-  uint8_t* ring_g = reinterpret_cast<uint8_t*>(part) + kPassRows * kPartStride * 4 + (size_t)w * (DEPTH * kRowStage);
-  const uint32_t st_base = smem_u32(ring_g), st_end = st_base + DEPTH * kRowStage;
+  uint8_t* ring_g = reinterpret_cast<uint8_t*>(part) + kPassRows * kPartStride * 4 + (size_t)w * (DEPTH * kColStage);
+  const uint32_t st_base = smem_u32(ring_g), st_end = st_base + DEPTH * kColStage;
 
-  // ---- code stream.  The ring slot of item (row group rg, chunk slot j) is
-  // (rg % kRgDepth) * CPW + j, so the refill issued after item (rg, j) is item
+  // ---- code stream.  An item is 8 weight rows x 128 bytes: lane (rs, pc) copies its 16
+  // bytes of rows rs and rs + 4 of the group.  The ring slot of item (row group rg, chunk
+  // slot j) is (rg % kRgDepth) * CPW + j, so the refill issued after item (rg, j) is item
   // (rg + kRgDepth, j): same slot, same j, and the source is a running pointer plus a
   // compile-time offset.  One copy group per slot, empty for slots the warp does not
-  // have, so the group count the math waits on is a constant.  Rows past the end of
-  // the matrix are not fetched (their sums are never stored).
+  // have, so the group count the math waits on is a constant.  Rows past the end of the
+  // matrix are not fetched (their sums are never stored).
   const uint8_t* cptr_f = p.codes + (int64_t)(r_beg + rs) * p.ld_codes + (size_t)w * 128 + pc * 16;
-  const uint8_t* nptr_f = p.norms + (int64_t)(r_beg + (lane & 3)) * p.ld_norms + (PACKED ? (size_t)w * 4 : (size_t)(w & ~1) * 2);
-  const int64_t cstep = 4 * p.ld_codes, nstep = 4 * p.ld_norms;
+  const uint8_t* nptr_f = p.norms + (int64_t)(r_beg + (lane & 7)) * p.ld_norms + (PACKED ? (size_t)w * 4 : (size_t)(w & ~1) * 2);
+  const int64_t chalf = 4 * p.ld_codes, cstep = 8 * p.ld_codes, nstep = 8 * p.ld_norms;
   int rg_f = 0;
-  bool row_ok = r_beg + rs < p.N, nrow_ok = lane < 4 && r_beg + lane < p.N;
-  auto fetch_group = [&](uint32_t st_rg) {  // all chunk slots of row group rg_f
-#pragma unroll
-    for (int j = 0; j < CPW; ++j) {
-      if (j < cnt && rg_f < n_rg) {
-        if (row_ok) cp_async16(st_rg + j * kRowStage + lane * 16, cptr_f + j * 2048);
-        if (nrow_ok) cp_async4(st_rg + j * kRowStage + kItemBytes + lane * 4, nptr_f + j * kNormStep);
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
+  bool ok0 = r_beg + rs < p.N, ok1 = r_beg + 4 + rs < p.N, nok = lane < 8 && r_beg + lane < p.N;
+  const uint32_t q_off = lane * 16;
+  auto fetch_item = [&](uint32_t st, int j) {
+    if (j < cnt && rg_f < n_rg) {
+      if (ok0) cp_async16(st + q_off, cptr_f + j * 2048);
+      if (ok1) cp_async16(st + kItemBytes + q_off, cptr_f + chalf + j * 2048);
+      if (nok) cp_async4(st + 2 * kItemBytes + lane * 4, nptr_f + j * kNormStep);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
   auto advance_fetch = [&]() {
     ++rg_f;
     cptr_f += cstep;
     nptr_f += nstep;
-    row_ok = r_beg + 4 * rg_f + rs < p.N;
-    nrow_ok = lane < 4 && r_beg + 4 * rg_f + lane < p.N;
+    const int r0 = r_beg + 8 * rg_f;
+    ok0 = r0 + rs < p.N;
+    ok1 = r0 + 4 + rs < p.N;
+    nok = lane < 8 && r0 + lane < p.N;
   };
 #pragma unroll
   for (int d = 0; d < kRgDepth; ++d) {
-    fetch_group(st_base + d * (CPW * kRowStage));
+#pragma unroll
+    for (int j = 0; j < CPW; ++j) fetch_item(st_base + (d * CPW + j) * kColStage, j);
     advance_fetch();
   }
 
-  // ---- centroid table
+
+  // ---- centroid table (built before the dependency wait: it needs nothing from the previous kernel)
   RegTable tb = {0, 0, 0, 0};
   if (PACKED && REGTAB) {
 #pragma unroll
@@ -451,23 +485,21 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
   {
     const bool raw = p.x_kind == PE_X_RAW;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
-    const bool fast = vec_ok && p.x_dtype == PE_F16;
     const int limit = raw ? p.in_f : p.K;
     constexpr int BPC = PACKED ? 2 : 1;  // quantization blocks per chunk
     float v[CPW * BPC][4];
+    // All loads are issued before any of them is used: the issue order is the program
+    // order, so a conversion placed right behind its load would make every load wait for
+    // the one before it (one memory round trip per block instead of one in total).
+    Raw4 raw4[CPW * BPC];
 #pragma unroll
     for (int u = 0; u < CPW * BPC; ++u) {
       const bool on = u / BPC < cnt;
       const int col = (on ? (w + 16 * (u / BPC)) * BPC + (u % BPC) : 0) * kBlock + lane * 4;
-      if (fast && on && col + 4 <= limit) {  // the common case inline: four fp16 values, one 8-byte load
-        uint2 h;
-        asm volatile("ld.global.v2.u32 {%0,%1}, [%2];" : "=r"(h.x), "=r"(h.y) : "l"(reinterpret_cast<const __half*>(p.x) + col));
-        const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h.x)), f1 = __half22float2(*reinterpret_cast<__half2*>(&h.y));
-        v[u][0] = f0.x; v[u][1] = f0.y; v[u][2] = f1.x; v[u][3] = f1.y;
-      } else {
-        load4_as_float(p.x, p.x_dtype, 0, col, on ? limit : 0, vec_ok, v[u]);
-      }
+      raw4[u] = load4_raw(p.x, p.x_dtype, 0, col, on ? limit : 0, vec_ok);
     }
+#pragma unroll
+    for (int u = 0; u < CPW * BPC; ++u) cvt4(raw4[u], p.x_dtype, v[u]);
 #pragma unroll
     for (int u = 0; u < CPW * BPC; ++u) {
       if (u / BPC < cnt) {  // warp-uniform
@@ -497,69 +529,53 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
       }
     }
   }
-
   if (!REGTAB) __syncthreads();  // the shared table has entries from every warp
 
   // ---- the item line, in passes of kPassRows rows
   const int n_warps_used = p.n_chunks < kRowWarps ? p.n_chunks : kRowWarps;
-  const uint32_t q_off = lane * 16;
-  const uint32_t norm_off = kItemBytes + rs * 4 + (PACKED ? (pc >> 2) * 2 : (w & 1) * 2);
+  const uint32_t norm_off = 2 * kItemBytes + rs * 4 + (PACKED ? (pc >> 2) * 2 : (w & 1) * 2);
   uint32_t st_rg = st_base;
-  for (int rg0 = 0; rg0 < n_rg; rg0 += kPassRows / 4) {
-    const int rg1 = n_rg < rg0 + kPassRows / 4 ? n_rg : rg0 + kPassRows / 4;
+  for (int rg0 = 0; rg0 < n_rg; rg0 += kPassRows / 8) {
+    const int rg1 = n_rg < rg0 + kPassRows / 8 ? n_rg : rg0 + kPassRows / 8;
     if (cnt > 0) {
       uint32_t part_s = smem_u32(part) + (rs * kPartStride + w) * 4;
       for (int rg = rg0; rg < rg1; ++rg) {
-        float acc = 0.f;
+        float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
         for (int j = 0; j < CPW; ++j) {
           asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+          const uint32_t st = st_rg + j * kColStage;
           if (j < cnt) {
-            const uint32_t st = st_rg + j * kRowStage;
-            const uint4 q = lds128(st + q_off);
-            unsigned short nh;
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh) : "r"(st + norm_off));
-            uint32_t a[4][4];
-            decode_word<PACKED, REGTAB>(q.x, lane_base, tb, a[0]);
-            decode_word<PACKED, REGTAB>(q.y, lane_base, tb, a[1]);
-            decode_word<PACKED, REGTAB>(q.z, lane_base, tb, a[2]);
-            decode_word<PACKED, REGTAB>(q.w, lane_base, tb, a[3]);
-            uint32_t c0, c1, c2, c3;
-            if (PACKED) {
-              c0 = hmul2_u(a[0][0], xr[j][0]); c1 = hmul2_u(a[1][0], xr[j][4]); c2 = hmul2_u(a[2][0], xr[j][8]); c3 = hmul2_u(a[3][0], xr[j][12]);
-#pragma unroll
-              for (int i = 1; i < 4; ++i) {
-                c0 = hfma2_u(a[0][i], xr[j][i], c0); c1 = hfma2_u(a[1][i], xr[j][4 + i], c1);
-                c2 = hfma2_u(a[2][i], xr[j][8 + i], c2); c3 = hfma2_u(a[3][i], xr[j][12 + i], c3);
-              }
-            } else {
-              c0 = hmul2_u(a[0][0], xr[j][0]); c1 = hmul2_u(a[1][0], xr[j][2]); c2 = hmul2_u(a[2][0], xr[j][4]); c3 = hmul2_u(a[3][0], xr[j][6]);
-              c0 = hfma2_u(a[0][1], xr[j][1], c0); c1 = hfma2_u(a[1][1], xr[j][3], c1);
-              c2 = hfma2_u(a[2][1], xr[j][5], c2); c3 = hfma2_u(a[3][1], xr[j][7], c3);
-            }
-            const float s = h2sum(hadd2_u(c0, c1)) + h2sum(hadd2_u(c2, c3));
-            acc = fmaf(__half2float(__ushort_as_half(nh)), s, acc);
+            const uint4 q0 = lds128(st + q_off), q1 = lds128(st + kItemBytes + q_off);
+            unsigned short nh0, nh1;
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh0) : "r"(st + norm_off));
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh1) : "r"(st + norm_off + 16));
+            const float s0 = reg_dot<PACKED, REGTAB>(q0, lane_base, tb, xr[j]);
+            const float s1 = reg_dot<PACKED, REGTAB>(q1, lane_base, tb, xr[j]);
+            acc0 = fmaf(__half2float(__ushort_as_half(nh0)), s0, acc0);
+            acc1 = fmaf(__half2float(__ushort_as_half(nh1)), s1, acc1);
           }
           __syncwarp();  // every lane has read the slot before it is refilled
-          if (j < cnt && rg_f < n_rg) {
-            if (row_ok) cp_async16(st_rg + j * kRowStage + q_off, cptr_f + j * 2048);
-            if (nrow_ok) cp_async4(st_rg + j * kRowStage + kItemBytes + lane * 4, nptr_f + j * kNormStep);
-          }
-          asm volatile("cp.async.commit_group;" ::: "memory");
+          fetch_item(st, j);
         }
         advance_fetch();
-        st_rg += CPW * kRowStage;
+        st_rg += CPW * kColStage;
         if (st_rg == st_end) st_rg = st_base;
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-        if (pc == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_s), "f"(acc) : "memory");
-        part_s += 4 * kPartStride * 4;
+#pragma unroll
+        for (int m = 1; m <= 4; m <<= 1) {
+          acc0 += __shfl_xor_sync(0xffffffffu, acc0, m);
+          acc1 += __shfl_xor_sync(0xffffffffu, acc1, m);
+        }
+        if (pc == 0) {
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_s), "f"(acc0) : "memory");
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_s + 4 * kPartStride * 4), "f"(acc1) : "memory");
+        }
+        part_s += 8 * kPartStride * 4;
       }
     }
     __syncthreads();
-    for (int r = tid; r < 4 * (rg1 - rg0); r += kRowThreads) {
-      const int row = r_beg + 4 * rg0 + r;
+    for (int r = tid; r < 8 * (rg1 - rg0); r += kRowThreads) {
+      const int row = r_beg + 8 * rg0 + r;
       if (row < r_end) {
         float s = 0.f;
         for (int ww = 0; ww < n_warps_used; ++ww) s += part[r * kPartStride + ww];
@@ -574,9 +590,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
 
 template <bool PACKED, bool REGTAB, int CPW>
 static int launch_cols(const ColArgs& a, int G, cudaStream_t st) {
-  constexpr int DEPTH = 12;
+  constexpr int DEPTH = CPW == 4 ? 8 : 6;  // items (1 KB of codes) in flight per warp
   const unsigned dyn_bytes = (REGTAB ? 0u : (unsigned)kLutBytes) + kRowWarps * CPW * 512u + kPassRows * kPartStride * 4u +
-                             kRowWarps * DEPTH * (unsigned)kRowStage;
+                             kRowWarps * DEPTH * (unsigned)kColStage;
   auto kfn = gemv_cols_kernel<PACKED, REGTAB, CPW, DEPTH>;
   static thread_local bool configured[16] = {false};
   int dev = 0;
@@ -620,8 +636,8 @@ static int gemv_cols_try(const void* codes, int packed, int64_t ld_codes, const 
   const int n_chunks = (int)(row_bytes / 128);
   const int cpw = (n_chunks + kRowWarps - 1) / kRowWarps;
   if (cpw > 4) return 1;
-  const int G = out_f / 8 < sms ? out_f / 8 : sms;  // at least two row groups per CTA
-  if (G < 1 || (long long)out_f * n_chunks < (long long)G * kRowWarps * 16) return 1;
+  const int G = out_f / 16 < sms ? out_f / 16 : sms;  // at least two row groups per CTA
+  if (G < 1 || (long long)out_f * n_chunks < (long long)G * kRowWarps * 16) return 1;  // < 2 items per warp
   ColArgs a;
   a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
   a.norms = static_cast<const uint8_t*>(norms); a.ld_norms = ld_norms * 2;

@@ -3,8 +3,10 @@
 This is measurement scaffolding around the quantized-linear path, not a model zoo: a
 9B-class decoder (hidden 4096, 32 query / 8 KV heads of 128, intermediate 12288, 36
 layers, vocabulary 151936) whose every projection, the embedding and the LM head run
-through the native kernels.  RMSNorm, rotary embedding, attention over the KV cache and
-SiLU are plain torch ops (they are not the path under test).
+through the native kernels.  Residual add + RMSNorm, rotary embedding + KV-cache write and
+SiLU * up are single native launches (``decode_ops``); attention over the KV cache is torch's
+SDPA (not the path under test).  ``rms_norm`` and ``rope`` below are the op-by-op torch
+formulations the fused ops are tested against.
 
 Tensor parallelism follows vLLM's layout, which is also the only place where ranks
 exchange data: q/k/v and gate/up are column parallel (heads / intermediate split), o and
@@ -22,6 +24,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
+from .decode_ops import add_rmsnorm, rope_cache, silu_mul
 from .kernels import quant_embedding, quant_matmul, retile
 from .packing import pack_codes_half_block
 from .utils import get_centroids, get_ct_scaled
@@ -133,35 +136,23 @@ class QuantDecoder:
         cfg, d = self.cfg, self.cfg.head_dim
         b, t = ids.shape
         x = quant_embedding(self.embed.codes, self.embed.packed, self.embed.norms, self.embed.ct, ids, cfg.hidden)
-        if torch.is_tensor(pos0):
-            pos = pos0 + torch.arange(t, device=self.dev)
-        else:
-            pos = torch.arange(pos0, pos0 + t, device=self.dev)
+        x = x.view(b * t, cfg.hidden)  # residual stream, updated in place by add_rmsnorm
+        delta = None                   # output of the previous layer's down projection, not yet added
         for li, L in enumerate(self.layers):
-            h = rms_norm(x, L["ln1"], cfg.rms_eps)
-            qkv = L["qkv"](h.reshape(b * t, cfg.hidden)).view(b, t, self.hq + 2 * self.hkv, d)
-            q = rope(qkv[:, :, : self.hq].transpose(1, 2), pos, cfg.rope_theta)
-            k = rope(qkv[:, :, self.hq: self.hq + self.hkv].transpose(1, 2), pos, cfg.rope_theta)
-            v = qkv[:, :, self.hq + self.hkv:].transpose(1, 2)
-            if torch.is_tensor(pos0):  # decode: static shapes, positions from a device scalar
-                idx = pos.view(1, 1, t, 1).expand(b, self.hkv, t, d)
-                self.k_cache[li].scatter_(2, idx, k)
-                self.v_cache[li].scatter_(2, idx, v)
+            h = add_rmsnorm(x, delta, L["ln1"], cfg.rms_eps)
+            qkv = L["qkv"](h)
+            q = rope_cache(qkv, pos0, self.k_cache[li], self.v_cache[li], b, t, self.hq, self.hkv, d, cfg.rope_theta)
+            if torch.is_tensor(pos0):  # decode: static shapes, the mask hides positions beyond the current one
                 att = F.scaled_dot_product_attention(q, self.k_cache[li], self.v_cache[li], attn_mask=mask, enable_gqa=True)
             else:
-                self.k_cache[li][:, :, pos0:pos0 + t] = k
-                self.v_cache[li][:, :, pos0:pos0 + t] = v
                 att = F.scaled_dot_product_attention(q, self.k_cache[li][:, :, : pos0 + t], self.v_cache[li][:, :, : pos0 + t],
                                                      is_causal=(pos0 == 0 and t > 1), enable_gqa=True)
             att = att.transpose(1, 2).reshape(b * t, self.hq * d)
-            o = self._all_reduce(L["o"](att, torch.float32)).to(torch.float16).view(b, t, cfg.hidden)
-            x = x + o
-            h = rms_norm(x, L["ln2"], cfg.rms_eps)
-            gu = L["gate_up"](h.reshape(b * t, cfg.hidden))
-            act = F.silu(gu[:, : self.inter]) * gu[:, self.inter:]
-            dn = self._all_reduce(L["down"](act, torch.float32)).to(torch.float16).view(b, t, cfg.hidden)
-            x = x + dn
-        h = rms_norm(x[:, -1], self.final_ln, cfg.rms_eps)
+            o = self._all_reduce(L["o"](att, torch.float32))
+            h = add_rmsnorm(x, o, L["ln2"], cfg.rms_eps)
+            act = silu_mul(L["gate_up"](h), self.inter)
+            delta = self._all_reduce(L["down"](act, torch.float32))
+        h = add_rmsnorm(x, delta, self.final_ln, cfg.rms_eps).view(b, t, cfg.hidden)[:, -1]
         logits = self.head(h, torch.float32)                      # (B, vocab / tp)
         val, idx = logits.max(dim=-1)
         if self.tp > 1:

@@ -1,0 +1,65 @@
+"""The decoder-layer glue ops (residual add + RMSNorm, rotary + KV-cache write, SiLU * up)
+against their op-by-op torch formulations (decoder.rms_norm / decoder.rope / F.silu)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (5, 4096), (3, 512), (2, 12288), (7, 16384), (4, 2688)])
+@pytest.mark.parametrize("delta_kind", ["none", "f16", "f32"])
+def test_add_rmsnorm(rows, hidden, delta_kind):
+    from polarengine_vllm_b200.decode_ops import add_rmsnorm
+    from polarengine_vllm_b200.decoder import rms_norm
+    g = torch.Generator(device="cuda").manual_seed(rows + hidden)
+    x = torch.randn(rows, hidden, device="cuda", generator=g).half()
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=g)).half()
+    delta = None
+    if delta_kind != "none":
+        delta = 0.5 * torch.randn(rows, hidden, device="cuda", generator=g)
+        delta = delta.half() if delta_kind == "f16" else delta
+    x_ref = x.clone() if delta is None else x + delta.half()
+    ref = rms_norm(x_ref, w, 1e-6)
+    xs = x.clone()
+    out = add_rmsnorm(xs, delta, w, 1e-6)
+    assert torch.equal(xs, x_ref)  # the residual stream is updated bit-exactly
+    assert out.dtype == torch.float16 and out.shape == x.shape
+    # the sum of squares is reduced in another order: results may differ by one fp16 rounding
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-3, atol=1e-3)
+    assert (out != ref).float().mean() < 0.02
+
+
+@pytest.mark.parametrize("batch,t,pos0,on_device", [(1, 1, 37, True), (2, 1, 5, True), (2, 20, 0, False), (1, 33, 7, False)])
+def test_rope_cache(batch, t, pos0, on_device):
+    from polarengine_vllm_b200.decode_ops import rope_cache
+    from polarengine_vllm_b200.decoder import rope
+    hq, hkv, d, max_len, theta = 4, 2, 128, 64, 1e6
+    g = torch.Generator(device="cuda").manual_seed(t + pos0)
+    qkv = torch.randn(batch * t, (hq + 2 * hkv) * d, device="cuda", generator=g).half()
+    kc = torch.zeros(batch, hkv, max_len, d, dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    p = torch.tensor(pos0, device="cuda") if on_device else pos0
+    q = rope_cache(qkv, p, kc, vc, batch, t, hq, hkv, d, theta)
+    v4 = qkv.view(batch, t, hq + 2 * hkv, d)
+    pos = torch.arange(pos0, pos0 + t, device="cuda")
+    q_ref = rope(v4[:, :, :hq].transpose(1, 2), pos, theta)
+    k_ref = rope(v4[:, :, hq:hq + hkv].transpose(1, 2), pos, theta)
+    v_ref = v4[:, :, hq + hkv:].transpose(1, 2)
+    assert q.shape == (batch, hq, t, d)
+    assert torch.allclose(q.float(), q_ref.float(), rtol=2e-3, atol=2e-3)
+    assert torch.allclose(kc[:, :, pos0:pos0 + t].float(), k_ref.float(), rtol=2e-3, atol=2e-3)
+    assert torch.equal(vc[:, :, pos0:pos0 + t], v_ref)
+    # nothing outside the written positions is touched
+    assert float(kc[:, :, :pos0].abs().max() if pos0 else 0) == 0 and float(kc[:, :, pos0 + t:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("rows,inter", [(1, 12288), (3, 1024), (64, 1856)])
+def test_silu_mul(rows, inter):
+    from polarengine_vllm_b200.decode_ops import silu_mul
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    gu = (2 * torch.randn(rows, 2 * inter, device="cuda", generator=g)).half()
+    ref = F.silu(gu[:, :inter]) * gu[:, inter:]
+    out = silu_mul(gu, inter)
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-3, atol=1e-4)
+    assert (out != ref).float().mean() < 0.02
