@@ -199,7 +199,7 @@ def model_decode(a, dev, rank, world):
     pos = torch.tensor(a.prompt, device=dev, dtype=torch.int64)
     stream = torch.cuda.Stream(dev)
     def step():
-        out = model.forward(ids_buf, pos, model.decode_mask(pos))
+        out = model.forward(ids_buf, pos)
         ids_buf.copy_(out.view(b, 1))
         pos.add_(1)
     with torch.cuda.stream(stream):
@@ -253,7 +253,7 @@ def model_decode(a, dev, rank, world):
                        "launch": "eager" if a.no_graph else "cuda graph"},
             "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
             "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
-            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (4 * a.layers + 2)}))
+            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (8 * a.layers + 3)}))
     finish(world)
 
 
@@ -492,7 +492,7 @@ def main():
                        "launch": "eager" if a.no_graph else "cuda graph"},
             "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
             "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
-            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (4 * a.layers + 2)}))
+            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (8 * a.layers + 3)}))
     finish(world)
 
 

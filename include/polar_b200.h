@@ -92,12 +92,18 @@ int pe_embedding(const void* codes, int packed, int64_t ld_codes, const void* no
  *   key heads (frequencies theta^(-2j/d)); queries go to q_out (batch, hq, t, head_dim),
  *   rotated keys and the values into the caches (batch, hkv, max_len, head_dim) at their
  *   positions (positions outside [0, max_len) are dropped).
- * pe_silu_mul: out[r, i] = fp16(silu(gate_up[r, i])) * gate_up[r, inter + i]. */
+ * pe_silu_mul: out[r, i] = fp16(silu(gate_up[r, i])) * gate_up[r, inter + i].
+ * pe_decode_attention: one new token per sequence.  q (batch, hq, head_dim), caches as
+ *   above holding positions 0 .. pos (pos = *pos_dev or pos_host, the token just written);
+ *   out (batch, hq * head_dim) = softmax(q K^T / sqrt(head_dim)) V per query head, query head
+ *   i reading kv head i / (hq / hkv).  head_dim = 128, hq / hkv in {1, 2, 4, 8}. */
 int pe_add_rmsnorm(void* x, const void* delta, int delta_dtype, const void* weight, void* out, int rows, int hidden,
                    float eps, void* stream);
 int pe_rope_cache(const void* qkv, int64_t ld_qkv, const int64_t* pos_dev, int64_t pos_host, void* q_out, void* k_cache,
                   void* v_cache, int batch, int t, int hq, int hkv, int head_dim, int max_len, float theta, void* stream);
 int pe_silu_mul(const void* gate_up, int64_t ld_gu, void* out, int64_t ld_out, int rows, int inter, void* stream);
+int pe_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos_dev, int64_t pos_host,
+                        void* out, int batch, int hq, int hkv, int head_dim, int max_len, void* stream);
 
 /* ---- nibble packing ---------------------------------------------------------
  * int8 codes (out_f, in_f_padded) -> uint8 (out_f, in_f_padded/2), byte i of each
@@ -132,6 +138,29 @@ int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, 
             const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
             int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- grouped decode-size matmul: the experts of a mixture layer -----------------
+ * One launch over a stack of matrices of one shape (expert e at codes + e * codes_stride
+ * bytes, norms + e * norms_stride halves), each against its own 1..16 activation rows.
+ * `problems` is a DEVICE array of max_problems int32 quadruples (expert, first, rows, 0):
+ * problem i multiplies rows first .. first + rows - 1 of the row list -- row x_rows[j] of
+ * x when x_rows is not NULL (a gather by token id), else row j of x -- with expert
+ * `expert` and writes rows first .. of y.  Entries with rows <= 0 are skipped, so the host
+ * sizes the launch for the worst case and never reads the routing back.  An expert with
+ * more than 16 rows takes several problems.  No bias.  The scratch
+ * (pe_gemv_grouped_workspace_bytes; 0 = too many problems) is its own buffer, not the one
+ * of pe_gemv: its first 4 MiB must be zero before the first use and are left zero, so
+ * calls of any shapes can share it in stream order.
+ * Replaces the per-expert loop of the reference's MoE layer (nemotron_offload.py:190-226:
+ * for each selected expert, gate/up projection, activation, down projection) with two
+ * grouped launches; the reference's vLLM path has no quantized expert arithmetic
+ * (moe_method.py:18-98). */
+size_t pe_gemv_grouped_workspace_bytes(int max_problems, int out_f, int in_f_padded);
+int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, int64_t codes_stride, const void* norms,
+                    int64_t ld_norms, int64_t norms_stride, const float* ct_scaled, int n_levels, const void* x,
+                    int x_kind, int x_dtype, int64_t ld_x, int in_f, const int32_t* x_rows, void* y, int y_dtype,
+                    int64_t ld_y, const int32_t* problems, int max_problems, int out_f, int in_f_padded,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- tiled weight layout for the decode kernel -----------------------------------
  * pe_retile rewrites a layer (codes + norms, the reference's row-major layouts) into the

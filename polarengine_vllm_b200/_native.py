@@ -33,6 +33,9 @@ SIGNATURES = {
     "pe_gemv_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                      _vp, _sz, _vp]),
+    "pe_gemv_grouped_workspace_bytes": (_sz, [_i, _i, _i]),
+    "pe_gemv_grouped": (_i, [_vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _vp, _i, _i64, _vp,
+                            _i, _i, _i, _vp, _sz, _vp]),
     "pe_retile_bytes": (_sz, [_i, _i64, _i64]),
     "pe_retile": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i64, _i64, _vp]),
     "pe_gemv_tiled": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i, _vp, _sz, _vp]),
@@ -42,6 +45,7 @@ SIGNATURES = {
     "pe_add_rmsnorm": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, ctypes.c_float, _vp]),
     "pe_rope_cache": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, ctypes.c_float, _vp]),
     "pe_silu_mul": (_i, [_vp, _i64, _vp, _i64, _i, _i, _vp]),
+    "pe_decode_attention": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp]),
     "pe_gemv_noalloc_max_bytes": (_sz, []),
     "pe_gemv_noalloc": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                              _vp]),
@@ -117,6 +121,19 @@ def gemv_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
         _scratch[key] = buf
+    return buf
+
+
+_grouped_scratch = {}
+
+
+def grouped_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch of the grouped launches (its own buffer: the counter zone differs from pe_gemv's)."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _grouped_scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
+        _grouped_scratch[key] = buf
     return buf
 
 

@@ -146,6 +146,149 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* gu, int64_t
   *reinterpret_cast<uint4*>(out + r * ld_out + col) = o;
 }
 
+
+// Single-query attention over the KV cache for one decode step (grouped-query form).
+// One CTA per (kv head, sequence): its G = hq / hkv query heads share every K and V row.
+//  1. scores: thread = cache position (strided); the 16 16-byte pieces of its K row are
+//     requested together (one memory round trip per position), then the full 128-wide dot
+//     per query head with the queries broadcast from shared memory;
+//  2. softmax per query head by one warp each (max, exp, sum);
+//  3. output: thread = (position stride 16, 16-byte piece of the V row), eight rows in
+//     flight per thread; the 16 position groups meet in shared memory.
+constexpr int kAttThreads = 256;
+constexpr int kAttMaxGroup = 8;
+
+template <int D, int G>
+__device__ __forceinline__ void attention_body(const __half* q, const __half* kb, const __half* vb, __half* out_row, float* att_smem,
+                                               int L, int max_len, float scale) {
+  static_assert(D == 128, "pieces and thread mapping are laid out for 128-wide heads");
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  float* qs = att_smem;                 // [G][D]
+  float* sc = qs + kAttMaxGroup * D;    // [G][max_len]
+  float* red = sc + G * max_len;        // [16 position groups][G][D]
+  for (int i = tid; i < G * D; i += kAttThreads) qs[i] = __half2float(q[i]) * scale;
+  __syncthreads();
+  for (int p = tid; p < L; p += kAttThreads) {
+    uint4 u[D / 8];
+    const uint4* row = reinterpret_cast<const uint4*>(kb + (int64_t)p * D);
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) u[c] = row[c];
+    float acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) acc[g] = 0.f;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      const __half2* h2 = reinterpret_cast<const __half2*>(&u[c]);
+      float kf[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h2[i]);
+        kf[2 * i] = f.x;
+        kf[2 * i + 1] = f.y;
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float4 qa = *reinterpret_cast<const float4*>(qs + g * D + c * 8);
+        const float4 qb = *reinterpret_cast<const float4*>(qs + g * D + c * 8 + 4);
+        acc[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x + kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) sc[g * max_len + p] = acc[g];
+  }
+  __syncthreads();
+  if (w < G) {  // softmax of head w
+    float* s = sc + w * max_len;
+    float m = -INFINITY;
+    for (int p = lane; p < L; p += 32) m = fmaxf(m, s[p]);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int p = lane; p < L; p += 32) {
+      const float e = __expf(s[p] - m);
+      s[p] = e;
+      sum += e;
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+    for (int p = lane; p < L; p += 32) s[p] *= inv;
+  }
+  __syncthreads();
+  {
+    const int ps = tid >> 4, piece = tid & 15;
+    float acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+    constexpr int U = 8;
+    for (int p0 = ps; p0 < L; p0 += 16 * U) {
+      uint4 u[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int p = p0 + 16 * j;
+        u[j] = p < L ? *reinterpret_cast<const uint4*>(vb + (int64_t)p * D + piece * 8) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int p = p0 + 16 * j;
+        if (p < L) {
+          const __half2* h2 = reinterpret_cast<const __half2*>(&u[j]);
+          float vf[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h2[i]);
+            vf[2 * i] = f.x;
+            vf[2 * i + 1] = f.y;
+          }
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float pr = sc[g * max_len + p];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] += pr * vf[i];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float* dst = red + (ps * G + g) * D + piece * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < G * D; i += kAttThreads) {
+    float s = 0.f;
+#pragma unroll
+    for (int gs = 0; gs < 16; ++gs) s += red[gs * G * D + i];
+    out_row[i] = __float2half_rn(s);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(const __half* q, const __half* k_cache, const __half* v_cache,
+                                                                        const int64_t* pos_dev, int64_t pos_host, __half* out,
+                                                                        int hq, int hkv, int max_len, float scale) {
+  extern __shared__ __align__(16) float att_smem[];
+  const int G = hq / hkv;
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int64_t len64 = (pos_dev ? *pos_dev : pos_host) + 1;  // the current token is already in the cache
+  const int L = (int)(len64 < 1 ? 1 : (len64 > max_len ? max_len : len64));
+  const __half* qp = q + ((int64_t)b * hq + (int64_t)kvh * G) * D;
+  const __half* kb = k_cache + ((int64_t)b * hkv + kvh) * (int64_t)max_len * D;
+  const __half* vb = v_cache + ((int64_t)b * hkv + kvh) * (int64_t)max_len * D;
+  __half* op = out + ((int64_t)b * hq + (int64_t)kvh * G) * D;
+  switch (G) {
+    case 1: attention_body<D, 1>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
+    case 2: attention_body<D, 2>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
+    case 4: attention_body<D, 4>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
+    case 8: attention_body<D, 8>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
+    default: break;
+  }
+}
+
 }  // namespace pe
 
 using namespace pe;
@@ -188,6 +331,31 @@ extern "C" int pe_silu_mul(const void* gate_up, int64_t ld_gu, void* out, int64_
   if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
   silu_mul_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(gate_up), ld_gu,
                                                                                  static_cast<__half*>(out), ld_out, inter, n_vec);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
+
+extern "C" int pe_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos_dev,
+                                   int64_t pos_host, void* out, int batch, int hq, int hkv, int head_dim, int max_len,
+                                   void* stream) {
+  if (!q || !k_cache || !v_cache || !out || batch < 1 || hq < 1 || hkv < 1 || max_len < 1) return PE_ERR_ARG;
+  if (head_dim != 128 || hq % hkv) return PE_ERR_SHAPE;
+  if (hq / hkv != 1 && hq / hkv != 2 && hq / hkv != 4 && hq / hkv != 8) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return PE_ERR_ALIGN;
+  const int G = hq / hkv;
+  const size_t smem = ((size_t)kAttMaxGroup * 128 + (size_t)G * max_len + (size_t)16 * G * 128) * sizeof(float);
+  if (smem > 200 * 1024 || batch > 65535) return PE_ERR_LIMIT;
+  auto kfn = decode_attention_kernel<128>;
+  static thread_local size_t configured[16] = {0};
+  int dev = 0;
+  PE_CUDA_TRY(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev >= 16 || configured[dev] < smem)) {
+    PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 16) configured[dev] = smem;
+  }
+  kfn<<<dim3((unsigned)hkv, (unsigned)batch), kAttThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos_dev, pos_host,
+      static_cast<__half*>(out), hq, hkv, max_len, 1.f / sqrtf((float)head_dim));
   PE_CUDA_TRY(cudaGetLastError());
   return PE_OK;
 }

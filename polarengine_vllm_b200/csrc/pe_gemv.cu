@@ -1,37 +1,41 @@
-// Decode-size quantized matmul (1..16 activation rows) for sm_100a.
+// Decode-size quantized matmul (1..16 activation rows) for sm_100a: the tile kernel.
 //
 //   y[m, r] = sum_blk norm[r, blk] * sum_k ct[code[r, blk, k]] * xt[m, blk, k]   (+ bias[r])
 //
-// The operand that costs anything is the code stream (0.5 or 1 byte per weight, read
-// once from HBM); everything else is arranged so that the SM never waits on it:
+// One and two activation rows over whole-row shapes go to the row-owner kernels in
+// pe_gemv_rows.cu (gemv_run tries them first); everything else runs here.  The operand
+// that costs anything is the code stream (0.5 or 1 byte per weight, read once from HBM):
 //
 //  * One persistent CTA per SM, 16 warps.  The unit of work is a "step": one 16-row
 //    tile of the weight matrix times one 128-wide quantization block (1 KB of nibble
 //    codes, 2 KB of byte codes).  Steps are numbered (row-tile-of-256, block, warp) and
 //    the number line is cut into equal contiguous ranges, one per CTA, so every SM
 //    streams the same number of bytes whatever the layer shape is.
-//  * Lane (g, t) of a warp streams 16 B of row g and 16 B of row g+8 per step with
-//    128-bit non-allocating loads, several steps ahead of the math (register ring).
+//  * Codes travel by 16-byte asynchronous copies into a lane-private shared-memory ring
+//    (8 KB per warp in flight), from the row-major arrays or from the tiled copy
+//    (pe_retile: the step's codes followed by its 16 block norms, contiguous).
 //  * Centroids are looked up in a shared-memory table that is replicated per lane
-//    (entry e of lane l lives at table + e*256 + l*4), so 32 lanes with 32 different
-//    codes never collide on a bank.  The address is formed by ONE byte-permute from the
-//    code word and a per-lane base, which is why the table sits on a 64 KB boundary.
+//    (entry e of lane l lives at table + e*128 + l*4), so 32 lanes with 32 different
+//    codes never collide on a bank; the address is a byte extract and a multiply-add.
 //    Nibble-packed layers use a 256-entry table indexed by the whole byte whose entry is
-//    the fp16 pair (ct[lo], ct[hi]) = two weights per lookup.
+//    the fp16 pair (ct[lo], ct[hi]) = two weights per lookup; layers with at most eight
+//    levels use a register table and byte permutes instead (no memory traffic).
 //  * The dot products run on the tensor cores (mma.sync m16n8k16, fp16 in, fp32 out):
 //    weights are the 16x16 A tile, up to 8 (or 2x8) activation rows are the B tile.
 //    The k index of the MMA is a free permutation, so a lookup result is used as it
 //    comes: for nibble layers the pair (k, k+64) of the half-block layout is one A
 //    register and the activations are staged in shared memory in the same pairing.
+//    One or two activation rows use fp16x2 FMAs instead (seven eighths of an MMA would be
+//    padding).
 //  * The block norm multiplies the 8-MMA partial sum of a block, not each weight.
 //  * Activations are staged per CTA into shared memory once: either already rotated
 //    (fp32, the reference's x_transformed) or raw fp16/bf16/fp32, in which case the
 //    zero-pad and the FWHT-128 happen in the staging warps (one launch per layer).
 //  * Split-K falls out of the range cut: a row tile whose blocks are spread over
-//    several CTAs gets one fp32 partial per CTA in scratch memory; the CTA that
-//    completes the tile (a counter per 16-row tile) sums the partials in CTA order,
-//    adds the bias, converts and stores.  No float atomics: results are bit-identical
-//    from run to run.  The counters return to zero, so the scratch is reusable.
+//    several CTAs gets one fp32 partial per CTA in scratch memory; the CTA that owns the
+//    tile's last step sums the partials in CTA order (bounded wait on a counter), adds
+//    the bias, converts and stores.  No float atomics: results are bit-identical from
+//    run to run.  The counters return to zero, so the scratch is reusable.
 #include "pe_gemv_decode.cuh"
 
 namespace pe {
@@ -57,7 +61,15 @@ struct GemvArgs {
   float* ws_part; unsigned* ws_cnt; int* ws_status;
   unsigned dyn_bytes;
   long long* prof;  // optional per-warp time stamps (developer builds with -DPE_PROFILE)
+  // grouped launch (blockIdx.y = problem): several matrices of one shape -- the experts of
+  // a mixture layer -- each against its own few activation rows
+  const int* x_rows;          // activation row m of the problem is row x_rows[m] of x (nullptr: row m)
+  const int4* grp;            // per problem: (matrix index, first row of its rows in the row list / output, rows, -)
+  int64_t grp_codes_stride, grp_norms_stride;  // bytes / halves between consecutive matrices
+  size_t grp_ws_stride, grp_cnt_bytes;         // partial block and counter block per problem
 };
+
+__device__ __forceinline__ int64_t x_row_of(const GemvArgs& p, int m) { return p.x_rows ? (int64_t)p.x_rows[m] : (int64_t)m; }
 
 #ifdef PE_PROFILE
 #define PE_STAMP(i) do { if (p.prof && lane == 0) p.prof[((size_t)blockIdx.x * kWarps + w) * 8 + (i)] = clock64(); } while (0)
@@ -509,7 +521,7 @@ __device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* 
         const bool on = item < items;
         sl[u] = on ? item / p.batch : 0;
         mm[u] = on ? item - sl[u] * p.batch : 0;
-        raw4[u] = load4_raw(p.x, p.x_dtype, (int64_t)mm[u] * p.ld_x, slot_blk[sl[u]] * kBlock + lane * 4, on ? p.in_f : 0, vec_ok);
+        raw4[u] = load4_raw(p.x, p.x_dtype, x_row_of(p, mm[u]) * p.ld_x, slot_blk[sl[u]] * kBlock + lane * 4, on ? p.in_f : 0, vec_ok);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) cvt4(raw4[u], p.x_dtype, v[u]);
@@ -537,7 +549,7 @@ __device__ __noinline__ void stage_x(const GemvArgs& p, uint8_t* xs, const int* 
         const int sm = on ? item >> 4 : 0;
         const int sl = sm / p.batch, m = sm - sl * p.batch;
         const int col = slot_blk[sl] * kBlock;
-        const int64_t row_off = (int64_t)m * p.ld_x;
+        const int64_t row_off = x_row_of(p, m) * p.ld_x;
         const int lim = on ? p.K : 0;
         if (PACKED) {
           ra[u] = load4_raw(p.x, p.x_dtype, row_off, col + 4 * c, lim, vec_ok);
@@ -593,10 +605,33 @@ __device__ __noinline__ void stage_norms(const GemvArgs& p, __half* ns, int nstr
   }
 }
 
-template <bool PACKED, int NB, int DEPTH, bool REGTAB, bool FMA, bool TILED>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
+template <bool PACKED, int NB, int DEPTH, bool REGTAB, bool FMA, bool TILED, bool GROUPED = false>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int slot_rt[32], slot_blk[32];
+  __shared__ GemvArgs grp_args;
+  if (GROUPED) {
+    // this CTA's problem: patch a copy of the arguments (matrix, rows, output, scratch)
+    const int4 d = pin.grp[blockIdx.y];
+    if (d.z <= 0) return;  // unused problem slot
+    if (threadIdx.x == 0) {
+      GemvArgs t = pin;
+      t.codes += (int64_t)d.x * pin.grp_codes_stride;
+      t.norms += (int64_t)d.x * pin.grp_norms_stride;
+      t.batch = d.z < 16 ? d.z : 16;
+      if (pin.x_rows) t.x_rows = pin.x_rows + d.y;
+      else t.x = static_cast<const uint8_t*>(pin.x) + (int64_t)d.y * pin.ld_x * (pin.x_dtype == PE_F32 ? 4 : 2);
+      t.y = static_cast<uint8_t*>(pin.y) + (int64_t)d.y * pin.ld_y * (pin.y_dtype == PE_F32 ? 4 : 2);
+      // scratch: [counter zone: one counter block per problem][partials, one block per problem]
+      uint8_t* cnt = reinterpret_cast<uint8_t*>(pin.ws_cnt) + (size_t)blockIdx.y * pin.grp_cnt_bytes;
+      t.ws_cnt = reinterpret_cast<unsigned*>(cnt);
+      t.ws_status = reinterpret_cast<int*>(cnt + pin.grp_cnt_bytes - 4);
+      t.ws_part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(pin.ws_part) + (size_t)blockIdx.y * pin.grp_ws_stride);
+      grp_args = t;
+    }
+    __syncthreads();
+  }
+  const GemvArgs& p = GROUPED ? grp_args : pin;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int G = gridDim.x, cta = blockIdx.x;
@@ -654,7 +689,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs p) {
     x_sl = on ? w / p.batch : 0;
     x_m = on ? w - x_sl * p.batch : 0;
     const int qq = Q0 + x_sl;
-    xraw = load4_raw(p.x, p.x_dtype, (int64_t)x_m * p.ld_x, (qq % p.nb) * kBlock + lane * 4, on ? p.in_f : 0, vec_ok);
+    xraw = load4_raw(p.x, p.x_dtype, x_row_of(p, x_m) * p.ld_x, (qq % p.nb) * kBlock + lane * 4, on ? p.in_f : 0, vec_ok);
   }
 
   // ---- shared memory: [table 32 KB][activation slots][norms][code ring 16 x 8 KB]
@@ -922,13 +957,13 @@ extern "C" size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded)
   return best;
 }
 
-template <bool PACKED, int NB, int DEPTH, bool REGTAB, bool FMA, bool TILED>
-static int launch_t(GemvArgs a, const Plan& pl, cudaStream_t st) {
+template <bool PACKED, int NB, int DEPTH, bool REGTAB, bool FMA, bool TILED, bool GROUPED = false>
+static int launch_t(GemvArgs a, const Plan& pl, cudaStream_t st, int n_problems = 1) {
   const int G = pl.G;
   a.dyn_bytes = (TILED ? pl.fixed_bytes_tiled : pl.fixed_bytes) +
                 kWarps * DEPTH * (TILED ? TileGeom<PACKED>::kStageBytes : (PACKED ? 1024 : 2048));
   if (a.dyn_bytes > 231424u) return PE_ERR_LIMIT;  // 227 KB minus the 1 KB of static shared memory
-  auto kfn = gemv_kernel<PACKED, NB, DEPTH, REGTAB, FMA, TILED>;
+  auto kfn = gemv_kernel<PACKED, NB, DEPTH, REGTAB, FMA, TILED, GROUPED>;
   static thread_local unsigned configured[16] = {0};
   int dev = 0;
   PE_CUDA_TRY(cudaGetDevice(&dev));
@@ -939,7 +974,7 @@ static int launch_t(GemvArgs a, const Plan& pl, cudaStream_t st) {
     PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.dyn_bytes));
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(G);
+  cfg.gridDim = dim3(G, n_problems);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = a.dyn_bytes;
   cfg.stream = st;
@@ -1008,6 +1043,7 @@ static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void*
   const unsigned ring_need = kWarps * 8u * (tiles ? (unsigned)TileGeom<true>::kStageBytes : 1024u);
   const bool deep = (tiles ? pl.fixed_bytes_tiled : pl.fixed_bytes) + ring_need <= 231424u;
   a.prof = g_prof;
+  a.x_rows = nullptr; a.grp = nullptr; a.grp_codes_stride = a.grp_norms_stride = 0; a.grp_ws_stride = a.grp_cnt_bytes = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // DEPTH = ring stages per warp (1 KB nibble / 2 KB byte stages): 8 KB per warp when it fits, else 6 / 4 KB
   if (batch <= 2) {  // one or two activation rows: fp16x2 FMA path, no tensor cores (always fits the deep ring)
@@ -1033,6 +1069,90 @@ extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const vo
                        int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
   return gemv_run(codes, packed, ld_codes, norms, ld_norms, nullptr, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
                   y_dtype, ld_y, bias, batch, out_f, in_f_padded, workspace, workspace_bytes, stream);
+}
+
+// ---- grouped launch: the experts of a mixture layer ------------------------------------
+//
+// `max_problems` problems of one shape share a launch (grid y).  Problem i is described on
+// the device by (matrix index, first row, rows <= 16, 0): rows first .. first + rows - 1 of
+// the row list `x_rows` (or of x itself when x_rows is NULL) times matrix `index` of a
+// stack of matrices, written to the same rows of y.  Slots with rows <= 0 return at once,
+// so the caller can size the launch for the worst case without knowing the routing.
+namespace pe {
+// The scratch starts with a counter zone of fixed size, whatever the shapes, so that the
+// partials of one call can never land where a later call keeps counters (which must read
+// zero on entry and are returned to zero).
+constexpr size_t kGroupedCounterZone = 4u << 20;
+static size_t grouped_cnt_bytes(int n_rt16) { return ((size_t)(n_rt16 + 1) * 4 + 255) & ~(size_t)255; }
+static int grouped_ctas(int max_problems, long long S, int sms) {
+  long long g = (2ll * sms) / max_problems;  // about two CTAs per SM-slot over all problems
+  if (g < 1) g = 1;
+  if (g > sms) g = sms;
+  if (g > S / 16) g = S / 16 < 1 ? 1 : S / 16;
+  return (int)g;
+}
+}  // namespace pe
+
+extern "C" size_t pe_gemv_grouped_workspace_bytes(int max_problems, int out_f, int in_f_padded) {
+  if (max_problems < 1 || out_f < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
+  const long long S = (long long)((out_f + 255) / 256) * (in_f_padded / kBlock) * 16;
+  const Plan pl = make_plan(16, out_f, in_f_padded, grouped_ctas(max_problems, S, kMaxSms));
+  if ((size_t)max_problems * grouped_cnt_bytes(pl.n_rt16) > kGroupedCounterZone) return 0;
+  return kGroupedCounterZone + (size_t)max_problems * pl.part_bytes;
+}
+
+extern "C" int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, int64_t codes_stride, const void* norms,
+                               int64_t ld_norms, int64_t norms_stride, const float* ct_scaled, int n_levels, const void* x,
+                               int x_kind, int x_dtype, int64_t ld_x, int in_f, const int32_t* x_rows, void* y, int y_dtype,
+                               int64_t ld_y, const int32_t* problems, int max_problems, int out_f, int in_f_padded,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+  if (!codes || !norms || !ct_scaled || !x || !y || !problems || !workspace) return PE_ERR_ARG;
+  if (max_problems < 1 || max_problems > 65535 || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
+  if (x_kind != PE_X_ROTATED && x_kind != PE_X_RAW) return PE_ERR_ARG;
+  if (x_dtype < PE_F32 || x_dtype > PE_BF16 || y_dtype < PE_F32 || y_dtype > PE_BF16) return PE_ERR_ARG;
+  if (n_levels < 2 || n_levels > 256 || (packed && n_levels > 16)) return PE_ERR_ARG;
+  if (in_f_padded % kBlock) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15) || (codes_stride & 15) ||
+      (reinterpret_cast<uintptr_t>(problems) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return PE_ERR_ALIGN;
+  if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  if (ld_x < (x_kind == PE_X_RAW ? in_f : in_f_padded) || ld_y < out_f) return PE_ERR_ARG;
+  const int sms = sm_count();
+  if (sms <= 0) return PE_ERR_CUDA;
+  if (sms > kMaxSms || (out_f + 15) / 16 > kMaxRowTiles) return PE_ERR_LIMIT;
+  const long long S = (long long)((out_f + 255) / 256) * (in_f_padded / kBlock) * 16;
+  if (S >= (1ll << 31) / kMaxSms) return PE_ERR_LIMIT;
+  Plan pl = make_plan(16, out_f, in_f_padded, grouped_ctas(max_problems, S, sms));
+  const size_t cnt_bytes = grouped_cnt_bytes(pl.n_rt16);
+  // sized like pe_gemv_grouped_workspace_bytes (its CTA count per problem is an upper bound of this one)
+  const size_t need = pe_gemv_grouped_workspace_bytes(max_problems, out_f, in_f_padded);
+  if (need == 0) return PE_ERR_LIMIT;
+  if (workspace_bytes < need) return PE_ERR_WORKSPACE;
+  const Plan pl_max = make_plan(16, out_f, in_f_padded, grouped_ctas(max_problems, S, kMaxSms));
+
+  GemvArgs a;
+  a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
+  a.norms = static_cast<const __half*>(norms); a.ld_norms = ld_norms;
+  a.tiles = nullptr;
+  a.ct = ct_scaled; a.n_levels = n_levels;
+  a.x = x; a.x_kind = x_kind; a.x_dtype = x_dtype; a.ld_x = ld_x; a.in_f = in_f;
+  a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  a.bias = nullptr;
+  a.batch = 16; a.N = out_f; a.K = in_f_padded; a.nb = pl.nb;
+  a.n_rt16 = pl.n_rt16; a.n_rt256 = pl.n_rt256; a.S = (int)pl.S; a.cap = pl.cap; a.max_slots = pl.max_slots;
+  a.ws_cnt = static_cast<unsigned*>(workspace);
+  a.ws_status = nullptr;  // per problem, set in the kernel
+  a.ws_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kGroupedCounterZone);
+  a.prof = nullptr;
+  a.x_rows = x_rows;
+  a.grp = reinterpret_cast<const int4*>(problems);
+  a.grp_codes_stride = codes_stride; a.grp_norms_stride = norms_stride;
+  a.grp_cnt_bytes = cnt_bytes;
+  a.grp_ws_stride = pl_max.part_bytes;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (packed && n_levels <= 8) return launch_t<true, 16, 6, true, false, false, true>(a, pl, st, max_problems);
+  if (packed) return launch_t<true, 16, 6, false, false, false, true>(a, pl, st, max_problems);
+  return launch_t<false, 16, 2, false, false, false, true>(a, pl, st, max_problems);
 }
 
 // ---- tiled weight layout ---------------------------------------------------------

@@ -56,3 +56,20 @@ def silu_mul(gate_up: torch.Tensor, inter: int) -> torch.Tensor:
     nv.check(nv.lib().pe_silu_mul(gate_up.data_ptr(), gate_up.stride(0), out.data_ptr(), out.stride(0), gate_up.shape[0],
                                   inter, nv.stream_ptr(dev)), "pe_silu_mul")
     return out
+
+
+def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: Union[int, torch.Tensor]) -> torch.Tensor:
+    """One new token per sequence: q (batch, hq, 1, head_dim) against the cache positions
+    0 .. pos (the token written last).  Returns (batch, hq * head_dim) fp16."""
+    dev = nv.require_cuda(q, k_cache, v_cache)
+    batch, hq, t, d = q.shape
+    if t != 1 or q.dtype != torch.float16 or not q.is_contiguous():
+        raise ValueError("decode_attention wants contiguous fp16 queries of one token per sequence")
+    hkv, max_len = k_cache.shape[1], k_cache.shape[2]
+    out = torch.empty(batch, hq * d, dtype=torch.float16, device=dev)
+    dev_pos = pos if torch.is_tensor(pos) else None
+    nv.check(nv.lib().pe_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                          dev_pos.data_ptr() if dev_pos is not None else None,
+                                          0 if dev_pos is not None else int(pos), out.data_ptr(), batch, hq, hkv, d, max_len,
+                                          nv.stream_ptr(dev)), "pe_decode_attention")
+    return out

@@ -4,8 +4,8 @@ This is measurement scaffolding around the quantized-linear path, not a model zo
 9B-class decoder (hidden 4096, 32 query / 8 KV heads of 128, intermediate 12288, 36
 layers, vocabulary 151936) whose every projection, the embedding and the LM head run
 through the native kernels.  Residual add + RMSNorm, rotary embedding + KV-cache write and
-SiLU * up are single native launches (``decode_ops``); attention over the KV cache is torch's
-SDPA (not the path under test).  ``rms_norm`` and ``rope`` below are the op-by-op torch
+SiLU * up are single native launches (``decode_ops``); decode-step attention over the KV cache is one native launch too
+(prefill attention is torch's SDPA); none of these is the path under test.  ``rms_norm`` and ``rope`` below are the op-by-op torch
 formulations the fused ops are tested against.
 
 Tensor parallelism follows vLLM's layout, which is also the only place where ranks
@@ -24,7 +24,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .decode_ops import add_rmsnorm, rope_cache, silu_mul
+from .decode_ops import add_rmsnorm, decode_attention, rope_cache, silu_mul
 from .kernels import quant_embedding, quant_matmul, retile
 from .packing import pack_codes_half_block
 from .utils import get_centroids, get_ct_scaled
@@ -130,7 +130,7 @@ class QuantDecoder:
                 total += L[k].codes.numel() * L[k].codes.element_size() + L[k].norms.numel() * 2
         return total + self.head.codes.numel() + self.head.norms.numel() * 2
 
-    def forward(self, ids: torch.Tensor, pos0, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, ids: torch.Tensor, pos0) -> torch.Tensor:
         """ids (B, T) -> next-token ids (B,).  ``pos0`` is an int (prefill) or a 0-d device
         tensor (decode under a CUDA graph); the KV cache is written at pos0..pos0+T-1."""
         cfg, d = self.cfg, self.cfg.head_dim
@@ -142,12 +142,13 @@ class QuantDecoder:
             h = add_rmsnorm(x, delta, L["ln1"], cfg.rms_eps)
             qkv = L["qkv"](h)
             q = rope_cache(qkv, pos0, self.k_cache[li], self.v_cache[li], b, t, self.hq, self.hkv, d, cfg.rope_theta)
-            if torch.is_tensor(pos0):  # decode: static shapes, the mask hides positions beyond the current one
-                att = F.scaled_dot_product_attention(q, self.k_cache[li], self.v_cache[li], attn_mask=mask, enable_gqa=True)
+            if t == 1 and d == 128:  # decode: one launch over the cache, length from the position scalar
+                att = decode_attention(q, self.k_cache[li], self.v_cache[li], pos0)
             else:
-                att = F.scaled_dot_product_attention(q, self.k_cache[li][:, :, : pos0 + t], self.v_cache[li][:, :, : pos0 + t],
-                                                     is_causal=(pos0 == 0 and t > 1), enable_gqa=True)
-            att = att.transpose(1, 2).reshape(b * t, self.hq * d)
+                p0 = int(pos0)
+                att = F.scaled_dot_product_attention(q, self.k_cache[li][:, :, : p0 + t], self.v_cache[li][:, :, : p0 + t],
+                                                     is_causal=(p0 == 0 and t > 1), enable_gqa=True)
+                att = att.transpose(1, 2).reshape(b * t, self.hq * d)
             o = self._all_reduce(L["o"](att, torch.float32))
             h = add_rmsnorm(x, o, L["ln2"], cfg.rms_eps)
             act = silu_mul(L["gate_up"](h), self.inter)
@@ -163,8 +164,3 @@ class QuantDecoder:
             best = torch.stack(vals, 0).argmax(0)
             idx = torch.stack(idxs, 0).gather(0, best[None])[0]
         return idx
-
-    def decode_mask(self, length_tensor: torch.Tensor) -> torch.Tensor:
-        """(1, 1, 1, max_len) additive mask: 0 for positions <= current, -inf beyond."""
-        ar = torch.arange(self.max_len, device=self.dev)
-        return torch.where(ar <= length_tensor, 0.0, float("-inf")).to(torch.float16).view(1, 1, 1, self.max_len)

@@ -15,6 +15,8 @@ from typing import Optional, Tuple
 
 import torch
 
+from . import _native as nv
+from .decode_ops import silu_mul
 from .kernels import quant_matmul
 from .packing import pack_codes_half_block
 from .utils import get_ct_scaled
@@ -132,11 +134,77 @@ class PolarQuantMoEMethod:
             topk_weights, topk_ids = route_softmax_topk(a, int(b), bool(renorm))
         return self.moe_forward(layer, x, topk_weights, topk_ids, expert_map)
 
+    # average (token, expert) pairs per local expert up to which the grouped decode-size
+    # launches are used; beyond it every expert has a tensor-core-sized batch of its own
+    GROUPED_MAX_ROWS_PER_EXPERT = 32
+
     def moe_forward(self, layer, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                     expert_map: Optional[torch.Tensor] = None) -> torch.Tensor:
         """y[t] = sum_k w[t,k] * down_e(silu(gate_e(x[t])) * up_e(x[t])), e = ids[t,k]; fp16 out.
-        Tokens are grouped by expert on the device; each expert's tokens go through the
-        two projections in batches (native kernels pick decode or tensor-core path)."""
+        Decode-size batches: two grouped launches over all experts (``pe_gemv_grouped``),
+        nothing read back to the host.  Prefill-size batches: per-expert tensor-core matmuls."""
+        pairs = topk_ids.numel()
+        if pairs <= self.GROUPED_MAX_ROWS_PER_EXPERT * layer.w13_codes.shape[0] and x.dtype in (torch.float16, torch.bfloat16):
+            return self._moe_forward_grouped(layer, x, topk_weights, topk_ids, expert_map)
+        return self._moe_forward_per_expert(layer, x, topk_weights, topk_ids, expert_map)
+
+    def _moe_forward_grouped(self, layer, x, topk_weights, topk_ids, expert_map) -> torch.Tensor:
+        lead = x.shape[:-1]
+        h, i = layer.moe_hidden, layer.moe_inter
+        hp, ip = layer.moe_hidden_padded, layer.moe_inter_padded
+        x2 = x.reshape(-1, h)
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        dev = nv.require_cuda(x2, layer.w13_codes, layer.w2_codes)
+        nv.ensure_init(dev)
+        t, k = topk_ids.shape
+        n_local = layer.w13_codes.shape[0]
+        pairs = t * k
+        ids = topk_ids.reshape(-1).long()
+        if expert_map is not None:
+            ids = expert_map.to(dev)[ids]
+        valid = ids >= 0
+        key = torch.where(valid, ids, torch.full_like(ids, n_local))      # pairs of other ranks sort last
+        order = torch.argsort(key, stable=True)
+        counts = torch.zeros(n_local + 1, dtype=torch.long, device=dev).index_add_(0, key, torch.ones_like(key))[:n_local]
+        n_prob = (counts + 15) // 16                                         # problems of <= 16 rows per expert
+        p_end = torch.cumsum(n_prob, 0)
+        first_row = torch.cumsum(counts, 0) - counts
+        max_problems = min(n_local, pairs) + pairs // 16
+        slot = torch.arange(max_problems, device=dev)
+        e_of = torch.searchsorted(p_end, slot, right=True).clamp_(max=n_local - 1)
+        j = slot - (p_end - n_prob)[e_of]
+        rows = (counts[e_of] - 16 * j).clamp_(0, 16) * (slot < p_end[-1])
+        desc = torch.stack([e_of, first_row[e_of] + 16 * j, rows, torch.zeros_like(rows)], 1).to(torch.int32).contiguous()
+        tok_sorted = (order // k).to(torch.int32)
+
+        l = nv.lib()
+        st = nv.stream_ptr(dev)
+        def grouped(codes, packed, norms, ct, xin, x_rows, in_f, kp, y):
+            need = l.pe_gemv_grouped_workspace_bytes(max_problems, y.shape[1], kp)
+            if need == 0:
+                raise RuntimeError("pe_gemv_grouped: too many problems for the scratch counter zone")
+            ws = nv.grouped_scratch(dev, need)
+            nv.check(l.pe_gemv_grouped(codes.data_ptr(), int(packed), codes.stride(1) * codes.element_size(),
+                                       codes.stride(0) * codes.element_size(), norms.data_ptr(), norms.stride(1), norms.stride(0),
+                                       ct.data_ptr(), ct.numel(), xin.data_ptr(), nv.PE_X_RAW, nv.dtype_code(xin), xin.stride(0),
+                                       in_f, x_rows.data_ptr() if x_rows is not None else None, y.data_ptr(), nv.dtype_code(y),
+                                       y.stride(0), desc.data_ptr(), max_problems, y.shape[1], kp, ws.data_ptr(), ws.numel(), st),
+                     "pe_gemv_grouped")
+        gu = torch.zeros(pairs, 2 * i, dtype=torch.float16, device=dev)
+        grouped(layer.w13_codes, self.w13_bits <= 4, layer.w13_norms, layer.w13_ct_scaled, x2, tok_sorted, h, hp, gu)
+        act = silu_mul(gu, i)
+        d = torch.zeros(pairs, h, dtype=torch.float32, device=dev)
+        grouped(layer.w2_codes, self.w2_bits <= 4, layer.w2_norms, layer.w2_ct_scaled, act, None, i, ip, d)
+        inv = torch.empty_like(order).scatter_(0, order, torch.arange(pairs, device=dev))
+        wts = topk_weights.reshape(-1).float() * valid
+        out = (d[inv].view(t, k, h) * wts.view(t, k, 1)).sum(1)             # slot order: reproducible
+        return out.to(torch.float16).view(*lead, h)
+
+    def _moe_forward_per_expert(self, layer, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                                expert_map: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Tokens are grouped by expert on the device; each expert's tokens go through the
+        two projections as one batch (tensor-core path for more than 16 rows)."""
         lead = x.shape[:-1]
         h, i = layer.moe_hidden, layer.moe_inter
         x2 = x.reshape(-1, h)

@@ -63,3 +63,23 @@ def test_silu_mul(rows, inter):
     out = silu_mul(gu, inter)
     assert torch.allclose(out.float(), ref.float(), rtol=2e-3, atol=1e-4)
     assert (out != ref).float().mean() < 0.02
+
+
+@pytest.mark.parametrize("batch,hq,hkv,pos,on_device", [(1, 32, 8, 512, True), (2, 4, 2, 20, True), (3, 8, 8, 0, False),
+                                                        (1, 16, 2, 639, False), (8, 32, 8, 100, True)])
+def test_decode_attention(batch, hq, hkv, pos, on_device):
+    """One-token attention over the cache against torch's SDPA on the first pos + 1 positions."""
+    from polarengine_vllm_b200.decode_ops import decode_attention
+    d, max_len = 128, 640
+    g = torch.Generator(device="cuda").manual_seed(pos + hq)
+    q = torch.randn(batch, hq, 1, d, device="cuda", generator=g).half()
+    kc = torch.randn(batch, hkv, max_len, d, device="cuda", generator=g).half()
+    vc = torch.randn(batch, hkv, max_len, d, device="cuda", generator=g).half()
+    p = torch.tensor(pos, device="cuda") if on_device else pos
+    out = decode_attention(q, kc, vc, p)
+    rep = hq // hkv
+    k = kc[:, :, : pos + 1].float().repeat_interleave(rep, dim=1)
+    v = vc[:, :, : pos + 1].float().repeat_interleave(rep, dim=1)
+    ref = F.scaled_dot_product_attention(q.float(), k, v).transpose(1, 2).reshape(batch, hq * d)
+    assert out.shape == (batch, hq * d) and out.dtype == torch.float16
+    assert torch.allclose(out.float(), ref, rtol=2e-3, atol=2e-3)

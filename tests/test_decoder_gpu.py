@@ -23,7 +23,7 @@ def test_graph_decode_equals_eager():
     ids, pos = nxt.view(2, 1).clone(), torch.tensor(20, device="cuda")
     eager = []
     for _ in range(4):
-        out = m.forward(ids, pos, m.decode_mask(pos))
+        out = m.forward(ids, pos)
         eager.append(out.clone()); ids.copy_(out.view(2, 1)); pos.add_(1)
     # same tokens when prefill is replayed position by position with the static-shape path
     m2cfg, m2 = small_model()
@@ -33,7 +33,7 @@ def test_graph_decode_equals_eager():
     s = torch.cuda.Stream()
     with torch.cuda.stream(s):
         def step():
-            out = m2.forward(ids2, pos2, m2.decode_mask(pos2)); ids2.copy_(out.view(2, 1)); pos2.add_(1)
+            out = m2.forward(ids2, pos2); ids2.copy_(out.view(2, 1)); pos2.add_(1)
         step(); torch.cuda.synchronize()
         first = ids2.clone()
         gr = torch.cuda.CUDAGraph()
