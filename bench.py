@@ -257,6 +257,96 @@ def model_decode(a, dev, rank, world):
     finish(world)
 
 
+def moe_layer(a, dev, rank, world):
+    """BASELINE configs[4]: 128 experts, top-8 softmax routing from a seeded fp16 gate (2688 -> 128), expert
+    intermediate 1856, gate/up Q3 and down Q4 codes; expert parallel over the ranks (tokens replicated, every rank
+    runs its local experts, all-reduce of the layer output).  value = tokens / time."""
+    import torch.distributed as dist
+    from polarengine_vllm_b200.moe_method import PolarQuantMoEMethod, route_softmax_topk
+    from polarengine_vllm_b200.parallel import expert_placement
+    from polarengine_vllm_b200.utils import get_ct_scaled
+    E, H, I, K = 128, 2688, 1856, 8
+    T = a.tokens
+    e_local = E // world
+    method = PolarQuantMoEMethod(3, 4)
+    layer = torch.nn.Module()
+    g = torch.Generator(device=dev).manual_seed(4242 + rank)
+    hp, ip = 2688, 1920
+    layer.w13_codes = torch.randint(0, 256, (e_local, 2 * I, hp // 2), dtype=torch.uint8, device=dev, generator=g) & 0x77
+    layer.w13_norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(e_local, 2 * I, hp // 128, device=dev, generator=g))).half()
+    layer.w2_codes = torch.randint(0, 256, (e_local, H, ip // 2), dtype=torch.uint8, device=dev, generator=g)
+    layer.w2_norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(e_local, H, ip // 128, device=dev, generator=g))).half()
+    layer.w13_ct_scaled, layer.w2_ct_scaled = get_ct_scaled(3).to(dev), get_ct_scaled(4).to(dev)
+    layer.moe_hidden, layer.moe_inter, layer.moe_hidden_padded, layer.moe_inter_padded = H, I, hp, ip
+    gs = torch.Generator(device=dev).manual_seed(7)  # same gate and tokens on every rank
+    gate = (0.02 * torch.randn(E, H, device=dev, generator=gs)).half()
+    x = torch.randn(T, H, device=dev, generator=gs).half()
+    emap = expert_placement(E, rank, world).to(dev) if world > 1 else None
+
+    def step():
+        w, ids = route_softmax_topk(x @ gate.T, K, True)
+        y = method.moe_forward(layer, x, w, ids, emap)
+        if world > 1:
+            dist.all_reduce(y)
+        return y
+
+    stream = torch.cuda.Stream(dev)
+    grouped = T * K <= method.GROUPED_MAX_ROWS_PER_EXPERT * e_local
+    steps = a.steps if a.steps != 4000 else (200 if grouped else 10)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        graph = None
+        if grouped:  # the grouped path reads nothing back to the host: one graph per step
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay() if graph is not None else step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        sampler.stop_flag = True
+    el = e0.elapsed_time(e1) / 1e3
+    if world > 1:
+        t = torch.tensor([el], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        el = float(t)
+    # algorithmic bytes: codes + norms of the experts that received a token (all ranks), activations negligible
+    _, ids = route_softmax_topk(x @ gate.T, K, True)
+    active = int(torch.unique(ids).numel())
+    per_expert = 2 * I * (hp // 2 + hp // 128 * 2) + H * (ip // 2 + ip // 128 * 2)
+    flops = 2.0 * T * K * (2 * I * H + H * I)
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        ms = el / steps * 1e3
+        print(json.dumps({
+            "metric": "MoE layer tokens/s", "unit": "tok/s", "value": T * steps / el, "n_gpus": a.gpus, "steps": steps,
+            "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"moe_layer (BASELINE configs[4]): 128 experts top-8, hidden 2688, intermediate 1856, "
+                                   f"gate/up Q3 down Q4, {T} tokens", "parallelism": f"ep{world}",
+                       "path": "two grouped launches (pe_gemv_grouped), CUDA graph" if grouped else "per-expert tensor-core matmuls, eager",
+                       "l2_defeat": "expert weights 970 MB >> L2"},
+            "active_experts": active, "expert_bytes_per_step": active * per_expert,
+            "weight_gbs": active * per_expert / (ms / 1e3) / 1e9,
+            "hbm_frac_of_measured": active * per_expert / (ms / 1e3) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)) / world,
+            "tflops": flops / (ms / 1e3) / 1e12, "clocks": sampler.summary(),
+            "gpu_launches": steps * (3 if grouped else 2 * min(active, e_local))}))
+    finish(world)
+
+
 def finish(world):
     """Leave a multi-rank run.  Tearing down the NCCL communicator while captured graphs that contain its kernels are
     alive can block forever; the ranks synchronise and exit without running the destructors instead."""
@@ -278,7 +368,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model", "moe"],
                     help="decode: decoder-layer GEMV pass (default, the headline); prefill: Q4 GEMM sweep of BASELINE "
                          "configs[2]; model: 36-layer 9B-class decode tok/s, tensor parallel over --gpus (configs[3])")
     ap.add_argument("--layers", type=int, default=36, help="decoder layers for --workload model")
@@ -286,6 +376,7 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true", help="model workload: launch decode steps eagerly")
     ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
+    ap.add_argument("--tokens", type=int, default=64, help="tokens for --workload moe (1 / 64 / 2048)")
     ap.add_argument("--probe", default=None, metavar="PROJ",
                     help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
     a = ap.parse_args()
@@ -323,6 +414,8 @@ def main():
     if a.workload == "prefill":
         prefill_sweep(a, dev, rank, world)
         return finish(world)
+    if a.workload == "moe":
+        return moe_layer(a, dev, rank, world)
     if a.workload == "model":
         return model_decode(a, dev, rank, world)
 
@@ -481,215 +574,11 @@ def main():
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except Exception:
             pass
-        wb = model.weight_bytes_per_step()
-        print(json.dumps({
-            "metric": "9B-class decode tok/s", "unit": "tok/s", "value": b * a.new_tokens / el, "n_gpus": a.gpus,
-            "steps": a.new_tokens, "warmup": 3, "ms_per_step": el / a.new_tokens * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers, hidden 4096, vocab 151936, "
-                                   f"prompt {a.prompt}, {a.new_tokens} new tokens", "batch": b,
-                       "parallelism": f"tp{world}", "l2_defeat": "weights per rank larger than L2",
-                       "launch": "eager" if a.no_graph else "cuda graph"},
-            "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
-            "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
-            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (8 * a.layers + 3)}))
-    finish(world)
-
-
-def finish(world):
-    """Leave a multi-rank run.  Tearing down the NCCL communicator while captured graphs that contain its kernels are
-    alive can block forever; the ranks synchronise and exit without running the destructors instead."""
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
-
-
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=4000)
-    ap.add_argument("--warmup", type=int, default=40)
-    ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--impl", default="ours")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
-                    help="decode: decoder-layer GEMV pass (default, the headline); prefill: Q4 GEMM sweep of BASELINE "
-                         "configs[2]; model: 36-layer 9B-class decode tok/s, tensor parallel over --gpus (configs[3])")
-    ap.add_argument("--layers", type=int, default=36, help="decoder layers for --workload model")
-    ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--new-tokens", type=int, default=128)
-    ap.add_argument("--no-graph", action="store_true", help="model workload: launch decode steps eagerly")
-    ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
-    ap.add_argument("--probe", default=None, metavar="PROJ",
-                    help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
-    a = ap.parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": "decoder_layer_gemv (BASELINE configs[1]): q/k/v Q5 fused, o Q6, gate/up Q3 fused, down Q4; "
-                          "hidden 4096, intermediate 12288", "batch": a.batch, "ring_layers": RING,
-              "l2_defeat": "inputs larger than L2 (ring of 8 layers = 964 MB of codes)",
-              "parallelism": f"replicas x{a.gpus}: each rank streams its own layers, no collective"}
-    base = {"metric": "quantized GEMV HBM GB/s", "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": config}
-
-    if a.impl == "reference":
-        if rank != 0:
-            return
-        # The reference has no CPU implementation of apply() (its Triton wrappers need a GPU);
-        # its CPU-runnable path is the torch math its kernels are tested against = the oracle.
-        cb, per_step = cpu_baseline(a.batch, budget_s=max(5.0, min(60.0, 0.3 * (a.steps + a.warmup))))
-        line = dict(base, impl="reference", value=cb["value"], ms_per_step=per_step * 1e3, cpu_baseline=cb, gpu_launches=0,
-                    e2e={"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
-        print(json.dumps(line))
-        return
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    from polarengine_vllm_b200 import kernels
-    from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
-    if a.workload == "prefill":
-        prefill_sweep(a, dev, rank, world)
-        return finish(world)
-    if a.workload == "model":
-        return model_decode(a, dev, rank, world)
-
-    steps = max(RING, a.steps // RING * RING)
-    warm = max(3, a.warmup)
-    layers = [make_layer(dev, 1000 + 16 * i + 97 * rank) for i in range(RING)]
-    g = torch.Generator(device=dev).manual_seed(7)
-    xh = torch.randn(a.batch, HIDDEN, device=dev, generator=g).half()
-    xi = torch.randn(a.batch, INTER, device=dev, generator=g).half()
-    outs = {name: torch.empty(a.batch, n, dtype=torch.float16, device=dev) for name, n, _, _ in PROJ}
-
-    def launch(layer, name):
-        w, packed, norms, ct, n, k, tiles = layer[name]
-        return kernels.quant_matmul(w, packed, norms, ct, xh if k == HIDDEN else xi, False, n, k, k, torch.float16,
-                                    tiles=tiles)
-
-    def ring_pass(names):
-        for layer in layers:
-            for name in names:
-                launch(layer, name)
-
-    all_names = [p[0] for p in PROJ]
-    if a.probe:
-        ring_pass([a.probe])
-        torch.cuda.synchronize()
-        print(json.dumps({"probe": a.probe, "launches": RING, "batch": a.batch}))
-        return
-    stream = torch.cuda.Stream(dev)
-
-    def timed_graph(names, reps, warm_reps):
-        """Capture one ring pass (RING steps) as a CUDA graph and time `reps` replays."""
-        with torch.cuda.stream(stream):
-            ring_pass(names)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                ring_pass(names)
-            for _ in range(warm_reps):
-                graph.replay()
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-                torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(reps):
-                graph.replay()
-            e1.record(stream)
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            return e0.elapsed_time(e1) / 1e3
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    elapsed = timed_graph(all_names, steps // RING, max(1, math.ceil(warm / RING)))
-    # dominant kernel alone: the nibble-code GEMV on the 4096x12288 Q4 layer (down_proj)
-    dom = ["down_proj"]
-    dom_elapsed = timed_graph(dom, steps // RING, 1)
-    sampler.stop_flag = True
-    if world > 1:
-        t = torch.tensor([elapsed], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed = float(t)
-    value = step_bytes(a.batch) * steps * world / elapsed / 1e9
-
-    # ---- end to end through the plugin surface with host buffers
-    method = {}
-    mods = {}
-    for name, n, k, bits in PROJ:
-        m = PolarQuantLinearMethod(128, bits)
-        mod = torch.nn.Module()
-        w, packed, norms, ct, _, _, tiles = layers[0][name]
-        mod.in_f, mod.out_f, mod.in_f_padded, mod.n_blocks, mod.bits, mod.block_size = k, n, k, k // 128, bits, 128
-        mod.packed, mod.norms, mod.ct_scaled = packed, norms, ct
-        if packed:
-            mod.codes_packed, mod.in_f_half = w, k // 2
-        else:
-            mod.codes = w
-        method[name], mods[name] = m, mod
-    hx = {k: torch.randn(a.batch, k).half().pin_memory() for k in (HIDDEN, INTER)}
-    hy = torch.empty(a.batch, HIDDEN, dtype=torch.float16).pin_memory()
-    e2e_steps = min(steps, 1000)
-
-    def e2e_step(i):
-        layer = layers[i % RING]
-        dx = {k: v.to(dev, non_blocking=True) for k, v in hx.items()}
-        y = None
-        for name, n, k, bits in PROJ:
-            mod = mods[name]
-            w, packed, norms, ct, _, _, tiles = layer[name]
-            mod.norms = norms
-            mod.codes_tiled = tiles
-            if packed:
-                mod.codes_packed = w
-            else:
-                mod.codes = w
-            y = method[name].apply(mod, dx[k])
-        hy.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for i in range(5):
-        e2e_step(i)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    torch.cuda.synchronize()
-    e2e_dt = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_dt], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_dt = float(t)
-    e2e = {"value": step_bytes(a.batch) * e2e_steps * world / e2e_dt / 1e9, "unit": "GB/s",
-           "h2d_bytes_per_step": a.batch * (HIDDEN + INTER) * 2, "d2h_bytes_per_step": a.batch * HIDDEN * 2,
-           "steps": e2e_steps, "api": "PolarQuantLinearMethod.apply x4 per step, pinned host in/out"}
-
-    if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         dom_launches = steps
         dom_bytes = sum(alg_bytes(n, k, b, a.batch) for nm, n, k, b in PROJ if nm in dom)
         achieved = dom_bytes / (dom_elapsed / dom_launches) / 1e9
-        roofline = {"bound": "hbm", "kernel": "gemv_kernel<packed> on down_proj 4096x12288 Q4", "achieved": achieved,
+        roofline = {"bound": "hbm", "kernel": "gemv_cols_kernel<packed, table, 3 chunks per warp> on down_proj 4096x12288 Q4", "achieved": achieved,
                     "peak": peak, "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                     "unit": "GB/s", "frac": achieved / peak, "avg_launch_us": dom_elapsed / dom_launches * 1e6,
                     "alg_bytes_per_launch": dom_bytes,
