@@ -187,7 +187,17 @@ def model_decode(a, dev, rank, world):
     from polarengine_vllm_b200.decoder import DecoderConfig, QuantDecoder
     cfg = DecoderConfig(n_layers=a.layers)
     b = a.batch
-    model = QuantDecoder(cfg, dev, rank, world, None, max_len=a.prompt + a.new_tokens + 8, batch=b)
+    fused = world > 1 and not a.nccl_allreduce
+    fused_note = "nccl all-reduce + add/norm kernels"
+    try:
+        model = QuantDecoder(cfg, dev, rank, world, None, max_len=a.prompt + a.new_tokens + 8, batch=b, fused_allreduce=fused)
+        if fused:
+            fused_note = "all-reduce + residual add + RMSNorm in one kernel over peer memory (decode steps); nccl in prefill"
+    except Exception as exc:  # peer mappings unavailable: the NCCL path still measures the model
+        if not fused:
+            raise
+        fused_note = f"nccl all-reduce (peer exchange unavailable: {type(exc).__name__})"
+        model = QuantDecoder(cfg, dev, rank, world, None, max_len=a.prompt + a.new_tokens + 8, batch=b)
     g = torch.Generator(device=dev).manual_seed(17)
     prompt = torch.randint(0, cfg.vocab, (b, a.prompt), device=dev, generator=g)
     torch.cuda.synchronize()
@@ -250,7 +260,8 @@ def model_decode(a, dev, rank, world):
             "config": {"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers, hidden 4096, vocab 151936, "
                                    f"prompt {a.prompt}, {a.new_tokens} new tokens", "batch": b,
                        "parallelism": f"tp{world}", "l2_defeat": "weights per rank larger than L2",
-                       "launch": "eager" if a.no_graph else "cuda graph"},
+                       "launch": "eager" if a.no_graph else "cuda graph", "row_parallel_epilogue": fused_note},
+            "exchange_timed_out": bool(model.xchg.timed_out()) if model.xchg is not None else None,
             "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
             "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
             "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (8 * a.layers + 3)}))
@@ -375,6 +386,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true", help="model workload: launch decode steps eagerly")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="model workload: NCCL all-reduce instead of the fused peer-memory epilogue")
     ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
     ap.add_argument("--tokens", type=int, default=64, help="tokens for --workload moe (1 / 64 / 2048)")
     ap.add_argument("--probe", default=None, metavar="PROJ",

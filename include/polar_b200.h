@@ -146,8 +146,9 @@ int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, 
  * problem i multiplies rows first .. first + rows - 1 of the row list -- row x_rows[j] of
  * x when x_rows is not NULL (a gather by token id), else row j of x -- with expert
  * `expert` and writes rows first .. of y.  Entries with rows <= 0 are skipped, so the host
- * sizes the launch for the worst case and never reads the routing back.  An expert with
- * more than 16 rows takes several problems.  No bias.  The scratch
+ * sizes the launch for the worst case and never reads the routing back.  max_rows (<= 16)
+ * bounds the rows of any problem (8 or less selects the lighter kernel); an expert with
+ * more rows takes several problems.  No bias.  The scratch
  * (pe_gemv_grouped_workspace_bytes; 0 = too many problems) is its own buffer, not the one
  * of pe_gemv: its first 4 MiB must be zero before the first use and are left zero, so
  * calls of any shapes can share it in stream order.
@@ -159,8 +160,44 @@ size_t pe_gemv_grouped_workspace_bytes(int max_problems, int out_f, int in_f_pad
 int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, int64_t codes_stride, const void* norms,
                     int64_t ld_norms, int64_t norms_stride, const float* ct_scaled, int n_levels, const void* x,
                     int x_kind, int x_dtype, int64_t ld_x, int in_f, const int32_t* x_rows, void* y, int y_dtype,
-                    int64_t ld_y, const int32_t* problems, int max_problems, int out_f, int in_f_padded,
-                    void* workspace, size_t workspace_bytes, void* stream);
+                    int64_t ld_y, const int32_t* problems, int max_problems, int max_rows, int out_f,
+                    int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- mixture-of-experts bookkeeping on the device ----------------------------------
+ * pe_moe_plan groups the (token, slot) pairs of a routing decision by local expert:
+ *   topk_ids (n_pairs = tokens * top_k, int64, token-major); expert_map (optional, int64,
+ *   global expert -> local index or -1, the expert-parallel placement);
+ *   row_token[r] = token of grouped row r (the x_rows list of pe_gemv_grouped),
+ *   pos[pair] = grouped row of the pair or -1 if its expert lives on another rank,
+ *   problems = the problem list of pe_gemv_grouped with at most rows_per_problem rows each
+ *   (max_problems >= min(experts, pairs) + pairs / rows_per_problem entries).
+ * pe_moe_combine: out[t, :] = sum_j topk_weights[t, j] * y[pos[t * top_k + j], :] (pairs
+ *   with pos < 0 contribute nothing), y fp32 (rows, hidden), out fp32/fp16/bf16.
+ * Together with pe_gemv_grouped they replace the per-expert Python loop of the reference's
+ * MoE layer (nemotron_offload.py:190-226: index tokens, run the expert, index_add). */
+int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, int n_pairs, int top_k, int n_local_experts,
+                int rows_per_problem, int max_problems, int32_t* row_token, int32_t* pos, int32_t* problems, void* stream);
+int pe_moe_combine(const float* y, int64_t ld_y, const int32_t* pos, const float* topk_weights, int tokens, int top_k,
+                   void* out, int out_dtype, int64_t ld_out, int hidden, void* stream);
+
+/* ---- row-parallel epilogue across tensor-parallel ranks -----------------------------
+ * One kernel per rank: all-reduce of the fp32 partial outputs of a row-parallel projection
+ * (o_proj / down_proj shards, loader.py:558-638 slices them) over peer memory, then
+ * x += fp16(sum), out = fp16(x * rsqrt(mean(x^2) + eps)) * weight (pe_add_rmsnorm).  It
+ * stands where a vLLM deployment issues an NCCL all-reduce plus its add and norm kernels.
+ *   peer_buffers: DEVICE array of `world` addresses, entry r = rank r's exchange buffer
+ *     (pe_allreduce_buffer_bytes, zero before the first call) as mapped in THIS process
+ *     (peer memory: CUDA IPC or symmetric-memory mappings; entry `rank` is the local one);
+ *   every rank launches the same call (rows, hidden) in the same order;
+ *   seq: device array of max_rows counters, zero at start, owned by the kernel;
+ *   status: device word set to 1 if a peer did not arrive within about a second (the
+ *     launch then completes with incomplete sums instead of hanging).
+ * rows <= max_rows, hidden % 8 == 0, hidden <= 16384 and the same for every call on one
+ * buffer, world <= 16.  Plain peer loads / stores only (no multicast). */
+size_t pe_allreduce_buffer_bytes(int world, int max_rows, int hidden);
+int pe_allreduce_add_rmsnorm(const float* partial, void* x, const void* weight, void* out, int rows, int hidden, float eps,
+                             const uint64_t* peer_buffers, int rank, int world, int max_rows, unsigned* seq, int* status,
+                             void* stream);
 
 /* ---- tiled weight layout for the decode kernel -----------------------------------
  * pe_retile rewrites a layer (codes + norms, the reference's row-major layouts) into the

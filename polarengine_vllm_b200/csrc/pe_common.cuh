@@ -25,7 +25,32 @@ inline int cuda_fail(cudaError_t e) {
 
 int sm_count();  // SM count of the current device (cached per device)
 
+// Launch with programmatic stream serialization: the grid may start while its predecessor
+// in the stream is still draining.  The kernel must call pdl_enter() (or its own
+// griddepcontrol.wait) before it touches anything the predecessor reads or writes.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- small device helpers ----------------------------------------------------
+// Let the next kernel of the stream start its own prologue now, then wait until the
+// previous kernel has completed and its writes are visible.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }

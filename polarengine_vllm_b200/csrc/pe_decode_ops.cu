@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__half* x, co
                                                                    __half* out, int hidden, float eps) {
   __shared__ float warp_sums[kNormThreads / 32];
   const int row = blockIdx.x, tid = threadIdx.x;
+  pdl_enter();
   __half* xr = x + (int64_t)row * hidden;
   float v[kNormMaxIter][8];
   float ss = 0.f;
@@ -98,6 +99,7 @@ __global__ void rope_cache_kernel(const __half* qkv, int64_t ld_qkv, const int64
                                   float theta) {
   const int tok = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
   const int b = tok / t, i = tok - b * t;
+  pdl_enter();
   const int64_t pos = (pos_dev ? *pos_dev : pos_host) + i;
   const __half* src = qkv + (int64_t)tok * ld_qkv + (int64_t)head * d;
   const int half_d = d >> 1;
@@ -127,6 +129,7 @@ __global__ void rope_cache_kernel(const __half* qkv, int64_t ld_qkv, const int64
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* gu, int64_t ld_gu, __half* out, int64_t ld_out, int inter,
                                                        int64_t n_vec) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_enter();
   if (idx >= n_vec) return;
   const int per_row = inter >> 3;
   const int64_t r = idx / per_row;
@@ -274,6 +277,7 @@ __global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(const __h
   extern __shared__ __align__(16) float att_smem[];
   const int G = hq / hkv;
   const int kvh = blockIdx.x, b = blockIdx.y;
+  pdl_enter();
   const int64_t len64 = (pos_dev ? *pos_dev : pos_host) + 1;  // the current token is already in the cache
   const int L = (int)(len64 < 1 ? 1 : (len64 > max_len ? max_len : len64));
   const __half* qp = q + ((int64_t)b * hq + (int64_t)kvh * G) * D;
@@ -301,9 +305,9 @@ extern "C" int pe_add_rmsnorm(void* x, const void* delta, int delta_dtype, const
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(weight) |
        reinterpret_cast<uintptr_t>(out)) & 15)
     return PE_ERR_ALIGN;
-  add_rmsnorm_kernel<<<rows, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__half*>(x), delta, delta_dtype, static_cast<const __half*>(weight), static_cast<__half*>(out), hidden, eps);
-  PE_CUDA_TRY(cudaGetLastError());
+  PE_CUDA_TRY(launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+                         static_cast<__half*>(x), delta, delta_dtype, static_cast<const __half*>(weight), static_cast<__half*>(out),
+                         hidden, eps));
   return PE_OK;
 }
 
@@ -314,10 +318,10 @@ extern "C" int pe_rope_cache(const void* qkv, int64_t ld_qkv, const int64_t* pos
   if (head_dim < 2 || head_dim > 2048 || (head_dim & 1)) return PE_ERR_SHAPE;
   if (ld_qkv < (int64_t)(hq + 2 * hkv) * head_dim) return PE_ERR_ARG;
   if ((int64_t)batch * t > 0x7fffffff || hq + 2 * hkv > 65535) return PE_ERR_LIMIT;
-  rope_cache_kernel<<<dim3((unsigned)(batch * t), (unsigned)(hq + 2 * hkv)), head_dim / 2, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(qkv), ld_qkv, pos_dev, pos_host, static_cast<__half*>(q_out), static_cast<__half*>(k_cache),
-      static_cast<__half*>(v_cache), t, hq, hkv, head_dim, max_len, theta);
-  PE_CUDA_TRY(cudaGetLastError());
+  PE_CUDA_TRY(launch_pdl(rope_cache_kernel, dim3((unsigned)(batch * t), (unsigned)(hq + 2 * hkv)), dim3(head_dim / 2), 0,
+                         static_cast<cudaStream_t>(stream), static_cast<const __half*>(qkv), ld_qkv, pos_dev, pos_host,
+                         static_cast<__half*>(q_out), static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), t, hq, hkv,
+                         head_dim, max_len, theta));
   return PE_OK;
 }
 
@@ -329,9 +333,8 @@ extern "C" int pe_silu_mul(const void* gate_up, int64_t ld_gu, void* out, int64_
   const int64_t n_vec = (int64_t)rows * (inter / 8);
   const int64_t blocks = (n_vec + 255) / 256;
   if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
-  silu_mul_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(gate_up), ld_gu,
-                                                                                 static_cast<__half*>(out), ld_out, inter, n_vec);
-  PE_CUDA_TRY(cudaGetLastError());
+  PE_CUDA_TRY(launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                         static_cast<const __half*>(gate_up), ld_gu, static_cast<__half*>(out), ld_out, inter, n_vec));
   return PE_OK;
 }
 
@@ -353,9 +356,8 @@ extern "C" int pe_decode_attention(const void* q, const void* k_cache, const voi
     PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 16) configured[dev] = smem;
   }
-  kfn<<<dim3((unsigned)hkv, (unsigned)batch), kAttThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos_dev, pos_host,
-      static_cast<__half*>(out), hq, hkv, max_len, 1.f / sqrtf((float)head_dim));
-  PE_CUDA_TRY(cudaGetLastError());
+  PE_CUDA_TRY(launch_pdl(kfn, dim3((unsigned)hkv, (unsigned)batch), dim3(kAttThreads), smem, static_cast<cudaStream_t>(stream),
+                         static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
+                         pos_dev, pos_host, static_cast<__half*>(out), hq, hkv, max_len, 1.f / sqrtf((float)head_dim)));
   return PE_OK;
 }

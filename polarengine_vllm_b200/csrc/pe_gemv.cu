@@ -618,7 +618,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
       GemvArgs t = pin;
       t.codes += (int64_t)d.x * pin.grp_codes_stride;
       t.norms += (int64_t)d.x * pin.grp_norms_stride;
-      t.batch = d.z < 16 ? d.z : 16;
+      t.batch = d.z < NB ? d.z : NB;
       if (pin.x_rows) t.x_rows = pin.x_rows + d.y;
       else t.x = static_cast<const uint8_t*>(pin.x) + (int64_t)d.y * pin.ld_x * (pin.x_dtype == PE_F32 ? 4 : 2);
       t.y = static_cast<uint8_t*>(pin.y) + (int64_t)d.y * pin.ld_y * (pin.y_dtype == PE_F32 ? 4 : 2);
@@ -1104,9 +1104,10 @@ extern "C" size_t pe_gemv_grouped_workspace_bytes(int max_problems, int out_f, i
 extern "C" int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, int64_t codes_stride, const void* norms,
                                int64_t ld_norms, int64_t norms_stride, const float* ct_scaled, int n_levels, const void* x,
                                int x_kind, int x_dtype, int64_t ld_x, int in_f, const int32_t* x_rows, void* y, int y_dtype,
-                               int64_t ld_y, const int32_t* problems, int max_problems, int out_f, int in_f_padded,
-                               void* workspace, size_t workspace_bytes, void* stream) {
+                               int64_t ld_y, const int32_t* problems, int max_problems, int max_rows, int out_f,
+                               int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
   if (!codes || !norms || !ct_scaled || !x || !y || !problems || !workspace) return PE_ERR_ARG;
+  if (max_rows < 1 || max_rows > 16) return PE_ERR_ARG;
   if (max_problems < 1 || max_problems > 65535 || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
   if (x_kind != PE_X_ROTATED && x_kind != PE_X_RAW) return PE_ERR_ARG;
   if (x_dtype < PE_F32 || x_dtype > PE_BF16 || y_dtype < PE_F32 || y_dtype > PE_BF16) return PE_ERR_ARG;
@@ -1150,6 +1151,11 @@ extern "C" int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, 
   a.grp_cnt_bytes = cnt_bytes;
   a.grp_ws_stride = pl_max.part_bytes;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (max_rows <= 8) {  // every problem fits one 8-row activation tile: half the tensor work per step
+    if (packed && n_levels <= 8) return launch_t<true, 8, 6, true, false, false, true>(a, pl, st, max_problems);
+    if (packed) return launch_t<true, 8, 6, false, false, false, true>(a, pl, st, max_problems);
+    return launch_t<false, 8, 2, false, false, false, true>(a, pl, st, max_problems);
+  }
   if (packed && n_levels <= 8) return launch_t<true, 16, 6, true, false, false, true>(a, pl, st, max_problems);
   if (packed) return launch_t<true, 16, 6, false, false, false, true>(a, pl, st, max_problems);
   return launch_t<false, 16, 2, false, false, false, true>(a, pl, st, max_problems);

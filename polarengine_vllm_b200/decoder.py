@@ -27,6 +27,7 @@ import torch.nn.functional as F
 from .decode_ops import add_rmsnorm, decode_attention, rope_cache, silu_mul
 from .kernels import quant_embedding, quant_matmul, retile
 from .packing import pack_codes_half_block
+from .parallel import PeerExchange
 from .utils import get_centroids, get_ct_scaled
 
 
@@ -89,7 +90,7 @@ def rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor:
 
 class QuantDecoder:
     def __init__(self, cfg: DecoderConfig, dev, tp_rank: int = 0, tp_size: int = 1, group=None, seed: int = 1000,
-                 max_len: int = 640, batch: int = 1):
+                 max_len: int = 640, batch: int = 1, fused_allreduce: bool = False):
         assert cfg.n_kv_heads % tp_size == 0 and (cfg.intermediate // tp_size) % 128 == 0
         self.cfg, self.dev, self.rank, self.tp, self.group = cfg, dev, tp_rank, tp_size, group
         self.hq, self.hkv = cfg.n_heads // tp_size, cfg.n_kv_heads // tp_size
@@ -113,6 +114,8 @@ class QuantDecoder:
         self.head = QWeight(cfg.vocab // tp_size, cfg.hidden, cfg.bits_head, dev, gh)
         self.final_ln = torch.ones(cfg.hidden, dtype=torch.float16, device=dev)
         self.max_len, self.batch = max_len, batch
+        # decode steps of a sharded model: all-reduce + residual add + norm as one launch over peer memory
+        self.xchg = PeerExchange(dev, tp_rank, tp_size, max(batch, 1), cfg.hidden, group) if fused_allreduce else None
         self.k_cache = [torch.zeros(batch, self.hkv, max_len, d, dtype=torch.float16, device=dev) for _ in range(cfg.n_layers)]
         self.v_cache = [torch.zeros(batch, self.hkv, max_len, d, dtype=torch.float16, device=dev) for _ in range(cfg.n_layers)]
 
@@ -138,8 +141,15 @@ class QuantDecoder:
         x = quant_embedding(self.embed.codes, self.embed.packed, self.embed.norms, self.embed.ct, ids, cfg.hidden)
         x = x.view(b * t, cfg.hidden)  # residual stream, updated in place by add_rmsnorm
         delta = None                   # output of the previous layer's down projection, not yet added
+        fused = self.xchg is not None and b * t <= self.xchg.max_rows
+
+        def reduce_add_norm(partial, w):   # x += sum over ranks of partial; returns norm(x) * w
+            if fused:
+                return self.xchg.allreduce_add_rmsnorm(partial, x, w, cfg.rms_eps)
+            return add_rmsnorm(x, self._all_reduce(partial), w, cfg.rms_eps)
+
         for li, L in enumerate(self.layers):
-            h = add_rmsnorm(x, delta, L["ln1"], cfg.rms_eps)
+            h = add_rmsnorm(x, None, L["ln1"], cfg.rms_eps) if delta is None else reduce_add_norm(delta, L["ln1"])
             qkv = L["qkv"](h)
             q = rope_cache(qkv, pos0, self.k_cache[li], self.v_cache[li], b, t, self.hq, self.hkv, d, cfg.rope_theta)
             if t == 1 and d == 128:  # decode: one launch over the cache, length from the position scalar
@@ -149,11 +159,10 @@ class QuantDecoder:
                 att = F.scaled_dot_product_attention(q, self.k_cache[li][:, :, : p0 + t], self.v_cache[li][:, :, : p0 + t],
                                                      is_causal=(p0 == 0 and t > 1), enable_gqa=True)
                 att = att.transpose(1, 2).reshape(b * t, self.hq * d)
-            o = self._all_reduce(L["o"](att, torch.float32))
-            h = add_rmsnorm(x, o, L["ln2"], cfg.rms_eps)
+            h = reduce_add_norm(L["o"](att, torch.float32), L["ln2"])
             act = silu_mul(L["gate_up"](h), self.inter)
-            delta = self._all_reduce(L["down"](act, torch.float32))
-        h = add_rmsnorm(x, delta, self.final_ln, cfg.rms_eps).view(b, t, cfg.hidden)[:, -1]
+            delta = L["down"](act, torch.float32)
+        h = reduce_add_norm(delta, self.final_ln).view(b, t, cfg.hidden)[:, -1]
         logits = self.head(h, torch.float32)                      # (B, vocab / tp)
         val, idx = logits.max(dim=-1)
         if self.tp > 1:

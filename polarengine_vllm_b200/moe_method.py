@@ -160,26 +160,19 @@ class PolarQuantMoEMethod:
         t, k = topk_ids.shape
         n_local = layer.w13_codes.shape[0]
         pairs = t * k
-        ids = topk_ids.reshape(-1).long()
-        if expert_map is not None:
-            ids = expert_map.to(dev)[ids]
-        valid = ids >= 0
-        key = torch.where(valid, ids, torch.full_like(ids, n_local))      # pairs of other ranks sort last
-        order = torch.argsort(key, stable=True)
-        counts = torch.zeros(n_local + 1, dtype=torch.long, device=dev).index_add_(0, key, torch.ones_like(key))[:n_local]
-        n_prob = (counts + 15) // 16                                         # problems of <= 16 rows per expert
-        p_end = torch.cumsum(n_prob, 0)
-        first_row = torch.cumsum(counts, 0) - counts
-        max_problems = min(n_local, pairs) + pairs // 16
-        slot = torch.arange(max_problems, device=dev)
-        e_of = torch.searchsorted(p_end, slot, right=True).clamp_(max=n_local - 1)
-        j = slot - (p_end - n_prob)[e_of]
-        rows = (counts[e_of] - 16 * j).clamp_(0, 16) * (slot < p_end[-1])
-        desc = torch.stack([e_of, first_row[e_of] + 16 * j, rows, torch.zeros_like(rows)], 1).to(torch.int32).contiguous()
-        tok_sorted = (order // k).to(torch.int32)
-
+        ids = topk_ids.reshape(-1).to(torch.int64).contiguous()
+        emap = expert_map.to(device=dev, dtype=torch.int64).contiguous() if expert_map is not None else None
+        # rows per problem: 8 while experts see few tokens (lighter kernel), else 16
+        rpp = 8 if pairs <= 6 * n_local else 16
+        max_problems = min(n_local, pairs) + pairs // rpp
+        tok_sorted = torch.empty(pairs, dtype=torch.int32, device=dev)   # token of every grouped row
+        pos = torch.empty(pairs, dtype=torch.int32, device=dev)          # grouped row of every pair (-1: other rank)
+        desc = torch.empty(max_problems, 4, dtype=torch.int32, device=dev)
         l = nv.lib()
         st = nv.stream_ptr(dev)
+        nv.check(l.pe_moe_plan(ids.data_ptr(), emap.data_ptr() if emap is not None else None, pairs, k, n_local, rpp,
+                               max_problems, tok_sorted.data_ptr(), pos.data_ptr(), desc.data_ptr(), st), "pe_moe_plan")
+
         def grouped(codes, packed, norms, ct, xin, x_rows, in_f, kp, y):
             need = l.pe_gemv_grouped_workspace_bytes(max_problems, y.shape[1], kp)
             if need == 0:
@@ -189,17 +182,18 @@ class PolarQuantMoEMethod:
                                        codes.stride(0) * codes.element_size(), norms.data_ptr(), norms.stride(1), norms.stride(0),
                                        ct.data_ptr(), ct.numel(), xin.data_ptr(), nv.PE_X_RAW, nv.dtype_code(xin), xin.stride(0),
                                        in_f, x_rows.data_ptr() if x_rows is not None else None, y.data_ptr(), nv.dtype_code(y),
-                                       y.stride(0), desc.data_ptr(), max_problems, y.shape[1], kp, ws.data_ptr(), ws.numel(), st),
+                                       y.stride(0), desc.data_ptr(), max_problems, rpp, y.shape[1], kp, ws.data_ptr(), ws.numel(), st),
                      "pe_gemv_grouped")
-        gu = torch.zeros(pairs, 2 * i, dtype=torch.float16, device=dev)
+        gu = torch.empty(pairs, 2 * i, dtype=torch.float16, device=dev)   # rows beyond the local pairs stay unused
         grouped(layer.w13_codes, self.w13_bits <= 4, layer.w13_norms, layer.w13_ct_scaled, x2, tok_sorted, h, hp, gu)
         act = silu_mul(gu, i)
-        d = torch.zeros(pairs, h, dtype=torch.float32, device=dev)
+        d = torch.empty(pairs, h, dtype=torch.float32, device=dev)
         grouped(layer.w2_codes, self.w2_bits <= 4, layer.w2_norms, layer.w2_ct_scaled, act, None, i, ip, d)
-        inv = torch.empty_like(order).scatter_(0, order, torch.arange(pairs, device=dev))
-        wts = topk_weights.reshape(-1).float() * valid
-        out = (d[inv].view(t, k, h) * wts.view(t, k, 1)).sum(1)             # slot order: reproducible
-        return out.to(torch.float16).view(*lead, h)
+        out = torch.empty(t, h, dtype=torch.float16, device=dev)
+        wts = topk_weights.reshape(-1).to(torch.float32).contiguous()
+        nv.check(l.pe_moe_combine(d.data_ptr(), d.stride(0), pos.data_ptr(), wts.data_ptr(), t, k, out.data_ptr(), nv.PE_F16,
+                                  out.stride(0), h, st), "pe_moe_combine")
+        return out.view(*lead, h)
 
     def _moe_forward_per_expert(self, layer, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                                 expert_map: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -97,3 +97,59 @@ class QuantLinearShard:
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(y, group=self.group)
         return y.to(out_dtype)
+
+
+class PeerExchange:
+    """Exchange buffers of the fused all-reduce + residual add + RMSNorm kernel
+    (``pe_allreduce_add_rmsnorm``): one buffer per rank, mapped into every rank.
+
+    With one rank the buffer is ordinary device memory (the kernel then exchanges with
+    itself, which is how the protocol is tested on a single GPU).  With several ranks the
+    buffers come from torch's symmetric-memory allocator, which only provides the peer
+    mappings; every load and store on them is issued by the kernel of this package.
+    """
+
+    def __init__(self, device, rank: int, world: int, max_rows: int, hidden: int, group=None):
+        from . import _native as nv
+        self.rank, self.world, self.max_rows, self.hidden = rank, world, max_rows, hidden
+        nbytes = nv.lib().pe_allreduce_buffer_bytes(world, max_rows, hidden)
+        if nbytes == 0:
+            raise ValueError("exchange buffer: unsupported world size / rows / hidden")
+        if world == 1:
+            self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            ptrs = [self.buf.data_ptr()]
+        else:
+            import os
+            import torch.distributed as dist
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings only
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            handle = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            self._handle = handle
+            torch.cuda.synchronize(device)
+            dist.barrier(group)  # every buffer reads zero before anyone's first launch
+        self.peers = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.seq = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def allreduce_add_rmsnorm(self, partial: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """x (rows, hidden) fp16 += fp16(sum over ranks of partial (rows, hidden) fp32), in place;
+        returns RMSNorm(x) * weight.  Every rank must make the same sequence of calls."""
+        from . import _native as nv
+        rows, hidden = x.shape
+        if hidden != self.hidden or rows > self.max_rows or partial.shape != x.shape:
+            raise ValueError("exchange: shape does not fit the buffer")
+        if partial.dtype != torch.float32 or x.dtype != torch.float16 or not partial.is_contiguous() or not x.is_contiguous():
+            raise ValueError("exchange: fp32 partials and an fp16 residual stream, both contiguous")
+        out = torch.empty_like(x)
+        nv.check(nv.lib().pe_allreduce_add_rmsnorm(partial.data_ptr(), x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, hidden,
+                                                   float(eps), self.peers.data_ptr(), self.rank, self.world, self.max_rows,
+                                                   self.seq.data_ptr(), self.status.data_ptr(), nv.stream_ptr(x.device)),
+                 "pe_allreduce_add_rmsnorm")
+        return out
+
+    def timed_out(self) -> bool:
+        """True if any call so far gave up waiting for a peer (reads the status word back)."""
+        return bool(int(self.status.item()))

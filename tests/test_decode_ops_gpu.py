@@ -83,3 +83,24 @@ def test_decode_attention(batch, hq, hkv, pos, on_device):
     ref = F.scaled_dot_product_attention(q.float(), k, v).transpose(1, 2).reshape(batch, hq * d)
     assert out.shape == (batch, hq * d) and out.dtype == torch.float16
     assert torch.allclose(out.float(), ref, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (4, 4096), (3, 512)])
+def test_exchange_with_one_rank_equals_add_rmsnorm(rows, hidden):
+    """World size 1: the fused all-reduce + add + norm kernel pushes to, waits for and reads
+    its own buffer, so the whole protocol (slots, flags, sequence numbers, both parities)
+    runs inside one launch on one GPU and must give the bits of add_rmsnorm."""
+    from polarengine_vllm_b200.decode_ops import add_rmsnorm
+    from polarengine_vllm_b200.parallel import PeerExchange
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    xchg = PeerExchange(torch.device("cuda"), 0, 1, 4, hidden)
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=g)).half()
+    x = torch.randn(rows, hidden, device="cuda", generator=g).half()
+    x_ref = x.clone()
+    for _ in range(5):  # consecutive calls alternate the slot parity
+        part = torch.randn(rows, hidden, device="cuda", generator=g)
+        out = xchg.allreduce_add_rmsnorm(part, x, w, 1e-6)
+        ref = add_rmsnorm(x_ref, part, w, 1e-6)
+        assert torch.equal(x, x_ref) and torch.equal(out, ref)
+    assert not xchg.timed_out()
+    assert int(xchg.seq[0]) == 5
