@@ -31,7 +31,7 @@ HIDDEN, INTER, QKV = 4096, 12288, 6144
 # (name, out_f, in_f, bits)
 PROJ = [("qkv_proj", QKV, HIDDEN, 5), ("o_proj", HIDDEN, HIDDEN, 6),
         ("gate_up_proj", 2 * INTER, HIDDEN, 3), ("down_proj", HIDDEN, INTER, 4)]
-NCU_DRAM_BYTES_DOWN_B1 = 26065664  # ncu capture of the down_proj launch, see profiles/
+NCU_DRAM_BYTES_DOWN_B1 = 26035072  # dram__bytes_read + write of one batch-1 down_proj launch (ncu capture summarised in profiles/)
 RING = 8  # layers in the ring: 8 x 120.5 MB = 964 MB >> 126 MB of L2
 
 
