@@ -15,7 +15,9 @@ import sys
 import numpy as np
 import torch
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/polarengine-vllm")
+ref_root = sys.argv[1]
 sys.path.insert(0, ref_root)
 here = os.path.dirname(os.path.abspath(__file__))
 
