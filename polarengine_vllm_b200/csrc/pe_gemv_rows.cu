@@ -359,7 +359,8 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
-constexpr int kColStage = 2 * kItemBytes + 32;  // two 4-row sub-items + the norms of 8 rows
+// ring slot of one item: SUB sub-items of 4 rows x 128 bytes, then 4 bytes of norms per row, rounded to whole 128-byte lines
+__host__ __device__ constexpr int col_stage_bytes(int sub) { return (sub * kItemBytes + sub * 16 + 127) & ~127; }
 
 // dot product of one lane's 16 bytes of codes with its activation registers
 template <bool PACKED, bool REGTAB, int NX>
@@ -385,19 +386,21 @@ __device__ __forceinline__ float reg_dot(const uint4& q, uint32_t lane_base, con
   return h2sum(hadd2_u(hadd2_u(c0, c1), hadd2_u(c2, c3)));
 }
 
-template <bool PACKED, bool REGTAB, int CPW, int DEPTH>
+template <bool PACKED, bool REGTAB, int CPW, int DEPTH, int SUB>
 __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs p) {
+  constexpr int kColStage = col_stage_bytes(SUB);
+  constexpr int kGroupRows = 4 * SUB;  // weight rows of one item
   static_assert(DEPTH % CPW == 0, "the ring holds whole row groups");
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int rs = lane >> 3, pc = lane & 7;  // row of the sub-item, 16-byte piece of the chunk
   const int G = gridDim.x, cta = blockIdx.x;
   constexpr int kXPerChunk = PACKED ? 16 : 8;  // fp16 pairs a lane keeps per chunk
-  constexpr int kRgDepth = DEPTH / CPW;        // row groups (8 rows) in flight per warp
+  constexpr int kRgDepth = DEPTH / CPW;        // row groups in flight per warp
   constexpr int kNormStep = PACKED ? 64 : 32;  // norm bytes between this warp's chunks
 
   const int r_beg = (int)((long long)p.N * cta / G), r_end = (int)((long long)p.N * (cta + 1) / G);
-  const int n_rg = (r_end - r_beg + 7) >> 3;
+  const int n_rg = (r_end - r_beg + kGroupRows - 1) / kGroupRows;
   int cnt = (p.n_chunks - w + kRowWarps - 1) / kRowWarps;  // chunks w, w+16, ... of this warp
   cnt = cnt < 0 ? 0 : (cnt > CPW ? CPW : cnt);
 
@@ -415,24 +418,27 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
   uint8_t* ring_g = reinterpret_cast<uint8_t*>(part) + kPassRows * kPartStride * 4 + (size_t)w * (DEPTH * kColStage);
   const uint32_t st_base = smem_u32(ring_g), st_end = st_base + DEPTH * kColStage;
 
-  // ---- code stream.  An item is 8 weight rows x 128 bytes: lane (rs, pc) copies its 16
-  // bytes of rows rs and rs + 4 of the group.  The ring slot of item (row group rg, chunk
+  // ---- code stream.  An item is 4 SUB weight rows x 128 bytes: lane (rs, pc) copies its 16
+  // bytes of rows rs, rs + 4, ... of the group.  The ring slot of item (row group rg, chunk
   // slot j) is (rg % kRgDepth) * CPW + j, so the refill issued after item (rg, j) is item
   // (rg + kRgDepth, j): same slot, same j, and the source is a running pointer plus a
   // compile-time offset.  One copy group per slot, empty for slots the warp does not
   // have, so the group count the math waits on is a constant.  Rows past the end of the
   // matrix are not fetched (their sums are never stored).
   const uint8_t* cptr_f = p.codes + (int64_t)(r_beg + rs) * p.ld_codes + (size_t)w * 128 + pc * 16;
-  const uint8_t* nptr_f = p.norms + (int64_t)(r_beg + (lane & 7)) * p.ld_norms + (PACKED ? (size_t)w * 4 : (size_t)(w & ~1) * 2);
-  const int64_t chalf = 4 * p.ld_codes, cstep = 8 * p.ld_codes, nstep = 8 * p.ld_norms;
+  const uint8_t* nptr_f = p.norms + (int64_t)(r_beg + (lane & (kGroupRows - 1))) * p.ld_norms + (PACKED ? (size_t)w * 4 : (size_t)(w & ~1) * 2);
+  const int64_t csub = 4 * p.ld_codes, cstep = kGroupRows * p.ld_codes, nstep = kGroupRows * p.ld_norms;
   int rg_f = 0;
-  bool ok0 = r_beg + rs < p.N, ok1 = r_beg + 4 + rs < p.N, nok = lane < 8 && r_beg + lane < p.N;
+  // sub-item s of the group being fetched covers rows r_beg + kGroupRows rg_f + 4 s .. + 3: skipped
+  // as a whole beyond the CTA's rows, per row beyond the matrix
+  int row_f = r_beg + rs;  // this lane's row in sub-item 0
   const uint32_t q_off = lane * 16;
   auto fetch_item = [&](uint32_t st, int j) {
     if (j < cnt && rg_f < n_rg) {
-      if (ok0) cp_async16(st + q_off, cptr_f + j * 2048);
-      if (ok1) cp_async16(st + kItemBytes + q_off, cptr_f + chalf + j * 2048);
-      if (nok) cp_async4(st + 2 * kItemBytes + lane * 4, nptr_f + j * kNormStep);
+#pragma unroll
+      for (int sb = 0; sb < SUB; ++sb)
+        if (row_f + 4 * sb - rs < r_end && row_f + 4 * sb < p.N) cp_async16(st + sb * kItemBytes + q_off, cptr_f + sb * csub + j * 2048);
+      if (lane < kGroupRows && row_f - rs + lane < p.N) cp_async4(st + SUB * kItemBytes + lane * 4, nptr_f + j * kNormStep);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -440,10 +446,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
     ++rg_f;
     cptr_f += cstep;
     nptr_f += nstep;
-    const int r0 = r_beg + 8 * rg_f;
-    ok0 = r0 + rs < p.N;
-    ok1 = r0 + 4 + rs < p.N;
-    nok = lane < 8 && r0 + lane < p.N;
+    row_f += kGroupRows;
   };
 #pragma unroll
   for (int d = 0; d < kRgDepth; ++d) {
@@ -533,27 +536,32 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
 
   // ---- the item line, in passes of kPassRows rows
   const int n_warps_used = p.n_chunks < kRowWarps ? p.n_chunks : kRowWarps;
-  const uint32_t norm_off = 2 * kItemBytes + rs * 4 + (PACKED ? (pc >> 2) * 2 : (w & 1) * 2);
+  const uint32_t norm_off = SUB * kItemBytes + rs * 4 + (PACKED ? (pc >> 2) * 2 : (w & 1) * 2);
   uint32_t st_rg = st_base;
-  for (int rg0 = 0; rg0 < n_rg; rg0 += kPassRows / 8) {
-    const int rg1 = n_rg < rg0 + kPassRows / 8 ? n_rg : rg0 + kPassRows / 8;
+  for (int rg0 = 0; rg0 < n_rg; rg0 += kPassRows / kGroupRows) {
+    const int rg1 = n_rg < rg0 + kPassRows / kGroupRows ? n_rg : rg0 + kPassRows / kGroupRows;
     if (cnt > 0) {
       uint32_t part_s = smem_u32(part) + (rs * kPartStride + w) * 4;
       for (int rg = rg0; rg < rg1; ++rg) {
-        float acc0 = 0.f, acc1 = 0.f;
+        const int rows_left = r_end - r_beg - kGroupRows * rg;  // sub-items beyond the CTA's rows were not fetched
+        float acc[SUB];
+#pragma unroll
+        for (int sb = 0; sb < SUB; ++sb) acc[sb] = 0.f;
 #pragma unroll
         for (int j = 0; j < CPW; ++j) {
           asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
           const uint32_t st = st_rg + j * kColStage;
           if (j < cnt) {
-            const uint4 q0 = lds128(st + q_off), q1 = lds128(st + kItemBytes + q_off);
-            unsigned short nh0, nh1;
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh0) : "r"(st + norm_off));
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh1) : "r"(st + norm_off + 16));
-            const float s0 = reg_dot<PACKED, REGTAB>(q0, lane_base, tb, xr[j]);
-            const float s1 = reg_dot<PACKED, REGTAB>(q1, lane_base, tb, xr[j]);
-            acc0 = fmaf(__half2float(__ushort_as_half(nh0)), s0, acc0);
-            acc1 = fmaf(__half2float(__ushort_as_half(nh1)), s1, acc1);
+#pragma unroll
+            for (int sb = 0; sb < SUB; ++sb) {
+              if (4 * sb < rows_left) {  // warp-uniform
+                const uint4 q = lds128(st + sb * kItemBytes + q_off);
+                unsigned short nh;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(nh) : "r"(st + norm_off + sb * 16));
+                const float sdot = reg_dot<PACKED, REGTAB>(q, lane_base, tb, xr[j]);
+                acc[sb] = fmaf(__half2float(__ushort_as_half(nh)), sdot, acc[sb]);
+              }
+            }
           }
           __syncwarp();  // every lane has read the slot before it is refilled
           fetch_item(st, j);
@@ -563,19 +571,20 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
         if (st_rg == st_end) st_rg = st_base;
 #pragma unroll
         for (int m = 1; m <= 4; m <<= 1) {
-          acc0 += __shfl_xor_sync(0xffffffffu, acc0, m);
-          acc1 += __shfl_xor_sync(0xffffffffu, acc1, m);
+#pragma unroll
+          for (int sb = 0; sb < SUB; ++sb) acc[sb] += __shfl_xor_sync(0xffffffffu, acc[sb], m);
         }
         if (pc == 0) {
-          asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_s), "f"(acc0) : "memory");
-          asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_s + 4 * kPartStride * 4), "f"(acc1) : "memory");
+#pragma unroll
+          for (int sb = 0; sb < SUB; ++sb)
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_s + sb * (4 * kPartStride * 4)), "f"(acc[sb]) : "memory");
         }
-        part_s += 8 * kPartStride * 4;
+        part_s += kGroupRows * kPartStride * 4;
       }
     }
     __syncthreads();
-    for (int r = tid; r < 8 * (rg1 - rg0); r += kRowThreads) {
-      const int row = r_beg + 8 * rg0 + r;
+    for (int r = tid; r < kGroupRows * (rg1 - rg0); r += kRowThreads) {
+      const int row = r_beg + kGroupRows * rg0 + r;
       if (row < r_end) {
         float s = 0.f;
         for (int ww = 0; ww < n_warps_used; ++ww) s += part[r * kPartStride + ww];
@@ -590,10 +599,15 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
 
 template <bool PACKED, bool REGTAB, int CPW>
 static int launch_cols(const ColArgs& a, int G, cudaStream_t st) {
-  constexpr int DEPTH = CPW == 4 ? 8 : 6;  // items (1 KB of codes) in flight per warp
+  // Sub-items (4 rows each) per step = independent decode-multiply chains per lane.  Byte codes, whose
+  // every weight is a table lookup of its own, gain from four (measured 0.3 us per launch on the
+  // 4096-wide layers); nibble codes are as fast or faster with two and need fewer registers.
+  constexpr int SUB = (!PACKED && CPW <= 3) ? 4 : 2;
+  // items in flight per warp: 6 to 8 KB of codes
+  constexpr int DEPTH = SUB == 4 ? (CPW == 3 ? 3 : 4) : (CPW == 4 ? 8 : 6);
   const unsigned dyn_bytes = (REGTAB ? 0u : (unsigned)kLutBytes) + kRowWarps * CPW * 512u + kPassRows * kPartStride * 4u +
-                             kRowWarps * DEPTH * (unsigned)kColStage;
-  auto kfn = gemv_cols_kernel<PACKED, REGTAB, CPW, DEPTH>;
+                             kRowWarps * DEPTH * (unsigned)col_stage_bytes(SUB);
+  auto kfn = gemv_cols_kernel<PACKED, REGTAB, CPW, DEPTH, SUB>;
   static thread_local bool configured[16] = {false};
   int dev = 0;
   PE_CUDA_TRY(cudaGetDevice(&dev));
@@ -601,17 +615,7 @@ static int launch_cols(const ColArgs& a, int G, cudaStream_t st) {
     PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_bytes));
     if (dev < 16) configured[dev] = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(G);
-  cfg.blockDim = dim3(kRowThreads);
-  cfg.dynamicSmemBytes = dyn_bytes;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  PE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, a));
+  PE_CUDA_TRY(launch_pdl(kfn, dim3(G), dim3(kRowThreads), dyn_bytes, st, a));
   return PE_OK;
 }
 
@@ -636,7 +640,7 @@ static int gemv_cols_try(const void* codes, int packed, int64_t ld_codes, const 
   const int n_chunks = (int)(row_bytes / 128);
   const int cpw = (n_chunks + kRowWarps - 1) / kRowWarps;
   if (cpw > 4) return 1;
-  const int G = out_f / 16 < sms ? out_f / 16 : sms;  // at least two row groups per CTA
+  const int G = out_f / 32 < sms ? out_f / 32 : sms;  // at least two row groups per CTA
   if (G < 1 || (long long)out_f * n_chunks < (long long)G * kRowWarps * 16) return 1;  // < 2 items per warp
   ColArgs a;
   a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
