@@ -280,6 +280,8 @@ def moe_layer(a, dev, rank, world):
     T = a.tokens
     e_local = E // world
     method = PolarQuantMoEMethod(3, 4)
+    if a.moe_grouped_rows is not None:
+        method.GROUPED_MAX_ROWS_PER_EXPERT = a.moe_grouped_rows
     layer = torch.nn.Module()
     g = torch.Generator(device=dev).manual_seed(4242 + rank)
     hp, ip = 2688, 1920
@@ -389,6 +391,8 @@ def main():
     ap.add_argument("--nccl-allreduce", action="store_true", help="model workload: NCCL all-reduce instead of the fused peer-memory epilogue")
     ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
     ap.add_argument("--tokens", type=int, default=64, help="tokens for --workload moe (1 / 64 / 2048)")
+    ap.add_argument("--moe-grouped-rows", type=int, default=None,
+                    help="moe workload: average rows per expert up to which the grouped launches are used (default: the method's)")
     ap.add_argument("--probe", default=None, metavar="PROJ",
                     help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
     a = ap.parse_args()

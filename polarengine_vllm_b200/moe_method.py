@@ -134,9 +134,10 @@ class PolarQuantMoEMethod:
             topk_weights, topk_ids = route_softmax_topk(a, int(b), bool(renorm))
         return self.moe_forward(layer, x, topk_weights, topk_ids, expert_map)
 
-    # average (token, expert) pairs per local expert up to which the grouped decode-size
-    # launches are used; beyond it every expert has a tensor-core-sized batch of its own
-    GROUPED_MAX_ROWS_PER_EXPERT = 32
+    # average (token, expert) pairs per local expert up to which the grouped launches are
+    # used; beyond it every expert has enough rows to fill the tensor-core kernel by itself
+    # (measured on 128 experts: grouped 6.5 ms against 21.8 ms per-expert at 128 rows each)
+    GROUPED_MAX_ROWS_PER_EXPERT = 512
 
     def moe_forward(self, layer, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                     expert_map: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -145,10 +146,12 @@ class PolarQuantMoEMethod:
         nothing read back to the host.  Prefill-size batches: per-expert tensor-core matmuls."""
         pairs = topk_ids.numel()
         if pairs <= self.GROUPED_MAX_ROWS_PER_EXPERT * layer.w13_codes.shape[0] and x.dtype in (torch.float16, torch.bfloat16):
-            return self._moe_forward_grouped(layer, x, topk_weights, topk_ids, expert_map)
+            out = self._moe_forward_grouped(layer, x, topk_weights, topk_ids, expert_map)
+            if out is not None:
+                return out
         return self._moe_forward_per_expert(layer, x, topk_weights, topk_ids, expert_map)
 
-    def _moe_forward_grouped(self, layer, x, topk_weights, topk_ids, expert_map) -> torch.Tensor:
+    def _moe_forward_grouped(self, layer, x, topk_weights, topk_ids, expert_map) -> Optional[torch.Tensor]:
         lead = x.shape[:-1]
         h, i = layer.moe_hidden, layer.moe_inter
         hp, ip = layer.moe_hidden_padded, layer.moe_inter_padded
@@ -165,19 +168,18 @@ class PolarQuantMoEMethod:
         # rows per problem: 8 while experts see few tokens (lighter kernel), else 16
         rpp = 8 if pairs <= 6 * n_local else 16
         max_problems = min(n_local, pairs) + pairs // rpp
+        l = nv.lib()
+        if min(l.pe_gemv_grouped_workspace_bytes(max_problems, 2 * i, hp), l.pe_gemv_grouped_workspace_bytes(max_problems, h, ip)) == 0:
+            return None  # more problems than the scratch counter zone holds: the caller takes the per-expert path
         tok_sorted = torch.empty(pairs, dtype=torch.int32, device=dev)   # token of every grouped row
         pos = torch.empty(pairs, dtype=torch.int32, device=dev)          # grouped row of every pair (-1: other rank)
         desc = torch.empty(max_problems, 4, dtype=torch.int32, device=dev)
-        l = nv.lib()
         st = nv.stream_ptr(dev)
         nv.check(l.pe_moe_plan(ids.data_ptr(), emap.data_ptr() if emap is not None else None, pairs, k, n_local, rpp,
                                max_problems, tok_sorted.data_ptr(), pos.data_ptr(), desc.data_ptr(), st), "pe_moe_plan")
 
         def grouped(codes, packed, norms, ct, xin, x_rows, in_f, kp, y):
-            need = l.pe_gemv_grouped_workspace_bytes(max_problems, y.shape[1], kp)
-            if need == 0:
-                raise RuntimeError("pe_gemv_grouped: too many problems for the scratch counter zone")
-            ws = nv.grouped_scratch(dev, need)
+            ws = nv.grouped_scratch(dev, l.pe_gemv_grouped_workspace_bytes(max_problems, y.shape[1], kp))
             nv.check(l.pe_gemv_grouped(codes.data_ptr(), int(packed), codes.stride(1) * codes.element_size(),
                                        codes.stride(0) * codes.element_size(), norms.data_ptr(), norms.stride(1), norms.stride(0),
                                        ct.data_ptr(), ct.numel(), xin.data_ptr(), nv.PE_X_RAW, nv.dtype_code(xin), xin.stride(0),
