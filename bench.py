@@ -350,13 +350,15 @@ def moe_layer(a, dev, rank, world):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"moe_layer (BASELINE configs[4]): 128 experts top-8, hidden 2688, intermediate 1856, "
                                    f"gate/up Q3 down Q4, {T} tokens", "parallelism": f"ep{world}",
-                       "path": "two grouped launches (pe_gemv_grouped), CUDA graph" if grouped else "per-expert tensor-core matmuls, eager",
+                       "path": ("two grouped tcgen05 launches (pe_gemm_grouped), CUDA graph" if T * K >= method.TENSOR_CORE_MIN_ROWS_PER_EXPERT * e_local
+                                else "two grouped decode-size launches (pe_gemv_grouped), CUDA graph") if grouped
+                               else "per-expert tensor-core matmuls, eager",
                        "l2_defeat": "expert weights 970 MB >> L2"},
             "active_experts": active, "expert_bytes_per_step": active * per_expert,
             "weight_gbs": active * per_expert / (ms / 1e3) / 1e9,
             "hbm_frac_of_measured": active * per_expert / (ms / 1e3) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)) / world,
             "tflops": flops / (ms / 1e3) / 1e12, "clocks": sampler.summary(),
-            "gpu_launches": steps * (3 if grouped else 2 * min(active, e_local))}))
+            "gpu_launches": steps * (5 if grouped else 2 * min(active, e_local))}))
     finish(world)
 
 

@@ -163,6 +163,23 @@ int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, int64_t cod
                     int64_t ld_y, const int32_t* problems, int max_problems, int max_rows, int out_f,
                     int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- grouped prefill-size matmul: the experts of a mixture layer on the tensor cores -----
+ * pe_gemm over a stack of matrices (expert e's codes directly after expert e-1's:
+ * codes_stride == out_f * ld_codes; norms + e * norms_stride halves).  expert_rows is a
+ * DEVICE array of n_experts (first row, row count) pairs, ascending and contiguous (from
+ * pe_moe_plan): rows first .. first + count - 1 of the row list -- row x_rows[j] of x when
+ * x_rows is not NULL, else row j -- are multiplied with expert e and written to the same
+ * rows of y.  `rows` = length of the row list (pairs); rows past the last expert's range
+ * are ignored.  The tile list is built on the device, nothing is read back.  Replaces the
+ * per-expert loop of nemotron_offload.py:190-226 for batches where every expert has many
+ * rows; the reference's vLLM path runs vLLM's bf16 fused MoE here (moe_method.py:82-89). */
+size_t pe_gemm_grouped_workspace_bytes(int n_experts, int rows, int out_f, int in_f_padded);
+int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, int64_t codes_stride, const void* norms,
+                    int64_t ld_norms, int64_t norms_stride, const float* ct_scaled, int n_levels, const void* x,
+                    int x_kind, int x_dtype, int64_t ld_x, int in_f, const int32_t* x_rows, void* y, int y_dtype,
+                    int64_t ld_y, const int32_t* expert_rows, int n_experts, int rows, int out_f, int in_f_padded,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- mixture-of-experts bookkeeping on the device ----------------------------------
  * pe_moe_plan groups the (token, slot) pairs of a routing decision by local expert:
  *   topk_ids (n_pairs = tokens * top_k, int64, token-major); expert_map (optional, int64,
@@ -170,13 +187,16 @@ int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, int64_t cod
  *   row_token[r] = token of grouped row r (the x_rows list of pe_gemv_grouped),
  *   pos[pair] = grouped row of the pair or -1 if its expert lives on another rank,
  *   problems = the problem list of pe_gemv_grouped with at most rows_per_problem rows each
- *   (max_problems >= min(experts, pairs) + pairs / rows_per_problem entries).
+ *   (max_problems >= min(experts, pairs) + pairs / rows_per_problem entries),
+ *   expert_rows (optional) = (first grouped row, row count) per local expert, the input of
+ *   pe_gemm_grouped.
  * pe_moe_combine: out[t, :] = sum_j topk_weights[t, j] * y[pos[t * top_k + j], :] (pairs
  *   with pos < 0 contribute nothing), y fp32 (rows, hidden), out fp32/fp16/bf16.
  * Together with pe_gemv_grouped they replace the per-expert Python loop of the reference's
  * MoE layer (nemotron_offload.py:190-226: index tokens, run the expert, index_add). */
 int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, int n_pairs, int top_k, int n_local_experts,
-                int rows_per_problem, int max_problems, int32_t* row_token, int32_t* pos, int32_t* problems, void* stream);
+                int rows_per_problem, int max_problems, int32_t* row_token, int32_t* pos, int32_t* problems,
+                int32_t* expert_rows, void* stream);
 int pe_moe_combine(const float* y, int64_t ld_y, const int32_t* pos, const float* topk_weights, int tokens, int top_k,
                    void* out, int out_dtype, int64_t ld_out, int hidden, void* stream);
 

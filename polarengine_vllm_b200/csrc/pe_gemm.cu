@@ -52,7 +52,24 @@ struct GemmArgs {
   int nc;         // code stages
   int* status;
   unsigned long long* prof;  // developer builds (-DPE_PROFILE): cycles spent in each wait, per CTA
+  // grouped launch over a stack of matrices (the experts of a mixture layer): tile list on the device
+  const int4* gtiles;        // per tile: (first activation row, rows, first weight row inside the expert, expert)
+  const int* n_gtiles;       // number of tiles in the list
+  int64_t grp_norm_stride;   // halves between the norms of consecutive experts
 };
+
+// Activation rows [m0, m_end) and weight rows n0 .. n0 + 255 of an expert; crow0 = row of the code tensor.
+struct TileCoord { int m0, m_end, n0, crow0, expert; };
+__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& p, int tile) {
+  TileCoord t;
+  if (p.gtiles) {
+    const int4 d = p.gtiles[tile];
+    t.m0 = d.x; t.m_end = d.x + d.y; t.n0 = d.z; t.expert = d.w; t.crow0 = d.w * p.N + d.z;
+  } else {
+    t.m0 = (tile % p.tiles_m) * kTileM; t.m_end = p.M; t.n0 = (tile / p.tiles_m) * kTileN; t.expert = 0; t.crow0 = t.n0;
+  }
+  return t;
+}
 
 // ---- PTX wrappers -----------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -223,21 +240,21 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
   const uint32_t tmem = *tmem_slot;
 
   const int ksteps = p.K / kStepK;
-  const int n_tiles = p.tiles_m * p.tiles_n;
+  const int n_tiles = p.gtiles ? *p.n_gtiles : p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
     // ---------------- TMA producer: activations and codes ----------------
     if (lane == 0) {
       int it = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kTileM;
-        const int n0 = (tile / p.tiles_m) * kTileN;
-        const bool two = m0 + 128 < p.M;
+        const TileCoord tc = tile_coord(p, tile);
+        const int m0 = tc.m0;
+        const bool two = m0 + 128 < tc.m_end;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int sc = it % p.nc;
           if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6, p.prof)) goto done_producer;
           mbar_expect_tx(full_c(sc), kCodeStage);
-          tma_load_2d(base + c_off + sc * kCodeStage, &cmap, ks * kCodeRow, n0, full_c(sc));
+          tma_load_2d(base + c_off + sc * kCodeStage, &cmap, ks * kCodeRow, tc.crow0, full_c(sc));
           const int sx = it % kXStages;
           if (!mbar_wait(empty_x(sx), ((it / kXStages) & 1) ^ 1, abort_flag, p.status, 1, p.prof)) goto done_producer;
           mbar_expect_tx(full_x(sx), two ? 2 * kXTileBytes : kXTileBytes);
@@ -252,8 +269,8 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
     if (lane == 0) {
       int it = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kTileM;
-        const bool two = m0 + 128 < p.M;
+        const TileCoord tc = tile_coord(p, tile);
+        const bool two = tc.m0 + 128 < tc.m_end;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int sx = it % kXStages, sw = it % kWStages;
           if (!mbar_wait(full_x(sx), (it / kXStages) & 1, abort_flag, p.status, 2, p.prof)) goto done_mma;
@@ -290,13 +307,13 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
     const int sw7 = r & 7;
     int it = 0, tcount = 0;
     for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-      const int m0 = (tile % p.tiles_m) * kTileM;
-      const int n0 = (tile / p.tiles_m) * kTileN;
-      const bool two = m0 + 128 < p.M;
+      const TileCoord tc = tile_coord(p, tile);
+      const int m0 = tc.m0, n0 = tc.n0;
+      const bool two = m0 + 128 < tc.m_end;
       int row = n0 + r;
       const bool row_ok = row < p.N;
       if (!row_ok) row = p.N - 1;
-      const __half* nrow = p.norms + (int64_t)row * p.ld_norms;
+      const __half* nrow = p.norms + (int64_t)tc.expert * p.grp_norm_stride + (int64_t)row * p.ld_norms;
       bool dead = false;
       uint4 nq = make_uint4(0, 0, 0, 0);  // norms of eight consecutive blocks
       for (int ks = 0; ks < ksteps; ++ks, ++it) {
@@ -384,7 +401,7 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
           tmem_ld32(trow + cc * 32, rr);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           const int nb0 = n0 + cc * 32;
-          if (m < p.M && nb0 < p.N) {
+          if (m < tc.m_end && nb0 < p.N) {
             const bool full = nb0 + 32 <= p.N && (p.ld_y % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
             if (full && p.y_dtype != PE_F32) {
               uint32_t o[16];
@@ -432,16 +449,21 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
 
 // Activation preparation: (pad + FWHT for raw input), bf16, kernel K order.
 // One warp per (row, 128-block).
+// Grouped launches: row m of the prepared matrix is row x_rows[m] of x (a gather by token id), and only the first
+// valid_rows[0] + valid_rows[1] rows exist (the rest of the list is undefined and is written as zeros).
 __global__ void __launch_bounds__(256) gemm_prep_kernel(const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f,
-                                                        __nv_bfloat16* xq, int M, int K, int pair_layout) {
+                                                        __nv_bfloat16* xq, int M, int K, int pair_layout, const int* x_rows,
+                                                        const int* valid_rows) {
   const int lane = threadIdx.x & 31;
   const int nb = K / kBlock;
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (warp >= (int64_t)M * nb) return;
   const int m = (int)(warp / nb), blk = (int)(warp - (int64_t)m * nb);
   const bool vin = (ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  const bool live = !valid_rows || m < valid_rows[0] + valid_rows[1];
+  const int64_t src_row = (x_rows && live) ? x_rows[m] : m;
   float v[4];
-  load4_as_float(x, x_dtype, (int64_t)m * ld_x, blk * kBlock + lane * 4, x_kind == PE_X_RAW ? in_f : K, vin, v);
+  load4_as_float(x, x_dtype, src_row * ld_x, blk * kBlock + lane * 4, live ? (x_kind == PE_X_RAW ? in_f : K) : 0, vin, v);
   if (x_kind == PE_X_RAW) warp_fwht128(v, lane);
   __nv_bfloat16* dst = xq + (int64_t)m * K + blk * kBlock;
   if (pair_layout) {
@@ -453,6 +475,34 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const void* x, int x_kin
                                                              pack_bf16(v[2], o[2]), pack_bf16(v[3], o[3]));
   } else {
     *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+  }
+}
+
+// Tile list of a grouped launch from the experts' row ranges (first, count): for every expert its
+// ceil(count / 256) activation tiles x tiles_n weight tiles, weight tiles of one activation tile adjacent
+// (CTAs that run side by side then share the activation tile in L2).  One thread scans, the block writes.
+__global__ void __launch_bounds__(256) gemm_group_tiles_kernel(const int* expert_rows, int n_experts, int tiles_n, int max_tiles,
+                                                               int4* tiles, int* n_tiles) {
+  __shared__ int first_tile[1025];
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      first_tile[e] = t;
+      t += ((expert_rows[2 * e + 1] + kTileM - 1) / kTileM) * tiles_n;
+    }
+    first_tile[n_experts] = t;
+    *n_tiles = t < max_tiles ? t : max_tiles;
+  }
+  __syncthreads();
+  for (int e = 0; e < n_experts; ++e) {
+    const int first = expert_rows[2 * e], cnt = expert_rows[2 * e + 1];
+    const int nt = first_tile[e + 1] - first_tile[e];
+    for (int i = threadIdx.x; i < nt; i += blockDim.x) {
+      const int mt = i / tiles_n, ntile = i - mt * tiles_n;
+      const int rows = cnt - mt * kTileM;
+      if (first_tile[e] + i < max_tiles)
+        tiles[first_tile[e] + i] = make_int4(first + mt * kTileM, rows < kTileM ? rows : kTileM, ntile * kTileN, e);
+    }
   }
 }
 
@@ -514,7 +564,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   const int nb = in_f_padded / kBlock;
   const int64_t warps = (int64_t)m * nb;
   gemm_prep_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, m, in_f_padded,
-                                                                 packed ? 1 : 0);
+                                                                 packed ? 1 : 0, nullptr, nullptr);
   PE_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap map;
@@ -537,6 +587,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   a.tiles_n = (out_f + kTileN - 1) / kTileN;
   a.status = status;
   a.prof = g_gemm_prof;
+  a.gtiles = nullptr; a.n_gtiles = nullptr; a.grp_norm_stride = 0;
   a.lut_bytes = (packed ? 256 : n_levels) * 128;
   const int code_row = packed ? 32 : 64;
   const int code_stage = kTileN * code_row;
@@ -556,6 +607,111 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
 
   const int tiles = a.tiles_m * a.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
+  if (packed) {
+    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    gemm_kernel<true><<<grid, kGemmThreads, smem_bytes, st>>>(a, map, cmap);
+  } else {
+    PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    gemm_kernel<false><<<grid, kGemmThreads, smem_bytes, st>>>(a, map, cmap);
+  }
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
+
+// ---- grouped launch: the experts of a mixture layer, prefill-size batches ----------------------------
+// workspace: [status, 256 B][tile count, 256 B][tile list][bf16 activations rows x K]
+static int grouped_max_tiles(int n_experts, int rows, int out_f) {
+  return (n_experts + rows / kTileM) * ((out_f + kTileN - 1) / kTileN);
+}
+
+extern "C" size_t pe_gemm_grouped_workspace_bytes(int n_experts, int rows, int out_f, int in_f_padded) {
+  if (n_experts < 1 || n_experts > 1024 || rows < 1 || out_f < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
+  const size_t list = ((size_t)grouped_max_tiles(n_experts, rows, out_f) * 16 + 255) & ~(size_t)255;
+  return 512 + list + (size_t)rows * in_f_padded * 2;
+}
+
+extern "C" int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, int64_t codes_stride, const void* norms,
+                               int64_t ld_norms, int64_t norms_stride, const float* ct_scaled, int n_levels, const void* x,
+                               int x_kind, int x_dtype, int64_t ld_x, int in_f, const int32_t* x_rows, void* y, int y_dtype,
+                               int64_t ld_y, const int32_t* expert_rows, int n_experts, int rows, int out_f, int in_f_padded,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+  if (!codes || !norms || !ct_scaled || !x || !y || !expert_rows || !workspace) return PE_ERR_ARG;
+  if (n_experts < 1 || rows < 1 || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
+  if (n_experts > 1024) return PE_ERR_LIMIT;
+  if (x_kind != PE_X_ROTATED && x_kind != PE_X_RAW) return PE_ERR_ARG;
+  if (x_dtype < PE_F32 || x_dtype > PE_BF16 || y_dtype < PE_F32 || y_dtype > PE_BF16) return PE_ERR_ARG;
+  if (n_levels < 2 || n_levels > 256 || (packed && n_levels > 16)) return PE_ERR_ARG;
+  if (in_f_padded % kBlock) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15)) return PE_ERR_ALIGN;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return PE_ERR_ALIGN;
+  // the experts' code matrices are addressed as one tall 2-D tensor: they must follow each other
+  if (codes_stride != (int64_t)out_f * ld_codes) return PE_ERR_ARG;
+  if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  if (ld_x < (x_kind == PE_X_RAW ? in_f : in_f_padded) || ld_y < out_f) return PE_ERR_ARG;
+  if ((int64_t)n_experts * out_f > 0x7fffffff) return PE_ERR_LIMIT;
+  const size_t need = pe_gemm_grouped_workspace_bytes(n_experts, rows, out_f, in_f_padded);
+  if (need == 0) return PE_ERR_SHAPE;
+  if (workspace_bytes < need) return PE_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int sms = sm_count();
+  if (sms <= 0) return PE_ERR_CUDA;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return PE_ERR_CUDA;
+
+  const int max_tiles = grouped_max_tiles(n_experts, rows, out_f);
+  const size_t list_bytes = ((size_t)max_tiles * 16 + 255) & ~(size_t)255;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int* status = reinterpret_cast<int*>(ws);
+  int* n_tiles = reinterpret_cast<int*>(ws + 256);
+  int4* tiles = reinterpret_cast<int4*>(ws + 512);
+  __nv_bfloat16* xq = reinterpret_cast<__nv_bfloat16*>(ws + 512 + list_bytes);
+  PE_CUDA_TRY(cudaMemsetAsync(status, 0, 4, st));
+  const int tiles_n = (out_f + kTileN - 1) / kTileN;
+  gemm_group_tiles_kernel<<<1, 256, 0, st>>>(expert_rows, n_experts, tiles_n, max_tiles, tiles, n_tiles);
+  PE_CUDA_TRY(cudaGetLastError());
+  const int nb = in_f_padded / kBlock;
+  const int64_t warps = (int64_t)rows * nb;
+  gemm_prep_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, rows, in_f_padded,
+                                                                 packed ? 1 : 0, x_rows, expert_rows + 2 * (n_experts - 1));
+  PE_CUDA_TRY(cudaGetLastError());
+
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)in_f_padded, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)in_f_padded * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kStepK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return PE_ERR_CUDA;
+
+  GemmArgs a;
+  a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
+  a.norms = static_cast<const __half*>(norms); a.ld_norms = ld_norms;
+  a.ct = ct_scaled; a.n_levels = n_levels;
+  a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  a.bias = nullptr;
+  a.M = rows; a.N = out_f; a.K = in_f_padded;
+  a.tiles_m = 1; a.tiles_n = tiles_n;
+  a.status = status;
+  a.prof = nullptr;
+  a.gtiles = tiles; a.n_gtiles = n_tiles; a.grp_norm_stride = norms_stride;
+  a.lut_bytes = (packed ? 256 : n_levels) * 128;
+  const int code_row = packed ? 32 : 64;
+  const int code_stage = kTileN * code_row;
+  const unsigned fixed = kXStages * 2 * kXTileBytes + kWStages * kWTileBytes + a.lut_bytes + 256 + 1024;
+  a.nc = (fixed + 3 * code_stage <= 232448u) ? 3 : 2;
+  const unsigned smem_bytes = fixed + a.nc * code_stage;
+
+  CUtensorMap cmap;
+  const cuuint64_t cdims[2] = {(cuuint64_t)(packed ? in_f_padded / 2 : in_f_padded), (cuuint64_t)n_experts * (cuuint64_t)out_f};
+  const cuuint64_t cstrides[1] = {(cuuint64_t)ld_codes};
+  const cuuint32_t cbox[2] = {(cuuint32_t)code_row, (cuuint32_t)kTileN};
+  if (enc(&cmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(codes), cdims, cstrides, cbox, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return PE_ERR_CUDA;
+
+  const int grid = max_tiles < sms ? max_tiles : sms;
   if (packed) {
     PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     gemm_kernel<true><<<grid, kGemmThreads, smem_bytes, st>>>(a, map, cmap);

@@ -17,7 +17,8 @@ constexpr int kPlanMaxExperts = 1024;
 // combine step finds a pair's row through `pos`.
 __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const int64_t* ids, const int64_t* expert_map, int n_pairs, int top_k,
                                                                 int n_local, int rows_per_problem, int max_problems,
-                                                                int32_t* row_token, int32_t* pos, int4* problems) {
+                                                                int32_t* row_token, int32_t* pos, int4* problems,
+                                                                int32_t* expert_rows) {
   __shared__ int cnt[kPlanMaxExperts];     // pairs per expert, then a running cursor
   __shared__ int first[kPlanMaxExperts];   // first row of the expert in the grouped order
   __shared__ int pfirst[kPlanMaxExperts];  // first problem of the expert
@@ -45,6 +46,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const int64_t* i
   // problem list: expert e owns problems pfirst[e] .. ; unused slots get zero rows
   for (int e = tid; e < n_local; e += kPlanThreads) {
     const int c = cnt[e];
+    if (expert_rows) { expert_rows[2 * e] = first[e]; expert_rows[2 * e + 1] = c; }
     for (int j = 0, p = pfirst[e]; j * rows_per_problem < c && p < max_problems; ++j, ++p) {
       const int rows = c - j * rows_per_problem;
       problems[p] = make_int4(e, first[e] + j * rows_per_problem, rows < rows_per_problem ? rows : rows_per_problem, 0);
@@ -97,7 +99,7 @@ using namespace pe;
 
 extern "C" int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, int n_pairs, int top_k, int n_local_experts,
                            int rows_per_problem, int max_problems, int32_t* row_token, int32_t* pos, int32_t* problems,
-                           void* stream) {
+                           int32_t* expert_rows, void* stream) {
   if (!topk_ids || !row_token || !pos || !problems || n_pairs < 1 || top_k < 1 || max_problems < 1) return PE_ERR_ARG;
   if (rows_per_problem < 1 || rows_per_problem > 16) return PE_ERR_ARG;
   if (n_local_experts < 1 || n_local_experts > kPlanMaxExperts) return PE_ERR_LIMIT;
@@ -107,7 +109,7 @@ extern "C" int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, i
   if (max_problems < worst) return PE_ERR_WORKSPACE;
   moe_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(topk_ids, expert_map, n_pairs, top_k, n_local_experts,
                                                                              rows_per_problem, max_problems, row_token, pos,
-                                                                             reinterpret_cast<int4*>(problems));
+                                                                             reinterpret_cast<int4*>(problems), expert_rows);
   PE_CUDA_TRY(cudaGetLastError());
   return PE_OK;
 }

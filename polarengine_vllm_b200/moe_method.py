@@ -138,6 +138,10 @@ class PolarQuantMoEMethod:
     # used; beyond it every expert has enough rows to fill the tensor-core kernel by itself
     # (measured on 128 experts: grouped 6.5 ms against 21.8 ms per-expert at 128 rows each)
     GROUPED_MAX_ROWS_PER_EXPERT = 512
+    # average rows per expert from which the grouped launches run on the tensor cores (a 256 x 256
+    # tile per expert and weight tile costs the same for 1 or 256 rows; below this the streaming
+    # decode-size kernel is cheaper)
+    TENSOR_CORE_MIN_ROWS_PER_EXPERT = 12
 
     def moe_forward(self, layer, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                     expert_map: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -174,11 +178,26 @@ class PolarQuantMoEMethod:
         tok_sorted = torch.empty(pairs, dtype=torch.int32, device=dev)   # token of every grouped row
         pos = torch.empty(pairs, dtype=torch.int32, device=dev)          # grouped row of every pair (-1: other rank)
         desc = torch.empty(max_problems, 4, dtype=torch.int32, device=dev)
+        expert_rows = torch.empty(n_local, 2, dtype=torch.int32, device=dev)  # (first grouped row, rows) per expert
         st = nv.stream_ptr(dev)
         nv.check(l.pe_moe_plan(ids.data_ptr(), emap.data_ptr() if emap is not None else None, pairs, k, n_local, rpp,
-                               max_problems, tok_sorted.data_ptr(), pos.data_ptr(), desc.data_ptr(), st), "pe_moe_plan")
+                               max_problems, tok_sorted.data_ptr(), pos.data_ptr(), desc.data_ptr(), expert_rows.data_ptr(), st),
+                 "pe_moe_plan")
+        # many rows per expert: the tensor-core kernel over all experts (tile list built on the device);
+        # few: the decode-size kernel, which streams every expert's codes once per 8 or 16 rows
+        tensor_cores = pairs >= self.TENSOR_CORE_MIN_ROWS_PER_EXPERT * n_local
 
         def grouped(codes, packed, norms, ct, xin, x_rows, in_f, kp, y):
+            if tensor_cores and codes.stride(0) == codes.shape[1] * codes.stride(1):
+                need = l.pe_gemm_grouped_workspace_bytes(n_local, pairs, y.shape[1], kp)
+                ws = nv.gemm_workspace(dev, need)
+                nv.check(l.pe_gemm_grouped(codes.data_ptr(), int(packed), codes.stride(1) * codes.element_size(),
+                                           codes.stride(0) * codes.element_size(), norms.data_ptr(), norms.stride(1),
+                                           norms.stride(0), ct.data_ptr(), ct.numel(), xin.data_ptr(), nv.PE_X_RAW,
+                                           nv.dtype_code(xin), xin.stride(0), in_f, x_rows.data_ptr() if x_rows is not None else None,
+                                           y.data_ptr(), nv.dtype_code(y), y.stride(0), expert_rows.data_ptr(), n_local, pairs,
+                                           y.shape[1], kp, ws.data_ptr(), ws.numel(), st), "pe_gemm_grouped")
+                return
             ws = nv.grouped_scratch(dev, l.pe_gemv_grouped_workspace_bytes(max_problems, y.shape[1], kp))
             nv.check(l.pe_gemv_grouped(codes.data_ptr(), int(packed), codes.stride(1) * codes.element_size(),
                                        codes.stride(0) * codes.element_size(), norms.data_ptr(), norms.stride(1), norms.stride(0),
