@@ -212,6 +212,8 @@ def model_decode(a, dev, rank, world):
         out = model.forward(ids_buf, pos)
         ids_buf.copy_(out.view(b, 1))
         pos.add_(1)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()  # from the warm-up on: a query takes longer than a short timed region on a full box
     with torch.cuda.stream(stream):
         for _ in range(3):
             step()
@@ -227,8 +229,6 @@ def model_decode(a, dev, rank, world):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
-        sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(a.new_tokens):
@@ -304,8 +304,11 @@ def moe_layer(a, dev, rank, world):
         return y
 
     stream = torch.cuda.Stream(dev)
-    grouped = T * K <= method.GROUPED_MAX_ROWS_PER_EXPERT * e_local
+    local_pairs = method.expected_local_pairs(T * K, e_local, emap)
+    grouped = local_pairs <= method.GROUPED_MAX_ROWS_PER_EXPERT * e_local
     steps = a.steps if a.steps != 4000 else (200 if grouped else 10)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()  # from the warm-up on: a query takes longer than a short timed region on a full box
     with torch.cuda.stream(stream):
         for _ in range(3):
             step()
@@ -318,8 +321,6 @@ def moe_layer(a, dev, rank, world):
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
-        sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(steps):
@@ -350,7 +351,7 @@ def moe_layer(a, dev, rank, world):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"moe_layer (BASELINE configs[4]): 128 experts top-8, hidden 2688, intermediate 1856, "
                                    f"gate/up Q3 down Q4, {T} tokens", "parallelism": f"ep{world}",
-                       "path": ("two grouped tcgen05 launches (pe_gemm_grouped), CUDA graph" if T * K >= method.TENSOR_CORE_MIN_ROWS_PER_EXPERT * e_local
+                       "path": ("two grouped tcgen05 launches (pe_gemm_grouped), CUDA graph" if local_pairs >= method.TENSOR_CORE_MIN_ROWS_PER_EXPERT * e_local
                                 else "two grouped decode-size launches (pe_gemv_grouped), CUDA graph") if grouped
                                else "per-expert tensor-core matmuls, eager",
                        "l2_defeat": "expert weights 970 MB >> L2"},

@@ -148,12 +148,20 @@ class PolarQuantMoEMethod:
         """y[t] = sum_k w[t,k] * down_e(silu(gate_e(x[t])) * up_e(x[t])), e = ids[t,k]; fp16 out.
         Decode-size batches: two grouped launches over all experts (``pe_gemv_grouped``),
         nothing read back to the host.  Prefill-size batches: per-expert tensor-core matmuls."""
-        pairs = topk_ids.numel()
-        if pairs <= self.GROUPED_MAX_ROWS_PER_EXPERT * layer.w13_codes.shape[0] and x.dtype in (torch.float16, torch.bfloat16):
+        n_local = layer.w13_codes.shape[0]
+        if self.expected_local_pairs(topk_ids.numel(), n_local, expert_map) <= self.GROUPED_MAX_ROWS_PER_EXPERT * n_local \
+                and x.dtype in (torch.float16, torch.bfloat16):
             out = self._moe_forward_grouped(layer, x, topk_weights, topk_ids, expert_map)
             if out is not None:
                 return out
         return self._moe_forward_per_expert(layer, x, topk_weights, topk_ids, expert_map)
+
+    @staticmethod
+    def expected_local_pairs(pairs: int, n_local: int, expert_map: Optional[torch.Tensor]) -> int:
+        """(token, expert) pairs this rank expects to own: all of them without an expert map, else
+        the local share of uniformly routed pairs (kernel choices only; buffers hold every pair)."""
+        n_global = int(expert_map.numel()) if expert_map is not None else n_local
+        return max(1, pairs * n_local // max(n_global, 1))
 
     def _moe_forward_grouped(self, layer, x, topk_weights, topk_ids, expert_map) -> Optional[torch.Tensor]:
         lead = x.shape[:-1]
@@ -170,7 +178,8 @@ class PolarQuantMoEMethod:
         ids = topk_ids.reshape(-1).to(torch.int64).contiguous()
         emap = expert_map.to(device=dev, dtype=torch.int64).contiguous() if expert_map is not None else None
         # rows per problem: 8 while experts see few tokens (lighter kernel), else 16
-        rpp = 8 if pairs <= 6 * n_local else 16
+        local_pairs = self.expected_local_pairs(pairs, n_local, expert_map)
+        rpp = 8 if local_pairs <= 6 * n_local else 16
         max_problems = min(n_local, pairs) + pairs // rpp
         l = nv.lib()
         if min(l.pe_gemv_grouped_workspace_bytes(max_problems, 2 * i, hp), l.pe_gemv_grouped_workspace_bytes(max_problems, h, ip)) == 0:
@@ -185,7 +194,7 @@ class PolarQuantMoEMethod:
                  "pe_moe_plan")
         # many rows per expert: the tensor-core kernel over all experts (tile list built on the device);
         # few: the decode-size kernel, which streams every expert's codes once per 8 or 16 rows
-        tensor_cores = pairs >= self.TENSOR_CORE_MIN_ROWS_PER_EXPERT * n_local
+        tensor_cores = local_pairs >= self.TENSOR_CORE_MIN_ROWS_PER_EXPERT * n_local
 
         def grouped(codes, packed, norms, ct, xin, x_rows, in_f, kp, y):
             if tensor_cores and codes.stride(0) == codes.shape[1] * codes.stride(1):
