@@ -640,8 +640,10 @@ static int gemv_cols_try(const void* codes, int packed, int64_t ld_codes, const 
   const int n_chunks = (int)(row_bytes / 128);
   const int cpw = (n_chunks + kRowWarps - 1) / kRowWarps;
   if (cpw > 4) return 1;
-  const int G = out_f / 32 < sms ? out_f / 32 : sms;  // at least two row groups per CTA
-  if (G < 1 || (long long)out_f * n_chunks < (long long)G * kRowWarps * 16) return 1;  // < 2 items per warp
+  // Small matrices (tensor-parallel shards) are latency bound: as many CTAs as there are groups of 8 rows, up to
+  // one per SM.  Below 128 KB of codes the tile kernel's split along K spreads the few bytes better.
+  const int G = out_f / 8 < sms ? out_f / 8 : sms;
+  if (G < 1 || (long long)out_f * row_bytes < 131072) return 1;
   ColArgs a;
   a.codes = static_cast<const uint8_t*>(codes); a.ld_codes = ld_codes;
   a.norms = static_cast<const uint8_t*>(norms); a.ld_norms = ld_norms * 2;
