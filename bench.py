@@ -303,6 +303,11 @@ def moe_layer(a, dev, rank, world):
             dist.all_reduce(y)
         return y
 
+    if a.probe:  # one layer pass and out: the case captured under ncu
+        step(); step()
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": "moe", "tokens": T}))
+        return
     stream = torch.cuda.Stream(dev)
     local_pairs = method.expected_local_pairs(T * K, e_local, emap)
     grouped = local_pairs <= method.GROUPED_MAX_ROWS_PER_EXPERT * e_local

@@ -334,11 +334,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_rows_kernel(const RowArgs
 //
 // With a single activation row the loop above is bound by shared-memory bandwidth: every
 // 512 bytes of codes drag 2 KB of staged activations through the same port as the ring
-// and the table.  Here an item is EIGHT weight rows x 128 bytes (8 lanes x 16 B per row,
-// two rows per lane) and warp w owns the 128-byte column chunks w, w+16, ... of the CTA's
-// rows, so a lane meets the same few activation slices over and over and keeps them in
-// registers (16 fp16 pairs per chunk, at most CPW chunks), and the two rows of a lane give
-// the scheduler two independent dependency chains.  The price is a reduction per row
+// and the table.  Here an item is 8 or 16 weight rows x 128 bytes (8 lanes x 16 B per row,
+// two or four rows per lane) and warp w owns the 128-byte column chunks w, w+16, ... of the
+// CTA's rows, so a lane meets the same few activation slices over and over and keeps them in
+// registers (16 fp16 pairs per chunk, at most CPW chunks), and the rows of a lane give the
+// scheduler independent dependency chains.  The price is a reduction per row
 // group -- three shuffles over the 8 lanes of a row -- and a sum over the 16 warps' column
 // partials through shared memory, in warp order (bit-reproducible), after every pass of
 // 256 rows.  Each warp rotates only the blocks it owns.
