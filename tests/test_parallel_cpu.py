@@ -73,3 +73,53 @@ def test_row_and_column_parallel_on_two_gloo_ranks():
             p.join(120)
             assert p.exitcode == 0
         assert ret["row"] < 1e-5 and ret["col"] < 1e-6
+
+
+def _moe_worker(rank, world, port, ret):
+    """Expert parallel: every rank evaluates only the experts its placement map keeps
+    (oracle arithmetic), the all-reduce restores the full layer output."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        e, h, i, k, t = 8, 256, 128, 2, 12
+        g = torch.Generator().manual_seed(5)
+        experts = []
+        for _ in range(e):
+            ex = {}
+            for name, (rows, cols, bits) in {"gate": (i, h, 3), "up": (i, h, 3), "down": (h, i, 4)}.items():
+                q = oracle.quantize_tensor(torch.randn(rows, cols, generator=g) * 0.02, bits)
+                ex[name] = (q["codes"], q["norms"], q["ct_scaled"], cols)
+            experts.append(ex)
+        x = torch.randn(t, h, generator=g).half()
+        w, ids = oracle.moe_route(x, (torch.randn(e, h, generator=g) * 0.02).half(), k)
+        full = oracle.moe_forward(x, w, ids, experts)
+        emap = parallel.expert_placement(e, rank, world)
+        local = emap[ids] >= 0                                   # pairs whose expert lives here
+        part = oracle.moe_forward(x, w * local, ids, experts)     # remote pairs weigh nothing
+        dist.all_reduce(part)
+        if rank == 0:
+            ret["moe"] = float((part - full).abs().max() / full.abs().max())
+            ret["share"] = int(local.sum())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_on_two_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = 30100 + os.getpid() % 500
+        procs = [ctx.Process(target=_moe_worker, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(180)
+            assert p.exitcode == 0
+        assert ret["moe"] < 1e-5 and 0 < ret["share"] < 24
+
+
+def test_expected_local_pairs():
+    from polarengine_vllm_b200.moe_method import PolarQuantMoEMethod as M
+    assert M.expected_local_pairs(512, 128, None) == 512
+    assert M.expected_local_pairs(512, 16, parallel.expert_placement(128, 0, 8)) == 64
+    assert M.expected_local_pairs(3, 16, parallel.expert_placement(128, 0, 8)) == 1
