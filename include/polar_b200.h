@@ -96,14 +96,18 @@ int pe_embedding(const void* codes, int packed, int64_t ld_codes, const void* no
  * pe_decode_attention: one new token per sequence.  q (batch, hq, head_dim), caches as
  *   above holding positions 0 .. pos (pos = *pos_dev or pos_host, the token just written);
  *   out (batch, hq * head_dim) = softmax(q K^T / sqrt(head_dim)) V per query head, query head
- *   i reading kv head i / (hq / hkv).  head_dim = 128, hq / hkv in {1, 2, 4, 8}. */
+ *   i reading kv head i / (hq / hkv).  head_dim = 128, hq / hkv in {1, 2, 4, 8}.  With a
+ *   workspace (pe_decode_attention_workspace_bytes; its first 4 KB zero before the first call,
+ *   left zero) the cache positions are split over up to 8 CTAs per kv head; NULL = one CTA. */
 int pe_add_rmsnorm(void* x, const void* delta, int delta_dtype, const void* weight, void* out, int rows, int hidden,
                    float eps, void* stream);
 int pe_rope_cache(const void* qkv, int64_t ld_qkv, const int64_t* pos_dev, int64_t pos_host, void* q_out, void* k_cache,
                   void* v_cache, int batch, int t, int hq, int hkv, int head_dim, int max_len, float theta, void* stream);
 int pe_silu_mul(const void* gate_up, int64_t ld_gu, void* out, int64_t ld_out, int rows, int inter, void* stream);
+size_t pe_decode_attention_workspace_bytes(int batch, int hq, int hkv, int head_dim);
 int pe_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos_dev, int64_t pos_host,
-                        void* out, int batch, int hq, int hkv, int head_dim, int max_len, void* stream);
+                        void* out, int batch, int hq, int hkv, int head_dim, int max_len, void* workspace,
+                        size_t workspace_bytes, void* stream);
 
 /* ---- nibble packing ---------------------------------------------------------
  * int8 codes (out_f, in_f_padded) -> uint8 (out_f, in_f_padded/2), byte i of each

@@ -52,7 +52,8 @@ SIGNATURES = {
     "pe_add_rmsnorm": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, ctypes.c_float, _vp]),
     "pe_rope_cache": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, ctypes.c_float, _vp]),
     "pe_silu_mul": (_i, [_vp, _i64, _vp, _i64, _i, _i, _vp]),
-    "pe_decode_attention": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp]),
+    "pe_decode_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "pe_decode_attention": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pe_gemv_noalloc_max_bytes": (_sz, []),
     "pe_gemv_noalloc": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                              _vp]),

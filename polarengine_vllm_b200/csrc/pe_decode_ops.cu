@@ -151,29 +151,40 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* gu, int64_t
 
 
 // Single-query attention over the KV cache for one decode step (grouped-query form).
-// One CTA per (kv head, sequence): its G = hq / hkv query heads share every K and V row.
+// CTA (kv head, sequence, split): the G = hq / hkv query heads of a kv head share every K
+// and V row; the cache positions 0 .. L-1 are cut into `splits` equal ranges so that a
+// batch-1 step still fills many SMs.
 //  1. scores: thread = cache position (strided); the 16 16-byte pieces of its K row are
 //     requested together (one memory round trip per position), then the full 128-wide dot
 //     per query head with the queries broadcast from shared memory;
-//  2. softmax per query head by one warp each (max, exp, sum);
-//  3. output: thread = (position stride 16, 16-byte piece of the V row), eight rows in
-//     flight per thread; the 16 position groups meet in shared memory.
+//  2. per query head one warp: maximum, exponentials, their sum;
+//  3. weighted V rows: thread = (position stride 16, 16-byte piece of the row), eight rows
+//     in flight per thread; the 16 position groups meet in shared memory;
+//  4. one split: normalise and store.  Several: every CTA leaves (max, sum, weighted rows)
+//     in scratch and takes a ticket; the CTA that draws the last ticket merges the splits
+//     in split order (bit-reproducible) and returns the ticket counter to zero.  Nobody
+//     waits for anybody.
 constexpr int kAttThreads = 256;
 constexpr int kAttMaxGroup = 8;
+constexpr int kAttMaxSplits = 8;
 
 template <int D, int G>
 __device__ __forceinline__ void attention_body(const __half* q, const __half* kb, const __half* vb, __half* out_row, float* att_smem,
-                                               int L, int max_len, float scale) {
+                                               int p_lo, int p_hi, int chunk_cap, float scale, int splits, float* part,
+                                               unsigned* ticket) {
   static_assert(D == 128, "pieces and thread mapping are laid out for 128-wide heads");
+  __shared__ float head_max[kAttMaxGroup], head_sum[kAttMaxGroup];
+  __shared__ unsigned my_ticket;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int n = p_hi > p_lo ? p_hi - p_lo : 0;
   float* qs = att_smem;                 // [G][D]
-  float* sc = qs + kAttMaxGroup * D;    // [G][max_len]
-  float* red = sc + G * max_len;        // [16 position groups][G][D]
+  float* sc = qs + kAttMaxGroup * D;    // [G][chunk_cap]
+  float* red = sc + G * chunk_cap;      // [16 position groups][G][D]
   for (int i = tid; i < G * D; i += kAttThreads) qs[i] = __half2float(q[i]) * scale;
   __syncthreads();
-  for (int p = tid; p < L; p += kAttThreads) {
+  for (int i = tid; i < n; i += kAttThreads) {
     uint4 u[D / 8];
-    const uint4* row = reinterpret_cast<const uint4*>(kb + (int64_t)p * D);
+    const uint4* row = reinterpret_cast<const uint4*>(kb + (int64_t)(p_lo + i) * D);
 #pragma unroll
     for (int c = 0; c < D / 8; ++c) u[c] = row[c];
     float acc[G];
@@ -184,10 +195,10 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
       const __half2* h2 = reinterpret_cast<const __half2*>(&u[c]);
       float kf[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h2[i]);
-        kf[2 * i] = f.x;
-        kf[2 * i + 1] = f.y;
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h2[j]);
+        kf[2 * j] = f.x;
+        kf[2 * j + 1] = f.y;
       }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
@@ -197,25 +208,24 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
       }
     }
 #pragma unroll
-    for (int g = 0; g < G; ++g) sc[g * max_len + p] = acc[g];
+    for (int g = 0; g < G; ++g) sc[g * chunk_cap + i] = acc[g];
   }
   __syncthreads();
-  if (w < G) {  // softmax of head w
-    float* s = sc + w * max_len;
+  if (w < G) {  // head w: maximum, exponentials (kept unnormalised), sum
+    float* sh = sc + w * chunk_cap;
     float m = -INFINITY;
-    for (int p = lane; p < L; p += 32) m = fmaxf(m, s[p]);
+    for (int i = lane; i < n; i += 32) m = fmaxf(m, sh[i]);
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float sum = 0.f;
-    for (int p = lane; p < L; p += 32) {
-      const float e = __expf(s[p] - m);
-      s[p] = e;
+    for (int i = lane; i < n; i += 32) {
+      const float e = __expf(sh[i] - m);
+      sh[i] = e;
       sum += e;
     }
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = 1.f / sum;
-    for (int p = lane; p < L; p += 32) s[p] *= inv;
+    if (lane == 0) { head_max[w] = m; head_sum[w] = sum; }
   }
   __syncthreads();
   {
@@ -224,32 +234,32 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+      for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
     constexpr int U = 8;
-    for (int p0 = ps; p0 < L; p0 += 16 * U) {
+    for (int i0 = ps; i0 < n; i0 += 16 * U) {
       uint4 u[U];
 #pragma unroll
       for (int j = 0; j < U; ++j) {
-        const int p = p0 + 16 * j;
-        u[j] = p < L ? *reinterpret_cast<const uint4*>(vb + (int64_t)p * D + piece * 8) : make_uint4(0, 0, 0, 0);
+        const int i = i0 + 16 * j;
+        u[j] = i < n ? *reinterpret_cast<const uint4*>(vb + (int64_t)(p_lo + i) * D + piece * 8) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int j = 0; j < U; ++j) {
-        const int p = p0 + 16 * j;
-        if (p < L) {
+        const int i = i0 + 16 * j;
+        if (i < n) {
           const __half2* h2 = reinterpret_cast<const __half2*>(&u[j]);
           float vf[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h2[i]);
-            vf[2 * i] = f.x;
-            vf[2 * i + 1] = f.y;
+          for (int c = 0; c < 4; ++c) {
+            const float2 f = __half22float2(h2[c]);
+            vf[2 * c] = f.x;
+            vf[2 * c + 1] = f.y;
           }
 #pragma unroll
           for (int g = 0; g < G; ++g) {
-            const float pr = sc[g * max_len + p];
+            const float pr = sc[g * chunk_cap + i];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][i] += pr * vf[i];
+            for (int c = 0; c < 8; ++c) acc[g][c] += pr * vf[c];
           }
         }
       }
@@ -262,33 +272,75 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
     }
   }
   __syncthreads();
-  for (int i = tid; i < G * D; i += kAttThreads) {
-    float s = 0.f;
+  if (splits == 1) {
+    for (int i = tid; i < G * D; i += kAttThreads) {
+      float v = 0.f;
 #pragma unroll
-    for (int gs = 0; gs < 16; ++gs) s += red[gs * G * D + i];
-    out_row[i] = __float2half_rn(s);
+      for (int gs = 0; gs < 16; ++gs) v += red[gs * G * D + i];
+      out_row[i] = __float2half_rn(v / head_sum[i / D]);
+    }
+    return;
   }
+  // this split's record: [G][D + 2] = weighted rows, maximum, sum
+  for (int i = tid; i < G * D; i += kAttThreads) {
+    float v = 0.f;
+#pragma unroll
+    for (int gs = 0; gs < 16; ++gs) v += red[gs * G * D + i];
+    part[(i / D) * (D + 2) + (i % D)] = v;
+  }
+  if (tid < G) { part[tid * (D + 2) + D] = head_max[tid]; part[tid * (D + 2) + D + 1] = head_sum[tid]; }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) my_ticket = atomicAdd(ticket, 1u);
+  __syncthreads();
+  if (my_ticket != (unsigned)(splits - 1)) return;
+  __threadfence();
+  const float* all = part - (size_t)blockIdx.z * G * (D + 2);  // record of split 0
+  for (int i = tid; i < G * D; i += kAttThreads) {
+    const int g = i / D, d = i % D;
+    float m = -INFINITY;
+    for (int sp = 0; sp < splits; ++sp) m = fmaxf(m, __ldcg(all + ((size_t)sp * G + g) * (D + 2) + D));
+    float num = 0.f, den = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float* rec = all + ((size_t)sp * G + g) * (D + 2);
+      const float ls = __ldcg(rec + D + 1);
+      if (ls > 0.f) {  // an empty split has no maximum
+        const float f = __expf(__ldcg(rec + D) - m);
+        num += __ldcg(rec + d) * f;
+        den += ls * f;
+      }
+    }
+    out_row[i] = __float2half_rn(num / den);
+  }
+  if (tid == 0) *ticket = 0u;
 }
 
 template <int D>
 __global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(const __half* q, const __half* k_cache, const __half* v_cache,
                                                                         const int64_t* pos_dev, int64_t pos_host, __half* out,
-                                                                        int hq, int hkv, int max_len, float scale) {
+                                                                        int hq, int hkv, int max_len, float scale, float* parts,
+                                                                        unsigned* tickets) {
   extern __shared__ __align__(16) float att_smem[];
   const int G = hq / hkv;
-  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, splits = gridDim.z;
   pdl_enter();
   const int64_t len64 = (pos_dev ? *pos_dev : pos_host) + 1;  // the current token is already in the cache
   const int L = (int)(len64 < 1 ? 1 : (len64 > max_len ? max_len : len64));
+  // chunk_cap sizes the score rows in shared memory; a multiple of 4 keeps the float4 area behind them aligned
+  const int chunk = (L + splits - 1) / splits, chunk_cap = ((max_len + splits - 1) / splits + 3) & ~3;
+  const int p_lo = sp * chunk, p_hi = p_lo + chunk < L ? p_lo + chunk : L;
   const __half* qp = q + ((int64_t)b * hq + (int64_t)kvh * G) * D;
   const __half* kb = k_cache + ((int64_t)b * hkv + kvh) * (int64_t)max_len * D;
   const __half* vb = v_cache + ((int64_t)b * hkv + kvh) * (int64_t)max_len * D;
   __half* op = out + ((int64_t)b * hq + (int64_t)kvh * G) * D;
+  const size_t head = (size_t)b * hkv + kvh;
+  float* part = parts ? parts + (head * splits + sp) * G * (D + 2) : nullptr;
+  unsigned* ticket = tickets ? tickets + head : nullptr;
   switch (G) {
-    case 1: attention_body<D, 1>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
-    case 2: attention_body<D, 2>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
-    case 4: attention_body<D, 4>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
-    case 8: attention_body<D, 8>(qp, kb, vb, op, att_smem, L, max_len, scale); break;
+    case 1: attention_body<D, 1>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
+    case 2: attention_body<D, 2>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
+    case 4: attention_body<D, 4>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
+    case 8: attention_body<D, 8>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
     default: break;
   }
 }
@@ -338,15 +390,33 @@ extern "C" int pe_silu_mul(const void* gate_up, int64_t ld_gu, void* out, int64_
   return PE_OK;
 }
 
+// scratch of the split form: [tickets: one counter per (sequence, kv head), 4 KB, zero before the first
+// call and left zero][one record per (sequence, kv head, split, query head of the group)]
+extern "C" size_t pe_decode_attention_workspace_bytes(int batch, int hq, int hkv, int head_dim) {
+  if (batch < 1 || hq < 1 || hkv < 1 || head_dim != 128 || hq % hkv || (size_t)batch * hkv * 4 > 4096) return 0;
+  return 4096 + (size_t)batch * hkv * kAttMaxSplits * (hq / hkv) * (head_dim + 2) * sizeof(float);
+}
+
 extern "C" int pe_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos_dev,
                                    int64_t pos_host, void* out, int batch, int hq, int hkv, int head_dim, int max_len,
-                                   void* stream) {
+                                   void* workspace, size_t workspace_bytes, void* stream) {
   if (!q || !k_cache || !v_cache || !out || batch < 1 || hq < 1 || hkv < 1 || max_len < 1) return PE_ERR_ARG;
   if (head_dim != 128 || hq % hkv) return PE_ERR_SHAPE;
   if (hq / hkv != 1 && hq / hkv != 2 && hq / hkv != 4 && hq / hkv != 8) return PE_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return PE_ERR_ALIGN;
   const int G = hq / hkv;
-  const size_t smem = ((size_t)kAttMaxGroup * 128 + (size_t)G * max_len + (size_t)16 * G * 128) * sizeof(float);
+  // cut the cache positions so that the launch has about one CTA per SM (at most 8 ranges, none without a
+  // scratch buffer)
+  int splits = 1;
+  const size_t need = pe_decode_attention_workspace_bytes(batch, hq, hkv, head_dim);
+  if (workspace && need && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 15)) {
+    const int sms = sm_count();
+    splits = sms > 0 ? sms / (hkv * batch) : 1;
+    splits = splits < 1 ? 1 : (splits > kAttMaxSplits ? kAttMaxSplits : splits);
+    if (max_len < 64 * splits) splits = max_len / 64 < 1 ? 1 : max_len / 64;
+  }
+  const int chunk_cap = ((max_len + splits - 1) / splits + 3) & ~3;  // as in the kernel
+  const size_t smem = ((size_t)kAttMaxGroup * 128 + (size_t)G * chunk_cap + (size_t)16 * G * 128) * sizeof(float);
   if (smem > 200 * 1024 || batch > 65535) return PE_ERR_LIMIT;
   auto kfn = decode_attention_kernel<128>;
   static thread_local size_t configured[16] = {0};
@@ -356,8 +426,11 @@ extern "C" int pe_decode_attention(const void* q, const void* k_cache, const voi
     PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 16) configured[dev] = smem;
   }
-  PE_CUDA_TRY(launch_pdl(kfn, dim3((unsigned)hkv, (unsigned)batch), dim3(kAttThreads), smem, static_cast<cudaStream_t>(stream),
-                         static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
-                         pos_dev, pos_host, static_cast<__half*>(out), hq, hkv, max_len, 1.f / sqrtf((float)head_dim)));
+  float* parts = splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 4096) : nullptr;
+  unsigned* tickets = splits > 1 ? static_cast<unsigned*>(workspace) : nullptr;
+  PE_CUDA_TRY(launch_pdl(kfn, dim3((unsigned)hkv, (unsigned)batch, (unsigned)splits), dim3(kAttThreads), smem,
+                         static_cast<cudaStream_t>(stream), static_cast<const __half*>(q), static_cast<const __half*>(k_cache),
+                         static_cast<const __half*>(v_cache), pos_dev, pos_host, static_cast<__half*>(out), hq, hkv, max_len,
+                         1.f / sqrtf((float)head_dim), parts, tickets));
   return PE_OK;
 }

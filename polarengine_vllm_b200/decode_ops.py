@@ -68,8 +68,25 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     hkv, max_len = k_cache.shape[1], k_cache.shape[2]
     out = torch.empty(batch, hq * d, dtype=torch.float16, device=dev)
     dev_pos = pos if torch.is_tensor(pos) else None
+    need = nv.lib().pe_decode_attention_workspace_bytes(batch, hq, hkv, d)
+    ws = _attention_scratch(dev, need) if need else None
     nv.check(nv.lib().pe_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                                           dev_pos.data_ptr() if dev_pos is not None else None,
                                           0 if dev_pos is not None else int(pos), out.data_ptr(), batch, hq, hkv, d, max_len,
+                                          ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
                                           nv.stream_ptr(dev)), "pe_decode_attention")
     return out
+
+
+_att_ws = {}
+
+
+def _attention_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch of the split attention, one per (device, stream); the kernel leaves its
+    ticket counters at zero, so consecutive calls on a stream share it."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _att_ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _att_ws[key] = buf
+    return buf
