@@ -68,3 +68,14 @@ def test_create_weights_on_cpu():
     m._fwht_cache.put(torch.zeros(1), 1, torch.zeros(1))
     create_fwht_clear_hook(m)(None, None)
     assert m._fwht_cache.get(torch.zeros(1), 1) is None
+
+
+@pytest.mark.skipif(not HAVE_VLLM, reason="vLLM not importable")
+def test_plugin_entry_point_registers_with_vllm():
+    """``vllm.general_plugins`` calls register_polar_quant(); afterwards ``--quantization polarengine``
+    resolves to this package's config class (reference: polarengine_vllm/__init__.py:24-38)."""
+    import polarengine_vllm_b200
+    polarengine_vllm_b200.register_polar_quant()
+    from vllm.model_executor.layers.quantization import QUANTIZATION_METHODS, get_quantization_config
+    assert "polarengine" in QUANTIZATION_METHODS
+    assert get_quantization_config("polarengine") is PolarQuantConfig
