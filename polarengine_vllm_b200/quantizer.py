@@ -77,3 +77,37 @@ class PolarQuantizer:
         cfg = {"format": "polar_engine_v5" if any_q5 else "polar_engine_v4", "quantization": "polarengine",
                "block_size": self.block_size, "bit_assignment": self.bit_assignment, "layers": layers}
         return out, cfg
+
+
+def save_checkpoint(tensors: Mapping[str, torch.Tensor], polar_config: dict, output_dir: str,
+                    max_shard_bytes: int = 5 * 1024 ** 3) -> Dict[str, str]:
+    """Write the output of :meth:`PolarQuantizer.quantize_state_dict` the way the reference's
+    ``quantize_model`` does (quantizer.py:85-137, 386-403): safetensors shards of at most
+    ``max_shard_bytes`` named ``model-0000i-of-0000n.safetensors`` filled in insertion order,
+    ``model.safetensors.index.json`` (total size + weight map) and ``polar_config.json``.
+    Returns the weight map."""
+    import json
+    import os
+    from safetensors.torch import save_file
+    os.makedirs(output_dir, exist_ok=True)
+    shards, current, used = [], {}, 0
+    for name, t in tensors.items():
+        nbytes = t.numel() * t.element_size()
+        if current and used + nbytes > max_shard_bytes:
+            shards.append(current)
+            current, used = {}, 0
+        current[name] = t.contiguous()
+        used += nbytes
+    if current:
+        shards.append(current)
+    weight_map: Dict[str, str] = {}
+    for i, shard in enumerate(shards):
+        fname = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        save_file(shard, os.path.join(output_dir, fname))
+        weight_map.update({k: fname for k in shard})
+    with open(os.path.join(output_dir, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {"total_size": sum(t.numel() * t.element_size() for t in tensors.values())},
+                   "weight_map": weight_map}, f, indent=2)
+    with open(os.path.join(output_dir, "polar_config.json"), "w") as f:
+        json.dump(polar_config, f, indent=2)
+    return weight_map

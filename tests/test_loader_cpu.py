@@ -143,3 +143,34 @@ def test_golden_checkpoints_match_the_reference_loader():
         assert torch.equal(got["norms"].float().flatten(), torch.from_numpy(exp["hlwq/l/norms"]).flatten())
         assert torch.equal(got["ct_scaled"], torch.from_numpy(exp["hlwq/l/ct_scaled"]))
         assert got["in_f"] == int(exp["hlwq/l/_hlwq_in_f"][0])
+
+
+def test_quantize_save_load_round_trip(tmp_path):
+    """quantize_state_dict -> save_checkpoint -> PolarCheckpoint gives back the quantizer's codes,
+    norms and tables for every layer, across shard boundaries and for every packing."""
+    from polarengine_vllm_b200.quantizer import PolarQuantizer, save_checkpoint
+    g = torch.Generator().manual_seed(11)
+    state = {"model.layers.0.self_attn.q_proj.weight": torch.randn(32, 256, generator=g) * 0.02,      # Q5 -> packed_q5
+             "model.layers.0.self_attn.o_proj.weight": torch.randn(32, 256, generator=g) * 0.02,      # Q6 -> int8
+             "model.layers.0.mlp.gate_up_proj.weight": torch.randn(64, 200, generator=g) * 0.02,      # Q3 -> nibbles, padded K
+             "model.layers.0.mlp.down_proj.weight": torch.randn(32, 384, generator=g) * 0.02,         # Q4 -> nibbles
+             "model.layers.0.input_layernorm.weight": torch.ones(256), "model.layers.0.mlp.down_proj.bias": torch.zeros(32)}
+    qz = PolarQuantizer()
+    tensors, cfg = qz.quantize_state_dict(state)
+    wm = save_checkpoint(tensors, cfg, str(tmp_path), max_shard_bytes=16 * 1024)
+    assert len(set(wm.values())) > 1 and cfg["format"] == "polar_engine_v5"
+    with loader.PolarCheckpoint(str(tmp_path)) as ck:
+        assert ck.layer_names() == sorted(k[:-7] for k in state if k.endswith("proj.weight"))
+        for name, w in state.items():
+            if not name.endswith("proj.weight"):
+                continue
+            prefix = name[:-7]
+            bits = cfg["layers"][prefix]["bits"]
+            q = qz.quantize_tensor(w, bits)
+            t = ck.load_layer(prefix)
+            codes = packing.unpack_codes_half_block(t["codes"]) if t["packed"] else t["codes"]
+            assert t["packed"] == (bits <= 4) and torch.equal(codes, q["codes"]), prefix
+            assert torch.equal(t["norms"], q["norms"]) and torch.equal(t["ct_scaled"], q["ct_scaled"])
+            assert t["in_f"] == w.shape[1] and ck.layer_bits(prefix) == bits
+        assert torch.equal(ck.load_layer("model.layers.0.input_layernorm")["weight"], torch.ones(256).half())
+        assert "bias" in ck.load_layer("model.layers.0.mlp.down_proj")
