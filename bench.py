@@ -1,22 +1,29 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized-linear decode path: one "step" is one pass of the four
-projection launches of a 9B-class decoder layer (fused q/k/v 6144x4096 Q5, o 4096x4096
-Q6, fused gate/up 24576x4096 Q3, down 4096x12288 Q4; block 128, fp16 norms) over a
-batch of fp16 activations, rotating through a ring of layers larger than L2.
+"""Benchmark of the quantized-linear path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+    torchrun ... bench.py --gpus N ...            (one rank per GPU)
 
-Prints ONE JSON line.  `value` is algorithmic GB/s of the whole job with everything
-resident in HBM; `e2e` goes through linear_method.apply with host buffers; `roofline`
-is the dominant kernel (nibble-code GEMV) against the measured HBM copy bandwidth;
-`cpu_baseline` is the CPU oracle (the reference's torch math) on a bounded sample.
-With N > 1 (torchrun) every rank streams its own ring of layers (independent units, no
-collective on the data path): weak scaling.
+Prints ONE JSON line.  The headline is the decode-size matmul: one "step" is one pass of the four
+projection launches of a 9B-class decoder layer (fused q/k/v 6144x4096 Q5, o 4096x4096 Q6, fused
+gate/up 24576x4096 Q3, down 4096x12288 Q4; block 128, fp16 norms) over a batch of fp16 activations,
+rotating through a ring of layers larger than L2.  `value` is algorithmic GB/s of the whole job with
+everything resident in HBM; `e2e` goes through linear_method.apply with host buffers; `roofline` is
+the nibble-code launch on the 4096x12288 Q4 layer against the measured HBM copy bandwidth;
+`cpu_baseline` is the CPU oracle (the reference's torch math) on a bounded sample.  With N > 1 every
+rank streams its own ring of layers (independent units, no collective on that path: weak scaling).
+
+The same run then measures the rest of the metric and reports it as extra keys of the line:
+`prefill` (4096 bf16 tokens through the tensor-core kernel on the three layer shapes), `model_decode`
+(the 36-layer decoder, tensor parallel over the N ranks, batch 1 and 8, with a numeric check of the
+sharded model against the un-sharded one) and `moe` (128-expert layer, expert parallel over the N
+ranks, 64 and 2048 tokens).  `--workload prefill|model|moe` runs one of them alone with its own line.
 """
 import argparse
 import json
 import math
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -31,8 +38,31 @@ HIDDEN, INTER, QKV = 4096, 12288, 6144
 # (name, out_f, in_f, bits)
 PROJ = [("qkv_proj", QKV, HIDDEN, 5), ("o_proj", HIDDEN, HIDDEN, 6),
         ("gate_up_proj", 2 * INTER, HIDDEN, 3), ("down_proj", HIDDEN, INTER, 4)]
-NCU_DRAM_BYTES_DOWN_B1 = 26035072  # dram__bytes_read + write of one batch-1 down_proj launch (ncu capture summarised in profiles/)
 RING = 8  # layers in the ring: 8 x 120.5 MB = 964 MB >> 126 MB of L2
+MIN_TIMED_S = 0.25  # a timed region shorter than this is repeated (more replays, so that the clocks are sampled several times)
+
+
+def load_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+def measured_traffic(kernel_tag):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch from the kept ncu summary of that kernel
+    (a `traffic_bytes_per_launch[<tag>]: N` line under profiles/), or None when no capture is on record."""
+    pat = re.compile(r"traffic_bytes_per_launch\[" + re.escape(kernel_tag) + r"\]\s*:\s*(\d+)")
+    pdir = os.path.join(ROOT, "profiles")
+    try:
+        for name in sorted(os.listdir(pdir)):
+            if name.endswith((".md", ".txt")):
+                m = pat.search(open(os.path.join(pdir, name)).read())
+                if m:
+                    return int(m.group(1))
+    except OSError:
+        pass
+    return None
 
 
 def alg_bytes(out_f, in_f, bits, batch):
@@ -45,27 +75,21 @@ def step_bytes(batch):
     return sum(alg_bytes(n, k, b, batch) for _, n, k, b in PROJ)
 
 
-def lloyd_max_boundaries(ct):
-    return (ct[1:] + ct[:-1]) / 2
-
-
 def make_layer(dev, seed):
-    """Synthetic quantized layer: codes are the Lloyd-Max cells of N(0,1) draws (the
-    distribution the quantizer produces for Gaussian weights), norms ~ 0.02*sqrt(128)."""
+    """Synthetic quantized layer: codes are the Lloyd-Max cells of N(0,1) draws (the distribution the
+    quantizer produces for Gaussian weights), norms ~ 0.02*sqrt(128)."""
     from polarengine_vllm_b200.utils import get_centroids, get_ct_scaled
     from polarengine_vllm_b200.packing import pack_codes_half_block
-    from polarengine_vllm_b200.kernels import retile
     g = torch.Generator(device=dev).manual_seed(seed)
     out = {}
     for name, n, k, bits in PROJ:
         ct = get_centroids(bits).to(dev)
         r = torch.randn(n, k, device=dev, generator=g)
-        codes = torch.bucketize(r, lloyd_max_boundaries(ct)).to(torch.int8)
+        codes = torch.bucketize(r, (ct[1:] + ct[:-1]) / 2).to(torch.int8)
         del r
         norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(n, k // 128, device=dev, generator=g))).half()
         w = pack_codes_half_block(codes) if bits <= 4 else codes
-        # the decode kernel streams the tiled copy (what process_weights_after_loading builds)
-        out[name] = (w, bits <= 4, norms, get_ct_scaled(bits).to(dev), n, k, retile(w, bits <= 4, norms))
+        out[name] = (w, bits <= 4, norms, get_ct_scaled(bits).to(dev), n, k)
     return out
 
 
@@ -81,7 +105,7 @@ class ClockSampler(threading.Thread):
             try:
                 o = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}", "--format=csv,noheader,nounits"],
                                    capture_output=True, text=True, timeout=5).stdout.strip()
-                if o:
+                if o and not self.stop_flag:
                     self.rows.append([c.strip() for c in o.split(",")])
             except Exception:
                 pass
@@ -96,10 +120,17 @@ class ClockSampler(threading.Thread):
 
 
 def cpu_baseline(batch, budget_s=12.0):
-    """The reference's CPU-runnable form of the path (rotate, gather centroids, scale by
-    norms, contract) timed on the host cores for whole layer passes until ~budget_s."""
+    """The reference's CPU-runnable form of the path (rotate, gather centroids, scale by norms, contract)
+    timed on the host cores for whole layer passes until ~budget_s.  Every host core is used: launchers such
+    as torch.distributed.run export OMP_NUM_THREADS=1, which would time one core."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import polar_oracle as oracle
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except Exception:
+        pass
+    torch.set_num_threads(max(1, cores))
     g = torch.Generator().manual_seed(0)
     layers = []
     for name, n, k, bits in PROJ:
@@ -107,6 +138,7 @@ def cpu_baseline(batch, budget_s=12.0):
         norms = (torch.rand(n, k // 128, generator=g) * 0.02 + 0.2).half()
         layers.append((codes, norms, oracle.ct_scaled(bits), k))
     x = {k: torch.randn(batch, k, generator=g).half() for k in (HIDDEN, INTER)}
+
     def one_pass():
         for codes, norms, cts, k in layers:
             oracle.linear_hadamard_domain(x[k], codes, norms, cts)
@@ -120,125 +152,90 @@ def cpu_baseline(batch, budget_s=12.0):
             break
     dt = time.perf_counter() - t0
     return {"value": step_bytes(batch) * n / dt / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{n} decoder-layer passes (4 projections, batch {batch}) of the CPU oracle in {dt:.1f} s"}, dt / n
+            "sample": f"{n} decoder-layer passes (4 projections, batch {batch}) of the CPU oracle in {dt:.1f} s on one host"}, dt / n
 
 
-def prefill_sweep(a, dev, rank, world):
-    """BASELINE configs[2]: M tokens x K into N, bf16 activations, Q4 nibble codes.  One step = the three layer
-    shapes once; value = TFLOP/s of 2*M*N*K (rotation and activation preparation included in the time)."""
+# ------------------------------------------------------------------------------------------ prefill
+def prefill_record(dev, m=4096, steps=10):
+    """BASELINE configs[2]: M tokens x K into N, bf16 activations, Q4 nibble codes.  Per shape: TFLOP/s of
+    2*M*N*K (rotation and activation preparation included in the time) and the fraction of the measured
+    cuBLAS bf16 peaks (burst and sustained)."""
     from polarengine_vllm_b200 import kernels
+    from polarengine_vllm_b200.utils import get_ct_scaled
     shapes = [(4096, 4096), (12288, 4096), (4096, 12288)]
-    m = a.m
     g = torch.Generator(device=dev).manual_seed(3)
-    data = []
+    peaks = load_peaks()
+    burst, sustained = float(peaks.get("bf16_tflops", 1590.0)), float(peaks.get("bf16_tflops_sustained", 1400.0))
+    rec = {"m": m, "dtype": "bf16", "bits": 4, "steps": steps, "peak_burst_tflops": burst, "peak_sustained_tflops": sustained,
+           "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback", "shapes": {}}
     for n, k in shapes:
         w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
         norms = (0.2 + 0.02 * torch.rand(n, k // 128, device=dev, generator=g)).half()
-        from polarengine_vllm_b200.utils import get_ct_scaled
+        ct = get_ct_scaled(4).to(dev)
         x = torch.randn(m, k, device=dev, generator=g).bfloat16()
-        data.append((w, norms, get_ct_scaled(4).to(dev), x, n, k))
-    def step():
-        for w, norms, ct, x, n, k in data:
+        for _ in range(3):
             kernels.quant_matmul(w, True, norms, ct, x, False, n, k, k, torch.float16)
-    if a.probe:
-        step(); torch.cuda.synchronize()
-        print(json.dumps({"probe": "prefill", "m": m}))
-        return
-    steps = max(3, min(a.steps, 50))
-    for _ in range(3):
-        step()
-    torch.cuda.synchronize()
-    per = []
-    for w, norms, ct, x, n, k in data:
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             kernels.quant_matmul(w, True, norms, ct, x, False, n, k, k, torch.float16)
-        e1.record(); torch.cuda.synchronize()
-        per.append(e0.elapsed_time(e1) / 1e3 / steps)
-    flops = [2.0 * m * n * k for n, k in shapes]
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
-    peak = float(peaks.get("bf16_tflops", 1590.0))
-    best = max(range(3), key=lambda i: flops[i] / per[i])
-    if rank == 0:
-        print(json.dumps({
-            "metric": "prefill quantized GEMM TFLOP/s", "unit": "TFLOP/s", "value": sum(flops) / sum(per) / 1e12,
-            "n_gpus": a.gpus, "steps": steps, "warmup": 3, "ms_per_step": sum(per) * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"prefill_gemm (BASELINE configs[2]) M={m}, Q4, (N,K) in {shapes}",
-                       "l2_defeat": "operands larger than L2 at M=4096 (x + y + codes > 126 MB for two of three shapes)"},
-            "per_shape_tflops": {f"{n}x{k}": flops[i] / per[i] / 1e12 for i, (n, k) in enumerate(shapes)},
-            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<packed> N=%d K=%d" % shapes[best],
-                         "achieved": flops[best] / per[best] / 1e12, "peak": peak,
-                         "peak_source": "measured burst (MEASURED_PEAKS.json)" if peaks else "fallback",
-                         "unit": "TFLOP/s", "frac": flops[best] / per[best] / 1e12 / peak, "traffic": None},
-            "gpu_launches": 2 * 3 * steps}))
+        e1.record()
+        torch.cuda.synchronize()
+        per = e0.elapsed_time(e1) / 1e3 / steps
+        tf = 2.0 * m * n * k / per / 1e12
+        rec["shapes"][f"{n}x{k}"] = {"tflops": tf, "ms": per * 1e3, "frac_of_burst": tf / burst, "frac_of_sustained": tf / sustained}
+        del w, norms, x
+    rec["gpu_launches"] = 2 * 3 * steps
+    return rec
 
 
-def model_decode(a, dev, rank, world):
-    """BASELINE configs[3]: prompt of random ids, then greedy decode; every projection, the embedding and the LM
-    head are quantized; tensor parallel over the ranks (column q/k/v/gate/up, row o/down + NCCL all-reduce).
-    The decode step is captured in a CUDA graph.  value = batch * new_tokens / time (tok/s), strong scaling."""
+# ------------------------------------------------------------------------------------------ model decode
+def decode_run(model, dev, rank, world, batch, prompt_len, new_tokens, use_graph=True):
+    """Prompt of random ids, then greedy decode of `new_tokens` tokens; the decode step is captured in a CUDA
+    graph.  Returns the record and the objects that must be released before the process group."""
     import torch.distributed as dist
-    from polarengine_vllm_b200.decoder import DecoderConfig, QuantDecoder
-    cfg = DecoderConfig(n_layers=a.layers)
-    b = a.batch
-    fused = world > 1 and not a.nccl_allreduce
-    fused_note = "nccl all-reduce + add/norm kernels"
-    try:
-        model = QuantDecoder(cfg, dev, rank, world, None, max_len=a.prompt + a.new_tokens + 8, batch=b, fused_allreduce=fused)
-        if fused:
-            fused_note = "all-reduce + residual add + RMSNorm in one kernel over peer memory (decode steps); nccl in prefill"
-    except Exception as exc:  # peer mappings unavailable: the NCCL path still measures the model
-        if not fused:
-            raise
-        fused_note = f"nccl all-reduce (peer exchange unavailable: {type(exc).__name__})"
-        model = QuantDecoder(cfg, dev, rank, world, None, max_len=a.prompt + a.new_tokens + 8, batch=b)
+    cfg = model.cfg
+    model.alloc_cache(batch)
     g = torch.Generator(device=dev).manual_seed(17)
-    prompt = torch.randint(0, cfg.vocab, (b, a.prompt), device=dev, generator=g)
+    prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), device=dev, generator=g)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     nxt = model.forward(prompt, 0)
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0
-    ids_buf = nxt.view(b, 1).clone()
-    pos = torch.tensor(a.prompt, device=dev, dtype=torch.int64)
+    ids_buf = nxt.view(batch, 1).clone()
+    pos = torch.tensor(prompt_len, device=dev, dtype=torch.int64)
     stream = torch.cuda.Stream(dev)
+
     def step():
         out = model.forward(ids_buf, pos)
-        ids_buf.copy_(out.view(b, 1))
+        ids_buf.copy_(out.view(batch, 1))
         pos.add_(1)
-    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
-    sampler.start()  # from the warm-up on: a query takes longer than a short timed region on a full box
     with torch.cuda.stream(stream):
         for _ in range(3):
             step()
         torch.cuda.synchronize()
         graph = None
-        if not a.no_graph:
+        if use_graph:
             graph = torch.cuda.CUDAGraph()
             # thread_local: the NCCL watchdog thread may query events while this thread captures
             with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
                 step()
         torch.cuda.synchronize()
-        pos.fill_(a.prompt)
+        pos.fill_(prompt_len)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(a.new_tokens):
+        for _ in range(new_tokens):
             if graph is not None:
                 graph.replay()
             else:
                 step()
         e1.record(stream)
         torch.cuda.synchronize()
-        sampler.stop_flag = True
         if world > 1:
             dist.barrier()
     el = e0.elapsed_time(e1) / 1e3
@@ -246,42 +243,95 @@ def model_decode(a, dev, rank, world):
         t = torch.tensor([el], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         el = float(t)
-    if rank == 0:
-        peaks = {}
+    wb = model.weight_bytes_per_step()
+    peak = float(load_peaks().get("hbm_gbs", 6650.0))
+    rec = {"tok_s": batch * new_tokens / el, "ms_per_step": el / new_tokens * 1e3, "batch": batch, "new_tokens": new_tokens,
+           "prompt": prompt_len, "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
+           "hbm_frac_of_measured": wb / (el / new_tokens) / 1e9 / peak,
+           "exchange_timed_out": bool(model.xchg.timed_out()) if model.xchg is not None else None,
+           "launch": "cuda graph" if graph is not None else "eager"}
+    if graph is not None:
+        graph.reset()
+    return rec
+
+
+def tp_parity(dev, rank, world, fused):
+    """Numeric check of the sharded decoder: a 2-layer model of the full layer shapes, sharded over the ranks
+    (same seeded weights, every rank keeps its slice), against the un-sharded model computed on every rank:
+    logits of the last prompt position and of three decode steps.  Returns max |a - b| / max |b|."""
+    from polarengine_vllm_b200.decoder import DecoderConfig, QuantDecoder
+    cfg = DecoderConfig(n_layers=2, vocab=32768)
+    sharded = QuantDecoder(cfg, dev, rank, world, None, seed=4321, max_len=64, batch=2, fused_allreduce=fused)
+    full = QuantDecoder(cfg, dev, 0, 1, None, seed=4321, max_len=64, batch=2)
+    g = torch.Generator(device=dev).manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (2, 24), device=dev, generator=g)
+    worst = 0.0
+    a, b = sharded.forward(prompt, 0, return_logits=True), full.forward(prompt, 0, return_logits=True)
+    worst = max(worst, float((a - b).abs().max() / b.abs().max()))
+    same_tokens = True
+    ids = b.argmax(-1).view(2, 1)
+    for s in range(3):
+        pos = torch.tensor(24 + s, device=dev, dtype=torch.int64)
+        a, b = sharded.forward(ids, pos, return_logits=True), full.forward(ids, pos, return_logits=True)
+        worst = max(worst, float((a - b).abs().max() / b.abs().max()))
+        same_tokens = same_tokens and bool(torch.equal(a.argmax(-1), b.argmax(-1)))
+        ids = b.argmax(-1).view(2, 1)
+    timed_out = bool(sharded.xchg.timed_out()) if sharded.xchg is not None else None
+    del sharded, full
+    torch.cuda.empty_cache()
+    return {"max_rel": worst, "same_next_tokens": same_tokens, "exchange_timed_out": timed_out,
+            "model": "2 layers, hidden 4096, intermediate 12288, vocab 32768, batch 2, prompt 24 + 3 decode steps"}
+
+
+def model_record(a, dev, rank, world, batches=(1, 8)):
+    """BASELINE configs[3]: every projection, the embedding and the LM head quantized; tensor parallel over the
+    ranks (column q/k/v/gate/up/head, row o/down).  Strong scaling: the model is fixed, the ranks share it."""
+    from polarengine_vllm_b200.decoder import DecoderConfig, QuantDecoder
+    fused = world > 1 and not a.nccl_allreduce
+    note = "nccl all-reduce + add/norm kernels" if world > 1 else "no exchange (one rank)"
+    rec = {"layers": a.layers, "parallelism": f"tp{world}", "scaling": "strong"}
+    if world > 1:
         try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        wb = model.weight_bytes_per_step()
-        print(json.dumps({
-            "metric": "9B-class decode tok/s", "unit": "tok/s", "value": b * a.new_tokens / el, "n_gpus": a.gpus,
-            "steps": a.new_tokens, "warmup": 3, "ms_per_step": el / a.new_tokens * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers, hidden 4096, vocab 151936, "
-                                   f"prompt {a.prompt}, {a.new_tokens} new tokens", "batch": b,
-                       "parallelism": f"tp{world}", "l2_defeat": "weights per rank larger than L2",
-                       "launch": "eager" if a.no_graph else "cuda graph", "row_parallel_epilogue": fused_note},
-            "exchange_timed_out": bool(model.xchg.timed_out()) if model.xchg is not None else None,
-            "prefill_s": prefill_s, "weight_bytes_per_step_per_rank": wb,
-            "hbm_frac_of_measured": wb / (el / a.new_tokens) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)),
-            "clocks": sampler.summary(), "gpu_launches": a.new_tokens * (8 * a.layers + 3)}))
-    finish(world)
+            rec["tp_parity"] = tp_parity(dev, rank, world, fused)
+            rec["tp_parity_max_rel"] = rec["tp_parity"]["max_rel"]
+        except Exception as exc:
+            rec["tp_parity"] = {"error": f"{type(exc).__name__}: {exc}"}
+            rec["tp_parity_max_rel"] = None
+    else:
+        rec["tp_parity_max_rel"] = None
+    cfg = DecoderConfig(n_layers=a.layers)
+    max_len = a.prompt + a.new_tokens + 8
+    try:
+        model = QuantDecoder(cfg, dev, rank, world, None, max_len=max_len, batch=1, fused_allreduce=fused)
+        if fused:
+            note = "all-reduce + residual add + RMSNorm in one kernel over peer memory (decode steps); nccl in prefill"
+    except Exception as exc:  # peer mappings unavailable: the NCCL path still measures the model
+        if not fused:
+            raise
+        note = f"nccl all-reduce (peer exchange unavailable: {type(exc).__name__})"
+        model = QuantDecoder(cfg, dev, rank, world, None, max_len=max_len, batch=1)
+    rec["row_parallel_epilogue"] = note
+    for b in batches:
+        rec[f"batch{b}"] = decode_run(model, dev, rank, world, b, a.prompt, a.new_tokens, not a.no_graph)
+    rec["gpu_launches_per_step"] = 8 * a.layers + 3
+    del model
+    torch.cuda.empty_cache()
+    return rec
 
 
-def moe_layer(a, dev, rank, world):
+# ------------------------------------------------------------------------------------------ MoE
+def moe_run(dev, rank, world, tokens, steps=None):
     """BASELINE configs[4]: 128 experts, top-8 softmax routing from a seeded fp16 gate (2688 -> 128), expert
-    intermediate 1856, gate/up Q3 and down Q4 codes; expert parallel over the ranks (tokens replicated, every rank
-    runs its local experts, all-reduce of the layer output).  value = tokens / time."""
+    intermediate 1856, gate/up Q3 and down Q4 codes; expert parallel over the ranks (tokens replicated, every
+    rank runs its local experts, all-reduce of the layer output)."""
     import torch.distributed as dist
     from polarengine_vllm_b200.moe_method import PolarQuantMoEMethod, route_softmax_topk
     from polarengine_vllm_b200.parallel import expert_placement
     from polarengine_vllm_b200.utils import get_ct_scaled
     E, H, I, K = 128, 2688, 1856, 8
-    T = a.tokens
+    T = tokens
     e_local = E // world
     method = PolarQuantMoEMethod(3, 4)
-    if a.moe_grouped_rows is not None:
-        method.GROUPED_MAX_ROWS_PER_EXPERT = a.moe_grouped_rows
     layer = torch.nn.Module()
     g = torch.Generator(device=dev).manual_seed(4242 + rank)
     hp, ip = 2688, 1920
@@ -303,17 +353,11 @@ def moe_layer(a, dev, rank, world):
             dist.all_reduce(y)
         return y
 
-    if a.probe:  # one layer pass and out: the case captured under ncu
-        step(); step()
-        torch.cuda.synchronize()
-        print(json.dumps({"probe": "moe", "tokens": T}))
-        return
     stream = torch.cuda.Stream(dev)
     local_pairs = method.expected_local_pairs(T * K, e_local, emap)
     grouped = local_pairs <= method.GROUPED_MAX_ROWS_PER_EXPERT * e_local
-    steps = a.steps if a.steps != 4000 else (200 if grouped else 10)
-    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
-    sampler.start()  # from the warm-up on: a query takes longer than a short timed region on a full box
+    if steps is None:
+        steps = 200 if grouped else 10
     with torch.cuda.stream(stream):
         for _ in range(3):
             step()
@@ -332,7 +376,6 @@ def moe_layer(a, dev, rank, world):
             graph.replay() if graph is not None else step()
         e1.record(stream)
         torch.cuda.synchronize()
-        sampler.stop_flag = True
     el = e0.elapsed_time(e1) / 1e3
     if world > 1:
         t = torch.tensor([el], device=dev, dtype=torch.float64)
@@ -343,34 +386,38 @@ def moe_layer(a, dev, rank, world):
     active = int(torch.unique(ids).numel())
     per_expert = 2 * I * (hp // 2 + hp // 128 * 2) + H * (ip // 2 + ip // 128 * 2)
     flops = 2.0 * T * K * (2 * I * H + H * I)
-    if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        ms = el / steps * 1e3
-        print(json.dumps({
-            "metric": "MoE layer tokens/s", "unit": "tok/s", "value": T * steps / el, "n_gpus": a.gpus, "steps": steps,
-            "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"moe_layer (BASELINE configs[4]): 128 experts top-8, hidden 2688, intermediate 1856, "
-                                   f"gate/up Q3 down Q4, {T} tokens", "parallelism": f"ep{world}",
-                       "path": ("two grouped tcgen05 launches (pe_gemm_grouped), CUDA graph" if local_pairs >= method.TENSOR_CORE_MIN_ROWS_PER_EXPERT * e_local
-                                else "two grouped decode-size launches (pe_gemv_grouped), CUDA graph") if grouped
-                               else "per-expert tensor-core matmuls, eager",
-                       "l2_defeat": "expert weights 970 MB >> L2"},
-            "active_experts": active, "expert_bytes_per_step": active * per_expert,
-            "weight_gbs": active * per_expert / (ms / 1e3) / 1e9,
-            "hbm_frac_of_measured": active * per_expert / (ms / 1e3) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)) / world,
-            "tflops": flops / (ms / 1e3) / 1e12, "clocks": sampler.summary(),
-            "gpu_launches": steps * (5 if grouped else 2 * min(active, e_local))}))
-    finish(world)
+    peaks = load_peaks()
+    ms = el / steps * 1e3
+    tensor = local_pairs >= method.TENSOR_CORE_MIN_ROWS_PER_EXPERT * e_local
+    rec = {"tokens": T, "tok_s": T * steps / el, "ms_per_layer": ms, "steps": steps, "parallelism": f"ep{world}",
+           "path": (("two grouped tcgen05 launches (pe_gemm_grouped), CUDA graph" if tensor
+                     else "two grouped decode-size launches (pe_gemv_grouped), CUDA graph") if grouped
+                    else "per-expert tensor-core matmuls, eager"),
+           "active_experts": active, "expert_bytes_per_step": active * per_expert,
+           "weight_gbs": active * per_expert / (ms / 1e3) / 1e9,
+           "hbm_frac_of_measured": active * per_expert / (ms / 1e3) / 1e9 / float(peaks.get("hbm_gbs", 6650.0)) / world,
+           "tflops": flops / (ms / 1e3) / 1e12,
+           "tensor_frac_of_burst": flops / (ms / 1e3) / 1e12 / float(peaks.get("bf16_tflops", 1590.0)) / world,
+           "gpu_launches": steps * (5 if grouped else 2 * min(active, e_local))}
+    if graph is not None:
+        graph.reset()
+    return rec
 
 
+def moe_record(dev, rank, world, token_counts=(64, 2048)):
+    rec = {"config": "128 experts top-8, hidden 2688, intermediate 1856, gate/up Q3, down Q4; expert weights 970 MB >> L2"}
+    for t in token_counts:
+        rec[f"tokens{t}"] = moe_run(dev, rank, world, t)
+        torch.cuda.empty_cache()
+    return rec
+
+
+# ------------------------------------------------------------------------------------------ leaving
 def finish(world):
-    """Leave a multi-rank run.  Tearing down the NCCL communicator while captured graphs that contain its kernels are
-    alive can block forever; the ranks synchronise and exit without running the destructors instead."""
+    """Leave a multi-rank run in order: captured graphs were reset by their owners, every rank has finished its
+    device work, then the process group is destroyed.  (Destroying the communicator while captured graphs that
+    hold its kernels were alive blocked a 2-GPU run for good.)  A watchdog ends the process if the teardown
+    does not return within 30 s: the result line is already printed."""
     if world > 1:
         import torch.distributed as dist
         torch.cuda.synchronize()
@@ -378,31 +425,40 @@ def finish(world):
         torch.cuda.synchronize()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        threading.Timer(30.0, lambda: os._exit(0)).start()
+        dist.destroy_process_group()
+        os._exit(0)  # the timer thread must not keep the interpreter alive
+
+
+def sub_record(fn, *args, **kw):
+    """A secondary measurement must not take the headline down with it."""
+    try:
+        return fn(*args, **kw)
+    except Exception as exc:
+        torch.cuda.synchronize()
+        return {"error": f"{type(exc).__name__}: {exc}"}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=40)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model", "moe"],
-                    help="decode: decoder-layer GEMV pass (default, the headline); prefill: Q4 GEMM sweep of BASELINE "
-                         "configs[2]; model: 36-layer 9B-class decode tok/s, tensor parallel over --gpus (configs[3])")
-    ap.add_argument("--layers", type=int, default=36, help="decoder layers for --workload model")
+                    help="decode: decoder-layer GEMV pass (default, the headline) followed by the prefill, model and moe "
+                         "records; prefill / model / moe: that record alone")
+    ap.add_argument("--headline-only", action="store_true", help="decode workload without the prefill / model / moe records")
+    ap.add_argument("--secondary-limit", type=float, default=480.0, help="seconds the prefill / model / moe records may take together")
+    ap.add_argument("--layers", type=int, default=36, help="decoder layers of the model record")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
-    ap.add_argument("--no-graph", action="store_true", help="model workload: launch decode steps eagerly")
-    ap.add_argument("--nccl-allreduce", action="store_true", help="model workload: NCCL all-reduce instead of the fused peer-memory epilogue")
-    ap.add_argument("--m", type=int, default=4096, help="tokens for --workload prefill")
-    ap.add_argument("--tokens", type=int, default=64, help="tokens for --workload moe (1 / 64 / 2048)")
-    ap.add_argument("--moe-grouped-rows", type=int, default=None,
-                    help="moe workload: average rows per expert up to which the grouped launches are used (default: the method's)")
-    ap.add_argument("--probe", default=None, metavar="PROJ",
-                    help="profiling aid: launch PROJ (e.g. down_proj) once per ring layer and exit, no timing")
+    ap.add_argument("--no-graph", action="store_true", help="model record: launch decode steps eagerly")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="model record: NCCL all-reduce instead of the fused peer-memory epilogue")
+    ap.add_argument("--m", type=int, default=4096, help="tokens of the prefill record")
+    ap.add_argument("--tokens", type=int, default=None, help="moe workload alone: one token count instead of 64 and 2048")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -410,7 +466,8 @@ def main():
     config = {"workload": "decoder_layer_gemv (BASELINE configs[1]): q/k/v Q5 fused, o Q6, gate/up Q3 fused, down Q4; "
                           "hidden 4096, intermediate 12288", "batch": a.batch, "ring_layers": RING,
               "l2_defeat": "inputs larger than L2 (ring of 8 layers = 964 MB of codes)",
-              "parallelism": f"replicas x{a.gpus}: each rank streams its own layers, no collective"}
+              "parallelism": f"replicas x{a.gpus}: each rank streams its own layers, no collective (the model_decode and "
+                             f"moe records shard over the ranks)"}
     base = {"metric": "quantized GEMV HBM GB/s", "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": config}
@@ -421,6 +478,7 @@ def main():
         # The reference has no CPU implementation of apply() (its Triton wrappers need a GPU);
         # its CPU-runnable path is the torch math its kernels are tested against = the oracle.
         cb, per_step = cpu_baseline(a.batch, budget_s=max(5.0, min(60.0, 0.3 * (a.steps + a.warmup))))
+        config["parallelism"] = "one host: the CPU arm runs on rank 0 only, whatever --gpus says"
         line = dict(base, impl="reference", value=cb["value"], ms_per_step=per_step * 1e3, cpu_baseline=cb, gpu_launches=0,
                     e2e={"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
         print(json.dumps(line))
@@ -435,26 +493,49 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     from polarengine_vllm_b200 import kernels
     from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
-    if a.workload == "prefill":
-        prefill_sweep(a, dev, rank, world)
-        return finish(world)
-    if a.workload == "moe":
-        return moe_layer(a, dev, rank, world)
-    if a.workload == "model":
-        return model_decode(a, dev, rank, world)
+    peaks = load_peaks()
 
-    steps = max(RING, a.steps // RING * RING)
+    if a.workload != "decode":  # one secondary record alone, as its own line
+        common = {"n_gpus": a.gpus, "higher_is_better": True, "vs_baseline": None, "data": "synthetic", "warmup": 3}
+        sampler = ClockSampler(local)
+        sampler.start()
+        if a.workload == "prefill":
+            rec = prefill_record(dev, a.m, max(3, min(a.steps, 50)))
+            best = max(rec["shapes"].values(), key=lambda s: s["tflops"])
+            line = dict(common, metric="prefill quantized GEMM TFLOP/s", unit="TFLOP/s", value=best["tflops"], steps=rec["steps"],
+                        ms_per_step=best["ms"], scaling="weak", dtype="bf16",
+                        config={"workload": f"prefill_gemm (BASELINE configs[2]) M={a.m}, Q4"}, prefill=rec, gpu_launches=rec["gpu_launches"])
+        elif a.workload == "model":
+            rec = model_record(a, dev, rank, world, (a.batch,))
+            r = rec[f"batch{a.batch}"]
+            line = dict(common, metric="9B-class decode tok/s", unit="tok/s", value=r["tok_s"], steps=a.new_tokens,
+                        ms_per_step=r["ms_per_step"], scaling="strong", dtype="f16",
+                        config={"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers", "batch": a.batch,
+                                "parallelism": f"tp{world}"}, model_decode=rec, gpu_launches=a.new_tokens * rec["gpu_launches_per_step"])
+        else:
+            rec = moe_record(dev, rank, world, (a.tokens,) if a.tokens else (64, 2048))
+            first = next(v for k, v in rec.items() if k.startswith("tokens"))
+            line = dict(common, metric="MoE layer tokens/s", unit="tok/s", value=first["tok_s"], steps=first["steps"],
+                        ms_per_step=first["ms_per_layer"], scaling="strong", dtype="f16",
+                        config={"workload": "moe_layer (BASELINE configs[4])", "parallelism": f"ep{world}"}, moe=rec,
+                        gpu_launches=first["gpu_launches"])
+        sampler.stop_flag = True
+        line["clocks"] = sampler.summary()
+        if rank == 0:
+            print(json.dumps(line))
+        return finish(world)
+
+    # ---- headline: the decoder-layer pass
+    ring_passes = max(1, math.ceil(a.steps / RING))  # the graph holds RING steps: the asked-for step count is rounded up
     warm = max(3, a.warmup)
     layers = [make_layer(dev, 1000 + 16 * i + 97 * rank) for i in range(RING)]
     g = torch.Generator(device=dev).manual_seed(7)
     xh = torch.randn(a.batch, HIDDEN, device=dev, generator=g).half()
     xi = torch.randn(a.batch, INTER, device=dev, generator=g).half()
-    outs = {name: torch.empty(a.batch, n, dtype=torch.float16, device=dev) for name, n, _, _ in PROJ}
 
     def launch(layer, name):
-        w, packed, norms, ct, n, k, tiles = layer[name]
-        return kernels.quant_matmul(w, packed, norms, ct, xh if k == HIDDEN else xi, False, n, k, k, torch.float16,
-                                    tiles=tiles)
+        w, packed, norms, ct, n, k = layer[name]
+        return kernels.quant_matmul(w, packed, norms, ct, xh if k == HIDDEN else xi, False, n, k, k, torch.float16)
 
     def ring_pass(names):
         for layer in layers:
@@ -462,48 +543,53 @@ def main():
                 launch(layer, name)
 
     all_names = [p[0] for p in PROJ]
-    if a.probe:
-        ring_pass([a.probe])
-        torch.cuda.synchronize()
-        print(json.dumps({"probe": a.probe, "launches": RING, "batch": a.batch}))
-        return
     stream = torch.cuda.Stream(dev)
 
-    def timed_graph(names, reps, warm_reps):
-        """Capture one ring pass (RING steps) as a CUDA graph and time `reps` replays."""
+    def timed_graph(names, passes, warm_passes):
+        """Capture one ring pass (RING steps) as a CUDA graph and time `passes` replays, repeated until the
+        timed region is at least MIN_TIMED_S long.  Returns (seconds, ring passes timed)."""
         with torch.cuda.stream(stream):
             ring_pass(names)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 ring_pass(names)
-            for _ in range(warm_reps):
+            for _ in range(warm_passes):
                 graph.replay()
             torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
+            total, done = 0.0, 0
+            while True:
+                if world > 1:
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(passes):
+                    graph.replay()
+                e1.record(stream)
                 torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(reps):
-                graph.replay()
-            e1.record(stream)
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            return e0.elapsed_time(e1) / 1e3
+                el = e0.elapsed_time(e1) / 1e3
+                if world > 1:
+                    dist.barrier()
+                    t = torch.tensor([el], device=dev, dtype=torch.float64)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    el = float(t)
+                total += el
+                done += passes
+                if total >= MIN_TIMED_S or done >= 200000:
+                    break
+                passes = max(passes, int(passes * (MIN_TIMED_S - total) / max(el, 1e-6)) + 1)  # same on every rank (el is the max)
+            graph.reset()
+            return total, done
 
     sampler = ClockSampler(local)
     sampler.start()
-    elapsed = timed_graph(all_names, steps // RING, max(1, math.ceil(warm / RING)))
+    elapsed, passes_done = timed_graph(all_names, ring_passes, max(1, math.ceil(warm / RING)))
+    steps = passes_done * RING
     # dominant kernel alone: the nibble-code GEMV on the 4096x12288 Q4 layer (down_proj)
     dom = ["down_proj"]
-    dom_elapsed = timed_graph(dom, steps // RING, 1)
+    dom_elapsed, dom_passes = timed_graph(dom, ring_passes, 1)
     sampler.stop_flag = True
-    if world > 1:
-        t = torch.tensor([elapsed], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed = float(t)
     value = step_bytes(a.batch) * steps * world / elapsed / 1e9
 
     # ---- end to end through the plugin surface with host buffers
@@ -512,7 +598,7 @@ def main():
     for name, n, k, bits in PROJ:
         m = PolarQuantLinearMethod(128, bits)
         mod = torch.nn.Module()
-        w, packed, norms, ct, _, _, tiles = layers[0][name]
+        w, packed, norms, ct, _, _ = layers[0][name]
         mod.in_f, mod.out_f, mod.in_f_padded, mod.n_blocks, mod.bits, mod.block_size = k, n, k, k // 128, bits, 128
         mod.packed, mod.norms, mod.ct_scaled = packed, norms, ct
         if packed:
@@ -522,16 +608,15 @@ def main():
         method[name], mods[name] = m, mod
     hx = {k: torch.randn(a.batch, k).half().pin_memory() for k in (HIDDEN, INTER)}
     hy = torch.empty(a.batch, HIDDEN, dtype=torch.float16).pin_memory()
-    e2e_steps = min(steps, 1000)
+    e2e_steps = min(max(steps, 200), 1000)
 
     def e2e_body(i, dx):
         layer = layers[i % RING]
         y = None
         for name, n, k, bits in PROJ:
             mod = mods[name]
-            w, packed, norms, ct, _, _, tiles = layer[name]
+            w, packed, norms, ct, _, _ = layer[name]
             mod.norms = norms
-            mod.codes_tiled = tiles
             if packed:
                 mod.codes_packed = w
             else:
@@ -555,12 +640,12 @@ def main():
                 dx_static[k].copy_(hx[k], non_blocking=True)
             hy.copy_(e2e_body(i, dx_static), non_blocking=True)  # warm the allocator
             torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream, capture_error_mode="thread_local"):
                 for k in hx:
                     dx_static[k].copy_(hx[k], non_blocking=True)
                 hy.copy_(e2e_body(i, dx_static), non_blocking=True)
-            graphs.append(g)
+            graphs.append(gr)
 
     def e2e_step_graph(i):
         graphs[i % RING].replay()
@@ -586,34 +671,55 @@ def main():
 
     e2e_graph = time_e2e(e2e_step_graph)
     e2e_eager = time_e2e(e2e_step_eager)
+    for gr in graphs:
+        gr.reset()
     e2e = {"value": e2e_graph, "unit": "GB/s",
            "h2d_bytes_per_step": a.batch * (HIDDEN + INTER) * 2, "d2h_bytes_per_step": a.batch * HIDDEN * 2,
            "steps": e2e_steps, "eager_value": e2e_eager,
            "api": "PolarQuantLinearMethod.apply x4 per step with pinned host in/out copies, the step captured in a "
                   "CUDA graph and waited on by the host after every replay; eager_value = same step without the graph"}
 
-    if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        dom_launches = steps
-        dom_bytes = sum(alg_bytes(n, k, b, a.batch) for nm, n, k, b in PROJ if nm in dom)
-        achieved = dom_bytes / (dom_elapsed / dom_launches) / 1e9
-        roofline = {"bound": "hbm", "kernel": "gemv_cols_kernel<packed, table, 3 chunks per warp> on down_proj 4096x12288 Q4", "achieved": achieved,
-                    "peak": peak, "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
-                    "unit": "GB/s", "frac": achieved / peak, "avg_launch_us": dom_elapsed / dom_launches * 1e6,
-                    "alg_bytes_per_launch": dom_bytes,
-                    # dram__bytes_read.sum + dram__bytes_write.sum of one batch-1 launch (profiles/)
-                    "traffic": NCU_DRAM_BYTES_DOWN_B1 if a.batch == 1 else None}
-        line = dict(base, value=value, ms_per_step=elapsed / steps * 1e3, steps=steps, e2e=e2e, gpu_launches=4 * steps,
-                    roofline=roofline, clocks=sampler.summary(),
-                    frac_of_measured_hbm=value / world / peak)
-        if not a.no_cpu_baseline:
-            line["cpu_baseline"], _ = cpu_baseline(a.batch)
-        print(json.dumps(line))
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    dom_launches = dom_passes * RING
+    dom_bytes = sum(alg_bytes(n, k, b, a.batch) for nm, n, k, b in PROJ if nm in dom)
+    achieved = dom_bytes / (dom_elapsed / dom_launches) / 1e9
+    roofline = {"bound": "hbm", "kernel": "gemv_stream_kernel<nibble codes, table, 3 chunks per warp> on down_proj 4096x12288 Q4",
+                "achieved": achieved, "peak": peak, "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
+                "unit": "GB/s", "frac": achieved / peak, "avg_launch_us": dom_elapsed / dom_launches * 1e6,
+                "alg_bytes_per_launch": dom_bytes, "launches_timed": dom_launches,
+                "traffic": measured_traffic("down_proj_b1") if a.batch == 1 else None}
+    line = dict(base, value=value, ms_per_step=elapsed / steps * 1e3, steps=steps, steps_requested=a.steps, e2e=e2e,
+                gpu_launches=4 * steps, roofline=roofline, clocks=sampler.summary(), frac_of_measured_hbm=value / world / peak,
+                timed_region_s=elapsed)
+    del layers, mods, graphs
+    torch.cuda.empty_cache()
+
+    if rank == 0 and not a.no_cpu_baseline and world == 1:
+        line["cpu_baseline"], _ = cpu_baseline(a.batch)
+
+    # The secondary records run under a time limit: if one of them stalls (a rank that left a collective), the
+    # line is printed with what has been measured and the process ends.
+    emitted = threading.Lock()
+
+    def emit():
+        if emitted.acquire(blocking=False) and rank == 0:
+            print(json.dumps(line))
+            sys.stdout.flush()
+
+    def out_of_time():
+        line["secondary_records_cut_short_after_s"] = a.secondary_limit
+        emit()
+        os._exit(0)
+
+    if not a.headline_only:
+        limit = threading.Timer(a.secondary_limit, out_of_time)
+        limit.daemon = True
+        limit.start()
+        line["prefill"] = sub_record(prefill_record, dev, a.m)
+        line["model_decode"] = sub_record(model_record, a, dev, rank, world)
+        line["moe"] = sub_record(moe_record, dev, rank, world)
+        limit.cancel()
+    emit()
     finish(world)
 
 

@@ -50,10 +50,20 @@ enum {
   PE_ERR_LIMIT = -7      /* size beyond a compiled-in maximum                    */
 };
 
+/* values a kernel leaves in a status word when a bounded device-side wait ran out */
+enum {
+  PE_STATUS_SPLITK_TIMEOUT = 1 /* pe_gemv tile kernel: a split-K partial never arrived */
+};
+
 int pe_version(void);
 const char* pe_error_string(int code);
 /* cudaError_t of the last failing runtime call made by this library on this thread */
 int pe_last_cuda_error(void);
+
+/* Kernels that wait on another party (a peer rank's flag in pe_allreduce_add_rmsnorm) give up after a limit, record a status value and return, so that a
+ * missing peer costs a bounded time and never a hung GPU.  The default is about one second; this
+ * sets it for launches made afterwards (process-wide).  No counterpart in the reference. */
+int pe_set_wait_limit_us(int64_t microseconds);
 
 /* One-time per-device set-up (opt-in shared-memory sizes, SM count).  Safe to call
  * repeatedly.  Makes `device` current.  No counterpart in the reference. */
@@ -133,11 +143,16 @@ int pe_pack_nibble(const int8_t* codes, uint8_t* packed, int64_t out_f, int64_t 
  *           (zero-fill the buffer once after allocating it); every call returns
  *           them to zero, so the buffer can be reused by later calls of any shape
  *           on the same stream without refilling.  Calls that share a scratch
- *           buffer must not overlap on the device.
+ *           buffer must not overlap on the device.  The last int32 of those 256 KB
+ *           is a status word: a kernel whose bounded device-side wait ran out stores
+ *           a PE_STATUS_* value there (the output is then undefined);
+ *           pe_gemv_status() waits for the stream and returns the word (0 = ok),
+ *           clearing it when `clear` is non-zero.
  *
  * Replaces polar_matmul's batch==1 branches and (for 2..16 rows) its GEMM branch
  * (polar_gemm.py:485-534), plus the cast/bias epilogue of linear_method.py:214-221. */
 size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded);
+int pe_gemv_status(void* workspace, size_t workspace_bytes, int clear, void* stream);
 int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
             const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
@@ -187,7 +202,8 @@ int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, int64_t cod
 /* ---- mixture-of-experts bookkeeping on the device ----------------------------------
  * pe_moe_plan groups the (token, slot) pairs of a routing decision by local expert:
  *   topk_ids (n_pairs = tokens * top_k, int64, token-major); expert_map (optional, int64,
- *   global expert -> local index or -1, the expert-parallel placement);
+ *   global expert -> local index or -1, the expert-parallel placement, n_global_experts
+ *   entries: ids outside [0, n_global_experts) are treated as -1);
  *   row_token[r] = token of grouped row r (the x_rows list of pe_gemv_grouped),
  *   pos[pair] = grouped row of the pair or -1 if its expert lives on another rank,
  *   problems = the problem list of pe_gemv_grouped with at most rows_per_problem rows each
@@ -198,7 +214,7 @@ int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, int64_t cod
  *   with pos < 0 contribute nothing), y fp32 (rows, hidden), out fp32/fp16/bf16.
  * Together with pe_gemv_grouped they replace the per-expert Python loop of the reference's
  * MoE layer (nemotron_offload.py:190-226: index tokens, run the expert, index_add). */
-int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, int n_pairs, int top_k, int n_local_experts,
+int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, int n_global_experts, int n_pairs, int top_k, int n_local_experts,
                 int rows_per_problem, int max_problems, int32_t* row_token, int32_t* pos, int32_t* problems,
                 int32_t* expert_rows, void* stream);
 int pe_moe_combine(const float* y, int64_t ld_y, const int32_t* pos, const float* topk_weights, int tokens, int top_k,
@@ -273,8 +289,12 @@ int pe_gemm(const void* codes, int packed, int64_t ld_codes, const void* norms, 
  *  - All calls on a device share the one array and it keeps the previous call's
  *    contents; the entry point clears the counters it needs, in stream order, before
  *    the kernel.  Two calls that overlap on the GPU (different streams) race on it:
- *    keep them on one stream or order them with events. */
+ *    keep them on one stream or order them with events.
+ *  - A bounded device-side wait that runs out leaves a PE_STATUS_* value in a word of the
+ *    array; pe_gemv_noalloc_status() waits for the stream and returns that word (0 = every
+ *    wait completed), clearing it when `clear` is non-zero.  It allocates nothing either. */
 size_t pe_gemv_noalloc_max_bytes(void);
+int pe_gemv_noalloc_status(int clear, void* stream);
 int pe_gemv_noalloc(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
                     const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
                     int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,

@@ -27,6 +27,7 @@ SIGNATURES = {
     "pe_error_string": (ctypes.c_char_p, [_i]),
     "pe_last_cuda_error": (_i, []),
     "pe_init": (_i, [_i]),
+    "pe_set_wait_limit_us": (_i, [_i64]),
     "pe_fwht128": (_i, [_vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "pe_embedding": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "pe_pack_nibble": (_i, [_vp, _vp, _i64, _i64, _vp]),
@@ -36,7 +37,7 @@ SIGNATURES = {
     "pe_gemv_grouped_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv_grouped": (_i, [_vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _vp, _i, _i64, _vp,
                             _i, _i, _i, _i, _vp, _sz, _vp]),
-    "pe_moe_plan": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "pe_moe_plan": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "pe_gemm_grouped_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pe_gemm_grouped": (_i, [_vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _vp, _i, _i64, _vp,
                             _i, _i, _i, _i, _vp, _sz, _vp]),
@@ -54,6 +55,8 @@ SIGNATURES = {
     "pe_silu_mul": (_i, [_vp, _i64, _vp, _i64, _i, _i, _vp]),
     "pe_decode_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pe_decode_attention": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "pe_gemv_status": (_i, [_vp, _sz, _i, _vp]),
+    "pe_gemv_noalloc_status": (_i, [_i, _vp]),
     "pe_gemv_noalloc_max_bytes": (_sz, []),
     "pe_gemv_noalloc": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                              _vp]),
@@ -61,7 +64,8 @@ SIGNATURES = {
 
 
 def library_path() -> str:
-    """The in-tree build; POLAR_B200_LIB points developers at an instrumented build."""
+    """The in-tree build, or the file POLAR_B200_LIB names (a supported way to load a build kept elsewhere,
+    e.g. one compiled with other flags for an A/B comparison)."""
     return os.environ.get("POLAR_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), _LIB_NAME)
 
 

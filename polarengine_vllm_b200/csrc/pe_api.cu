@@ -4,6 +4,10 @@
 namespace pe {
 thread_local int g_last_cuda_error = 0;
 
+// Limit of the device-side waits on another party (a peer's flag, a bulk copy), in clock cycles.
+static long long g_wait_limit_cycles = 2000000000ll;  // about one second at 2 GHz
+long long wait_limit_cycles() { return g_wait_limit_cycles; }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -32,6 +36,12 @@ extern "C" const char* pe_error_string(int code) {
     case PE_ERR_LIMIT: return "size beyond a compiled-in maximum";
     default: return "unknown error";
   }
+}
+
+extern "C" int pe_set_wait_limit_us(int64_t microseconds) {
+  if (microseconds < 1 || microseconds > 60ll * 1000 * 1000) return PE_ERR_ARG;
+  pe::g_wait_limit_cycles = microseconds * 2000;  // SM clocks run at up to 2 GHz: an upper bound in cycles
+  return PE_OK;
 }
 
 extern "C" int pe_init(int device) {

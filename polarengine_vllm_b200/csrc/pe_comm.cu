@@ -39,7 +39,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 
 __global__ void __launch_bounds__(kArThreads) allreduce_add_rmsnorm_kernel(const float* partial, __half* x, const __half* w, __half* out,
                                                                            int hidden, float eps, const uint64_t* peers, int rank,
-                                                                           int world, int max_rows, unsigned* seq, int* status) {
+                                                                           int world, int max_rows, unsigned* seq, int* status,
+                                                                           long long wait_limit) {
   __shared__ float warp_sums[kArThreads / 32];
   const int row = blockIdx.x, tid = threadIdx.x;
   pdl_enter();
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_add_rmsnorm_kernel(const
     const unsigned* flag = reinterpret_cast<const unsigned*>(peers[rank]) + (size_t)tid * max_rows + row;
     const long long t0 = clock64();
     while ((int)(ld_acquire_sys(flag) - s) < 0) {
-      if (clock64() - t0 > (1ll << 31)) {  // about a second: a peer never arrived
+      if (clock64() - t0 > wait_limit) {  // about a second unless the host set another limit: a peer never arrived
         atomicExch(status, 1);
         break;
       }
@@ -160,6 +161,6 @@ extern "C" int pe_allreduce_add_rmsnorm(const float* partial, void* x, const voi
     return PE_ERR_ALIGN;
   PE_CUDA_TRY(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(rows), dim3(kArThreads), 0, static_cast<cudaStream_t>(stream), partial,
                          static_cast<__half*>(x), static_cast<const __half*>(weight), static_cast<__half*>(out), hidden, eps,
-                         peer_buffers, rank, world, max_rows, seq, status));
+                         peer_buffers, rank, world, max_rows, seq, status, wait_limit_cycles()));
   return PE_OK;
 }

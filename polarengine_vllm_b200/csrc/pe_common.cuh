@@ -24,6 +24,7 @@ inline int cuda_fail(cudaError_t e) {
   } while (0)
 
 int sm_count();  // SM count of the current device (cached per device)
+long long wait_limit_cycles();  // limit of device-side waits on another party (pe_set_wait_limit_us)
 
 // Launch with programmatic stream serialization: the grid may start while its predecessor
 // in the stream is still draining.  The kernel must call pdl_enter() (or its own

@@ -60,7 +60,6 @@ struct GemvArgs {
   int max_slots;     // scratch partials per 16-row tile
   float* ws_part; unsigned* ws_cnt; int* ws_status;
   unsigned dyn_bytes;
-  long long* prof;  // optional per-warp time stamps (developer builds with -DPE_PROFILE)
   // grouped launch (blockIdx.y = problem): several matrices of one shape -- the experts of
   // a mixture layer -- each against its own few activation rows
   const int* x_rows;          // activation row m of the problem is row x_rows[m] of x (nullptr: row m)
@@ -70,12 +69,6 @@ struct GemvArgs {
 };
 
 __device__ __forceinline__ int64_t x_row_of(const GemvArgs& p, int m) { return p.x_rows ? (int64_t)p.x_rows[m] : (int64_t)m; }
-
-#ifdef PE_PROFILE
-#define PE_STAMP(i) do { if (p.prof && lane == 0) p.prof[((size_t)blockIdx.x * kWarps + w) * 8 + (i)] = clock64(); } while (0)
-#else
-#define PE_STAMP(i) do { } while (0)
-#endif
 
 __device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -611,7 +604,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
   __shared__ int slot_rt[32], slot_blk[32];
   __shared__ GemvArgs grp_args;
   if (GROUPED) {
-    // this CTA's problem: patch a copy of the arguments (matrix, rows, output, scratch)
+    // this CTA's problem: patch a copy of the arguments (matrix, rows, output, scratch).  The problem list
+    // is written by the launch before this one (pe_moe_plan), so it is read only after the dependency wait;
+    // a grouped launch therefore overlaps nothing with its predecessor but its own start-up.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int4 d = pin.grp[blockIdx.y];
     if (d.z <= 0) return;  // unused problem slot
     if (threadIdx.x == 0) {
@@ -635,7 +632,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int G = gridDim.x, cta = blockIdx.x;
-  PE_STAMP(0);
 
   // ---- this CTA's and this warp's share of the step line
   const int s_beg = range_start(p.S, G, cta), s_end = range_start(p.S, G, cta + 1);
@@ -721,7 +717,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
 
-  PE_STAMP(7);
   if (lane < cnt0 && w == 0) { slot_rt[lane] = my_rt; slot_blk[lane] = my_blk; }
 
   // ---- centroid table, replicated per lane.  Warp w writes entries w, w+16, ...; the
@@ -752,12 +747,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
       else { tb.lo1 |= (hb & 0xff) << (8 * (i - 4)); tb.hi1 |= (hb >> 8) << (8 * (i - 4)); }
     }
   }
-  PE_STAMP(1);
   if (!TILED && lane < cnt0) {
 #pragma unroll
     for (int u = 0; u < NU; ++u) reinterpret_cast<unsigned short*>(ns)[(w + u * kWarps) * nstr + lane] = nv[u];
   }
-  PE_STAMP(2);
   if (p.x_kind == PE_X_RAW) {
     if (w < items0) {
       cvt4(xraw, p.x_dtype, xv);
@@ -772,7 +765,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
     __syncthreads();
     stage_x<PACKED>(p, xs, slot_blk, cnt0, w, lane);
   }
-  PE_STAMP(3);
 
   float acc[NB / 2];
 #pragma unroll
@@ -804,7 +796,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
       stage_x<PACKED>(p, xs, slot_blk, cnt, w, lane);
     }
     __syncthreads();
-    PE_STAMP(4);
     first_phase = false;
     const int q_stop = q_hi < ph_end ? q_hi : ph_end;
     while (q < q_stop) {
@@ -871,7 +862,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
       }
     }
   }
-  PE_STAMP(5);
   // every row-tile-of-256 this CTA's range touches gets a hand-off from every warp
   if (run > 0) {
     for (; next_flush < rt_c; ++next_flush)
@@ -890,7 +880,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs pin) {
   // A CTA owns the last step of at most one shared tile (only the first tile of its range
   // can have started in an earlier CTA and end here; later shared tiles end further on).
   if (pending >= 0) reduce_tile(p, pending, w, G, lane);
-  PE_STAMP(6);
 }
 
 // ---- host side -----------------------------------------------------------------
@@ -941,12 +930,6 @@ static constexpr int kMaxSms = 256;
 
 using namespace pe;
 
-static long long* g_prof = nullptr;
-#ifdef PE_PROFILE
-// developer hook: device buffer of gridDim * 16 * 8 int64 receiving clock64 stamps
-extern "C" void pe_debug_set_profile_buffer(void* p) { g_prof = static_cast<long long*>(p); }
-#endif
-
 extern "C" size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded) {
   if (batch < 1 || batch > 16 || out_f < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
   if ((out_f + 15) / 16 > kMaxRowTiles) return 0;
@@ -993,12 +976,11 @@ static int launch(const GemvArgs& a, const Plan& pl, cudaStream_t st) {
                  : launch_t<PACKED, NB, DEPTH, REGTAB, FMA, false>(a, pl, st);
 }
 
-// Shared by pe_gemv (row-major codes + norms) and pe_gemv_tiled (tiles != nullptr).
-static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
-                    const void* tiles, const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype,
-                    int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
-                    int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!ct_scaled || !x || !y || !workspace) return PE_ERR_ARG;
+// Argument checks shared by every decode-size entry point.
+static int gemv_check(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms, const void* tiles,
+                      const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f,
+                      void* y, int y_dtype, int64_t ld_y, int batch, int out_f, int in_f_padded) {
+  if (!ct_scaled || !x || !y) return PE_ERR_ARG;
   if (!tiles && (!codes || !norms)) return PE_ERR_ARG;
   if (batch < 1 || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
   if (x_kind != PE_X_ROTATED && x_kind != PE_X_RAW) return PE_ERR_ARG;
@@ -1012,12 +994,26 @@ static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void*
     if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
   }
   if (ld_x < (x_kind == PE_X_RAW ? in_f : in_f_padded) || ld_y < out_f) return PE_ERR_ARG;
+  return PE_OK;
+}
 
-  if (!tiles) {  // one or two activation rows over whole-row items: the row-owner kernel, no scratch
-    const int r = gemv_rows_try(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
-                                y_dtype, ld_y, bias, batch, out_f, in_f_padded, static_cast<cudaStream_t>(stream));
-    if (r <= 0) return r;
-  }
+// One or two activation rows over the row-major arrays: kernels that own whole weight rows and use no scratch
+// (only the status word, when a workspace is given).  PE_OK after a launch, 1 if the shape is not theirs.
+static int gemv_scratch_free(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                             const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
+                             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+                             int in_f_padded, void* workspace, void* stream) {
+  int* status = workspace ? reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kCounterBytes - 4) : nullptr;
+  return gemv_rows_try(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y, y_dtype,
+                       ld_y, bias, batch, out_f, in_f_padded, status, static_cast<cudaStream_t>(stream));
+}
+
+// The tile kernel (any batch up to 16, either layout); arguments already checked.
+static int gemv_tile_run(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                         const void* tiles, const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype,
+                         int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+                         int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace) return PE_ERR_ARG;
   const int sms = sm_count();
   if (sms <= 0) return PE_ERR_CUDA;
   if (sms > kMaxSms || (out_f + 15) / 16 > kMaxRowTiles) return PE_ERR_LIMIT;
@@ -1042,7 +1038,6 @@ static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void*
   // the deepest code ring that fits beside table, activation slots and norms
   const unsigned ring_need = kWarps * 8u * (tiles ? (unsigned)TileGeom<true>::kStageBytes : 1024u);
   const bool deep = (tiles ? pl.fixed_bytes_tiled : pl.fixed_bytes) + ring_need <= 231424u;
-  a.prof = g_prof;
   a.x_rows = nullptr; a.grp = nullptr; a.grp_codes_stride = a.grp_norms_stride = 0; a.grp_ws_stride = a.grp_cnt_bytes = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // DEPTH = ring stages per warp (1 KB nibble / 2 KB byte stages): 8 KB per warp when it fits, else 6 / 4 KB
@@ -1063,12 +1058,46 @@ static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void*
   return launch<false, 16, 2, false>(a, pl, st);
 }
 
+// Shared by pe_gemv (row-major codes + norms) and pe_gemv_tiled (tiles != nullptr).
+static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                    const void* tiles, const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype,
+                    int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
+                    int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace) return PE_ERR_ARG;
+  const int c = gemv_check(codes, packed, ld_codes, norms, ld_norms, tiles, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
+                           y_dtype, ld_y, batch, out_f, in_f_padded);
+  if (c != PE_OK) return c;
+  if (!tiles && batch <= 2) {
+    const int r = gemv_scratch_free(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f,
+                                    y, y_dtype, ld_y, bias, batch, out_f, in_f_padded,
+                                    workspace_bytes >= kCounterBytes ? workspace : nullptr, stream);
+    if (r <= 0) return r;
+  }
+  return gemv_tile_run(codes, packed, ld_codes, norms, ld_norms, tiles, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
+                       y_dtype, ld_y, bias, batch, out_f, in_f_padded, workspace, workspace_bytes, stream);
+}
+
 extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
                        const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
                        int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,
                        int in_f_padded, void* workspace, size_t workspace_bytes, void* stream) {
   return gemv_run(codes, packed, ld_codes, norms, ld_norms, nullptr, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
                   y_dtype, ld_y, bias, batch, out_f, in_f_padded, workspace, workspace_bytes, stream);
+}
+
+// Reads a status word back (and optionally clears it): waits for the stream, no allocation.
+static int read_status_word(int* word, int clear, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  PE_CUDA_TRY(cudaMemcpyAsync(&v, word, sizeof(int), cudaMemcpyDeviceToHost, st));
+  PE_CUDA_TRY(cudaStreamSynchronize(st));
+  if (clear && v != 0) PE_CUDA_TRY(cudaMemsetAsync(word, 0, sizeof(int), st));
+  return v < 0 ? 0 : v;
+}
+
+extern "C" int pe_gemv_status(void* workspace, size_t workspace_bytes, int clear, void* stream) {
+  if (!workspace || workspace_bytes < kCounterBytes) return PE_ERR_ARG;
+  return read_status_word(reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kCounterBytes - 4), clear, stream);
 }
 
 // ---- grouped launch: the experts of a mixture layer ------------------------------------
@@ -1144,7 +1173,6 @@ extern "C" int pe_gemv_grouped(const void* codes, int packed, int64_t ld_codes, 
   a.ws_cnt = static_cast<unsigned*>(workspace);
   a.ws_status = nullptr;  // per problem, set in the kernel
   a.ws_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kGroupedCounterZone);
-  a.prof = nullptr;
   a.x_rows = x_rows;
   a.grp = reinterpret_cast<const int4*>(problems);
   a.grp_codes_stride = codes_stride; a.grp_norms_stride = norms_stride;
@@ -1246,13 +1274,8 @@ static void* g_noalloc_ptr[64] = {nullptr};
 
 extern "C" size_t pe_gemv_noalloc_max_bytes(void) { return kNoAllocScratchBytes; }
 
-extern "C" int pe_gemv_noalloc(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
-                               const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype,
-                               int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch,
-                               int out_f, int in_f_padded, void* stream) {
-  const size_t need = pe_gemv_workspace_bytes(batch, out_f, in_f_padded);
-  if (need == 0) return batch > 16 || (in_f_padded % kBlock) ? PE_ERR_SHAPE : PE_ERR_ARG;
-  if (need > kNoAllocScratchBytes) return PE_ERR_LIMIT;  // shape needs more scratch than the built-in array holds
+// Device address of the array on the current device (looked up once per device).
+static int noalloc_scratch(void** out) {
   int dev = 0;
   PE_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PE_ERR_LIMIT;
@@ -1261,11 +1284,38 @@ extern "C" int pe_gemv_noalloc(const void* codes, int packed, int64_t ld_codes, 
     PE_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
     g_noalloc_ptr[dev] = ptr;
   }
-  void* ws = g_noalloc_ptr[dev];
+  *out = g_noalloc_ptr[dev];
+  return PE_OK;
+}
+
+extern "C" int pe_gemv_noalloc(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                               const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype,
+                               int64_t ld_x, int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch,
+                               int out_f, int in_f_padded, void* stream) {
+  const int c = gemv_check(codes, packed, ld_codes, norms, ld_norms, nullptr, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f,
+                           y, y_dtype, ld_y, batch, out_f, in_f_padded);
+  if (c != PE_OK) return c;
+  const size_t need = pe_gemv_workspace_bytes(batch, out_f, in_f_padded);
+  if (need == 0 || need > kNoAllocScratchBytes) return PE_ERR_LIMIT;  // shape needs more scratch than the built-in array holds
+  void* ws = nullptr;
+  const int r = noalloc_scratch(&ws);
+  if (r != PE_OK) return r;
+  if (batch <= 2) {  // kernels that own whole weight rows touch nothing of the array but its status word
+    const int rr = gemv_scratch_free(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f,
+                                     y, y_dtype, ld_y, bias, batch, out_f, in_f_padded, ws, stream);
+    if (rr <= 0) return rr;
+  }
   // The array keeps whatever the previous call left.  Only the tile counters have to
   // read zero on entry; clear the ones this shape uses, in stream order.
   const size_t counter_bytes = (size_t)((out_f + 15) / 16) * sizeof(unsigned);
   PE_CUDA_TRY(cudaMemsetAsync(ws, 0, counter_bytes, static_cast<cudaStream_t>(stream)));
-  return pe_gemv(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
-                 y_dtype, ld_y, bias, batch, out_f, in_f_padded, ws, kNoAllocScratchBytes, stream);
+  return gemv_tile_run(codes, packed, ld_codes, norms, ld_norms, nullptr, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
+                       y_dtype, ld_y, bias, batch, out_f, in_f_padded, ws, kNoAllocScratchBytes, stream);
+}
+
+extern "C" int pe_gemv_noalloc_status(int clear, void* stream) {
+  void* ws = nullptr;
+  const int r = noalloc_scratch(&ws);
+  if (r != PE_OK) return r;
+  return read_status_word(reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kCounterBytes - 4), clear, stream);
 }

@@ -47,42 +47,6 @@ struct RowArgs {
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-// fp16 pairs of one code word, in the order the staged activations have them.
-//  PACKED: the four bytes' pairs (ct[low nibble], ct[high nibble]) = weights (k, k+64)
-//  !PACKED: two pairs (ct[c0], ct[c1]), (ct[c2], ct[c3]) = consecutive weights
-template <bool PACKED, bool REGTAB>
-__device__ __forceinline__ void decode_word(uint32_t w, uint32_t lane_base, const RegTable& tb, uint32_t a[4]) {
-  if (PACKED && REGTAB) {
-    reg_decode(w, tb, a);
-  } else {
-    const uint32_t ad0 = lut_addr<0>(w, lane_base), ad1 = lut_addr<1>(w, lane_base), ad2 = lut_addr<2>(w, lane_base),
-                   ad3 = lut_addr<3>(w, lane_base);
-    const uint32_t v0 = lut_ld(ad0), v1 = lut_ld(ad1), v2 = lut_ld(ad2), v3 = lut_ld(ad3);
-    if (PACKED) {
-      a[0] = v0; a[1] = v1; a[2] = v2; a[3] = v3;
-    } else {
-      a[0] = lo_hi(v0, v1);
-      a[1] = lo_hi(v2, v3);
-    }
-  }
-}
-
 // dot product of one lane's 16 bytes of codes with its slice of one activation row
 template <bool PACKED, bool REGTAB>
 __device__ __forceinline__ float item_dot(const uint32_t a[4][4], uint32_t xp) {
@@ -361,30 +325,6 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 
 // ring slot of one item: SUB sub-items of 4 rows x 128 bytes, then 4 bytes of norms per row, rounded to whole 128-byte lines
 __host__ __device__ constexpr int col_stage_bytes(int sub) { return (sub * kItemBytes + sub * 16 + 127) & ~127; }
-
-// dot product of one lane's 16 bytes of codes with its activation registers
-template <bool PACKED, bool REGTAB, int NX>
-__device__ __forceinline__ float reg_dot(const uint4& q, uint32_t lane_base, const RegTable& tb, const uint32_t (&x)[NX]) {
-  uint32_t a[4][4];
-  decode_word<PACKED, REGTAB>(q.x, lane_base, tb, a[0]);
-  decode_word<PACKED, REGTAB>(q.y, lane_base, tb, a[1]);
-  decode_word<PACKED, REGTAB>(q.z, lane_base, tb, a[2]);
-  decode_word<PACKED, REGTAB>(q.w, lane_base, tb, a[3]);
-  uint32_t c0, c1, c2, c3;
-  if (PACKED) {
-    c0 = hmul2_u(a[0][0], x[0]); c1 = hmul2_u(a[1][0], x[4]); c2 = hmul2_u(a[2][0], x[8]); c3 = hmul2_u(a[3][0], x[12]);
-#pragma unroll
-    for (int i = 1; i < 4; ++i) {
-      c0 = hfma2_u(a[0][i], x[i], c0); c1 = hfma2_u(a[1][i], x[4 + i], c1);
-      c2 = hfma2_u(a[2][i], x[8 + i], c2); c3 = hfma2_u(a[3][i], x[12 + i], c3);
-    }
-  } else {
-    c0 = hmul2_u(a[0][0], x[0]); c1 = hmul2_u(a[1][0], x[2]); c2 = hmul2_u(a[2][0], x[4]); c3 = hmul2_u(a[3][0], x[6]);
-    c0 = hfma2_u(a[0][1], x[1], c0); c1 = hfma2_u(a[1][1], x[3], c1);
-    c2 = hfma2_u(a[2][1], x[5], c2); c3 = hfma2_u(a[3][1], x[7], c3);
-  }
-  return h2sum(hadd2_u(hadd2_u(c0, c1), hadd2_u(c2, c3)));
-}
 
 template <bool PACKED, bool REGTAB, int CPW, int DEPTH, int SUB>
 __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs p) {
@@ -692,7 +632,7 @@ static int launch_rows_depth(const RowArgs& a, int G, unsigned fixed, cudaStream
 int gemv_rows_try(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
                   const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f,
                   void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f, int in_f_padded,
-                  cudaStream_t stream) {
+                  int* status, cudaStream_t stream) {
   if (batch > 2 || !codes || !norms) return 1;
   const int K = in_f_padded, nb = K / kBlock;
   if (batch == 1) {

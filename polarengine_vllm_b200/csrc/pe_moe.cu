@@ -15,8 +15,8 @@ constexpr int kPlanMaxExperts = 1024;
 // the rows inside an expert depends on the arrival order of the atomics, which is harmless:
 // every row of a grouped problem is computed independently of its neighbours, and the
 // combine step finds a pair's row through `pos`.
-__global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const int64_t* ids, const int64_t* expert_map, int n_pairs, int top_k,
-                                                                int n_local, int rows_per_problem, int max_problems,
+__global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const int64_t* ids, const int64_t* expert_map, int n_global,
+                                                                int n_pairs, int top_k, int n_local, int rows_per_problem, int max_problems,
                                                                 int32_t* row_token, int32_t* pos, int4* problems,
                                                                 int32_t* expert_rows) {
   __shared__ int cnt[kPlanMaxExperts];     // pairs per expert, then a running cursor
@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const int64_t* i
   __syncthreads();
   for (int i = tid; i < n_pairs; i += kPlanThreads) {
     int64_t e = ids[i];
-    if (expert_map) e = e >= 0 ? expert_map[e] : -1;
+    if (expert_map) e = (e >= 0 && e < n_global) ? expert_map[e] : -1;  // ids outside the map belong to nobody
     if (e >= 0 && e < n_local) atomicAdd(&cnt[(int)e], 1);
   }
   __syncthreads();
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const int64_t* i
   __syncthreads();
   for (int i = tid; i < n_pairs; i += kPlanThreads) {
     int64_t e = ids[i];
-    if (expert_map) e = e >= 0 ? expert_map[e] : -1;
+    if (expert_map) e = (e >= 0 && e < n_global) ? expert_map[e] : -1;  // ids outside the map belong to nobody
     if (e >= 0 && e < n_local) {
       const int r = first[(int)e] + atomicAdd(&cnt[(int)e], 1);
       row_token[r] = i / top_k;
@@ -97,17 +97,19 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int64_
 
 using namespace pe;
 
-extern "C" int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, int n_pairs, int top_k, int n_local_experts,
+extern "C" int pe_moe_plan(const int64_t* topk_ids, const int64_t* expert_map, int n_global_experts, int n_pairs, int top_k,
+                           int n_local_experts,
                            int rows_per_problem, int max_problems, int32_t* row_token, int32_t* pos, int32_t* problems,
                            int32_t* expert_rows, void* stream) {
   if (!topk_ids || !row_token || !pos || !problems || n_pairs < 1 || top_k < 1 || max_problems < 1) return PE_ERR_ARG;
   if (rows_per_problem < 1 || rows_per_problem > 16) return PE_ERR_ARG;
+  if (expert_map && n_global_experts < 1) return PE_ERR_ARG;
   if (n_local_experts < 1 || n_local_experts > kPlanMaxExperts) return PE_ERR_LIMIT;
   if (reinterpret_cast<uintptr_t>(problems) & 15) return PE_ERR_ALIGN;
   // every possible routing must fit: at most min(experts, pairs) partial problems plus pairs / rows full ones
   const int worst = (n_local_experts < n_pairs ? n_local_experts : n_pairs) + n_pairs / rows_per_problem;
   if (max_problems < worst) return PE_ERR_WORKSPACE;
-  moe_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(topk_ids, expert_map, n_pairs, top_k, n_local_experts,
+  moe_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(topk_ids, expert_map, n_global_experts, n_pairs, top_k, n_local_experts,
                                                                              rows_per_problem, max_problems, row_token, pos,
                                                                              reinterpret_cast<int4*>(problems), expert_rows);
   PE_CUDA_TRY(cudaGetLastError());

@@ -27,7 +27,7 @@ import torch.nn.functional as F
 from .decode_ops import add_rmsnorm, decode_attention, rope_cache, silu_mul
 from .kernels import quant_embedding, quant_matmul, retile
 from .packing import pack_codes_half_block
-from .parallel import PeerExchange
+from .parallel import PeerExchange, shard_codes_for_tp, shard_norms_for_tp
 from .utils import get_centroids, get_ct_scaled
 
 
@@ -50,27 +50,52 @@ class DecoderConfig:
     rope_theta: float = 1e6
 
 
-class QWeight:
-    """Synthetic quantized (out_f, in_f) weight resident on one device."""
+def synth_weight(out_f: int, in_f: int, bits: int, dev, gen: torch.Generator):
+    """Synthetic quantizer output for a (out_f, in_f) weight: int8 codes (Lloyd-Max cells of N(0,1) draws) and
+    fp16 block norms ~ 0.02 * sqrt(128)."""
+    ct = get_centroids(bits).to(dev)
+    bounds = (ct[1:] + ct[:-1]) / 2
+    codes = torch.empty(out_f, in_f, dtype=torch.int8, device=dev)
+    step = max(1, (1 << 26) // in_f)
+    for r0 in range(0, out_f, step):  # bounded temporaries for vocabulary-sized tables
+        r1 = min(out_f, r0 + step)
+        codes[r0:r1] = torch.bucketize(torch.randn(r1 - r0, in_f, device=dev, generator=gen), bounds).to(torch.int8)
+    norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(out_f, in_f // 128, device=dev, generator=gen))).half()
+    return codes, norms
 
-    def __init__(self, out_f: int, in_f: int, bits: int, dev, gen: torch.Generator):
-        ct = get_centroids(bits).to(dev)
-        bounds = (ct[1:] + ct[:-1]) / 2
-        codes = torch.empty(out_f, in_f, dtype=torch.int8, device=dev)
-        step = max(1, (1 << 26) // in_f)
-        for r0 in range(0, out_f, step):  # bounded temporaries for vocabulary-sized tables
-            r1 = min(out_f, r0 + step)
-            codes[r0:r1] = torch.bucketize(torch.randn(r1 - r0, in_f, device=dev, generator=gen), bounds).to(torch.int8)
+
+class QWeight:
+    """Quantized (out_f, in_f) weight resident on one device, from int8 codes and fp16 norms."""
+
+    def __init__(self, codes: torch.Tensor, norms: torch.Tensor, bits: int):
         self.packed = bits <= 4
-        self.codes = pack_codes_half_block(codes) if self.packed else codes
-        self.norms = (0.02 * math.sqrt(128) * (1 + 0.05 * torch.randn(out_f, in_f // 128, device=dev, generator=gen))).half()
-        self.ct = get_ct_scaled(bits).to(dev)
-        self.tiles = retile(self.codes, self.packed, self.norms)  # streaming copy for decode-size batches
-        self.out_f, self.in_f = out_f, in_f
+        self.codes = pack_codes_half_block(codes) if self.packed else codes.contiguous()
+        self.norms = norms.contiguous()
+        self.ct = get_ct_scaled(bits).to(codes.device)
+        self.out_f, self.in_f = codes.shape
+        self.tiles = None  # streaming copy for batches of 3..16 rows, built the first time one arrives
+
+    @classmethod
+    def synthetic(cls, out_f: int, in_f: int, bits: int, dev, gen: torch.Generator) -> "QWeight":
+        return cls(*synth_weight(out_f, in_f, bits, dev, gen), bits)
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
+        if self.tiles is None and 3 <= x.shape[0] <= 16 and not torch.cuda.is_current_stream_capturing():
+            self.tiles = retile(self.codes, self.packed, self.norms)
         return quant_matmul(self.codes, self.packed, self.norms, self.ct, x, False, self.out_f, self.in_f, self.in_f, out_dtype,
                             tiles=self.tiles)
+
+
+def shard_fused_rows(codes, norms, sections, rank: int, world: int):
+    """Column-parallel shard of a fused projection: the rank's rows of every section (q | k | v, gate | up),
+    concatenated in section order -- the slicing vLLM's loader applies to fused ``qkv_proj`` / ``gate_up_proj``
+    shards (the reference's row helper is loader.py:558-598)."""
+    cs, ns, r0 = [], [], 0
+    for n in sections:
+        cs.append(shard_codes_for_tp(codes[r0:r0 + n], rank, world, 0))
+        ns.append(shard_norms_for_tp(norms[r0:r0 + n], rank, world, 0))
+        r0 += n
+    return torch.cat(cs, 0), torch.cat(ns, 0)
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -97,27 +122,49 @@ class QuantDecoder:
         self.inter = cfg.intermediate // tp_size
         d = cfg.head_dim
         self.layers: List[dict] = []
+        # Every rank draws the SAME full layer from the seed and keeps its shard (rows for the column-parallel
+        # projections, whole 128-blocks of K for the row-parallel ones), so a sharded model computes the same
+        # function as the un-sharded one and their outputs can be compared.
         for li in range(cfg.n_layers):
-            g = torch.Generator(device=dev).manual_seed(seed + 16 * li + 4099 * tp_rank)
+            g = torch.Generator(device=dev).manual_seed(seed + 16 * li)
+            nq, nkv = cfg.n_heads * d, cfg.n_kv_heads * d
+            c, n = synth_weight(nq + 2 * nkv, cfg.hidden, cfg.bits_qkv, dev, g)
+            qkv = QWeight(*shard_fused_rows(c, n, (nq, nkv, nkv), tp_rank, tp_size), cfg.bits_qkv)
+            c, n = synth_weight(cfg.hidden, nq, cfg.bits_o, dev, g)
+            o = QWeight(shard_codes_for_tp(c, tp_rank, tp_size, 1), shard_norms_for_tp(n, tp_rank, tp_size, 1), cfg.bits_o)
+            c, n = synth_weight(2 * cfg.intermediate, cfg.hidden, cfg.bits_gate_up, dev, g)
+            gate_up = QWeight(*shard_fused_rows(c, n, (cfg.intermediate, cfg.intermediate), tp_rank, tp_size), cfg.bits_gate_up)
+            c, n = synth_weight(cfg.hidden, cfg.intermediate, cfg.bits_down, dev, g)
+            down = QWeight(shard_codes_for_tp(c, tp_rank, tp_size, 1), shard_norms_for_tp(n, tp_rank, tp_size, 1), cfg.bits_down)
+            del c, n
             self.layers.append({
-                "qkv": QWeight((self.hq + 2 * self.hkv) * d, cfg.hidden, cfg.bits_qkv, dev, g),
-                "o": QWeight(cfg.hidden, self.hq * d, cfg.bits_o, dev, g),          # K slice of the row-parallel o
-                "gate_up": QWeight(2 * self.inter, cfg.hidden, cfg.bits_gate_up, dev, g),
-                "down": QWeight(cfg.hidden, self.inter, cfg.bits_down, dev, g),     # K slice of the row-parallel down
+                "qkv": qkv, "o": o, "gate_up": gate_up, "down": down,
                 "ln1": torch.ones(cfg.hidden, dtype=torch.float16, device=dev),
                 "ln2": torch.ones(cfg.hidden, dtype=torch.float16, device=dev),
             })
         ge = torch.Generator(device=dev).manual_seed(seed + 900)  # same table on every rank
-        self.embed = QWeight(cfg.vocab, cfg.hidden, cfg.bits_embed, dev, ge)
+        self.embed = QWeight.synthetic(cfg.vocab, cfg.hidden, cfg.bits_embed, dev, ge)
         assert cfg.vocab % tp_size == 0
-        gh = torch.Generator(device=dev).manual_seed(seed + 901 + 4099 * tp_rank)
-        self.head = QWeight(cfg.vocab // tp_size, cfg.hidden, cfg.bits_head, dev, gh)
+        gh = torch.Generator(device=dev).manual_seed(seed + 901)
+        c, n = synth_weight(cfg.vocab, cfg.hidden, cfg.bits_head, dev, gh)
+        self.head = QWeight(shard_codes_for_tp(c, tp_rank, tp_size, 0), shard_norms_for_tp(n, tp_rank, tp_size, 0), cfg.bits_head)
+        del c, n
         self.final_ln = torch.ones(cfg.hidden, dtype=torch.float16, device=dev)
-        self.max_len, self.batch = max_len, batch
+        self.max_len = max_len
+        self.fused_allreduce = fused_allreduce
+        self.xchg = None
+        self.alloc_cache(batch)
+
+    def alloc_cache(self, batch: int) -> None:
+        """(Re)allocate the KV cache and the exchange buffers for `batch` sequences (a collective call when the
+        fused row-parallel epilogue is on: every rank must make it)."""
+        cfg, dev, d = self.cfg, self.dev, self.cfg.head_dim
+        self.batch = batch
         # decode steps of a sharded model: all-reduce + residual add + norm as one launch over peer memory
-        self.xchg = PeerExchange(dev, tp_rank, tp_size, max(batch, 1), cfg.hidden, group) if fused_allreduce else None
-        self.k_cache = [torch.zeros(batch, self.hkv, max_len, d, dtype=torch.float16, device=dev) for _ in range(cfg.n_layers)]
-        self.v_cache = [torch.zeros(batch, self.hkv, max_len, d, dtype=torch.float16, device=dev) for _ in range(cfg.n_layers)]
+        if self.fused_allreduce and (self.xchg is None or self.xchg.max_rows < batch):
+            self.xchg = PeerExchange(dev, self.rank, self.tp, max(batch, 1), cfg.hidden, self.group)
+        self.k_cache = [torch.zeros(batch, self.hkv, self.max_len, d, dtype=torch.float16, device=dev) for _ in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros(batch, self.hkv, self.max_len, d, dtype=torch.float16, device=dev) for _ in range(cfg.n_layers)]
 
     # ---- collectives (the only exchanges on the path)
     def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
@@ -133,8 +180,9 @@ class QuantDecoder:
                 total += L[k].codes.numel() * L[k].codes.element_size() + L[k].norms.numel() * 2
         return total + self.head.codes.numel() + self.head.norms.numel() * 2
 
-    def forward(self, ids: torch.Tensor, pos0) -> torch.Tensor:
-        """ids (B, T) -> next-token ids (B,).  ``pos0`` is an int (prefill) or a 0-d device
+    def forward(self, ids: torch.Tensor, pos0, return_logits: bool = False) -> torch.Tensor:
+        """ids (B, T) -> next-token ids (B,), or the fp32 logits (B, vocab) of the last position (gathered over
+        the ranks) when ``return_logits`` is set.  ``pos0`` is an int (prefill) or a 0-d device
         tensor (decode under a CUDA graph); the KV cache is written at pos0..pos0+T-1."""
         cfg, d = self.cfg, self.cfg.head_dim
         b, t = ids.shape
@@ -164,6 +212,12 @@ class QuantDecoder:
             delta = L["down"](act, torch.float32)
         h = reduce_add_norm(delta, self.final_ln).view(b, t, cfg.hidden)[:, -1]
         logits = self.head(h, torch.float32)                      # (B, vocab / tp)
+        if return_logits:
+            if self.tp == 1:
+                return logits
+            parts = [torch.empty_like(logits) for _ in range(self.tp)]
+            dist.all_gather(parts, logits.contiguous(), group=self.group)
+            return torch.cat(parts, dim=-1)
         val, idx = logits.max(dim=-1)
         if self.tp > 1:
             vals = [torch.empty_like(val) for _ in range(self.tp)]

@@ -22,7 +22,6 @@ from typing import Any, Dict, List, Optional
 
 import torch
 
-from .fwht import FWHTCache
 from .kernels import pack_codes_int4, quant_matmul, retile
 from .utils import get_ct_scaled
 
@@ -45,8 +44,10 @@ class PolarQuantLinearMethod(_Base):
         self.block_size = block_size
         self.bits = bits
         self.layer_meta = layer_meta or {}
+        # The tiled copy of a layer (codes and norms interleaved per 16-row x 128-column tile) serves batches of
+        # 3..16 rows only; it is built the first time such a batch arrives, so a layer that only ever sees one
+        # token at a time, or prefill, keeps a single copy of its codes in HBM.
         self.decode_tiled = True
-        self._fwht_cache = FWHTCache()
 
     # ------------------------------------------------------------------ weights
     def create_weights(self, layer: torch.nn.Module, input_size_per_partition: int,
@@ -88,11 +89,7 @@ class PolarQuantLinearMethod(_Base):
             layer.codes_packed = packed
             layer.in_f_half = layer.n_blocks * (layer.block_size // 2)
             layer.packed = True
-        if self.decode_tiled:
-            # second copy of the layer in the decode kernel's streaming layout (codes + norms
-            # interleaved per 16-row x 128-column tile); the row-major copy feeds the prefill kernel
-            w = layer.codes_packed if layer.packed else layer.codes
-            layer.codes_tiled = retile(w.data, layer.packed, layer.norms.data)
+        layer.codes_tiled = None
 
     # ------------------------------------------------------------------ forward
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -100,6 +97,9 @@ class PolarQuantLinearMethod(_Base):
         x2 = x.reshape(-1, layer.in_f)
         packed = bool(getattr(layer, "packed", False))
         w = layer.codes_packed if packed else layer.codes
+        if (self.decode_tiled and 3 <= x2.shape[0] <= 16 and getattr(layer, "codes_tiled", None) is None
+                and not torch.cuda.is_current_stream_capturing()):
+            layer.codes_tiled = retile(w.data, packed, layer.norms.data)
         # one native entry for every batch size: <= 16 rows run the fused decode kernel,
         # more rows the tensor-core kernel (rotation is done by its preparation launch)
         y = quant_matmul(w, packed, layer.norms, layer.ct_scaled, x2, False, layer.out_f, layer.in_f,
@@ -108,7 +108,9 @@ class PolarQuantLinearMethod(_Base):
 
 
 def create_fwht_clear_hook(linear_method: PolarQuantLinearMethod):
-    """Forward pre-hook that empties the method's rotation memo (linear_method.py:265-288)."""
+    """The reference installs this forward pre-hook to empty the method's memo of rotated activations
+    (linear_method.py:265-288).  Here the rotation happens inside the matmul launch and nothing is memoised,
+    so the hook has nothing to clear; it exists so that code written against the reference keeps working."""
     def hook(module: torch.nn.Module, args: Any) -> None:
-        linear_method._fwht_cache.clear()
+        return None
     return hook

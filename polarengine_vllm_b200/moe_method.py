@@ -189,7 +189,8 @@ class PolarQuantMoEMethod:
         desc = torch.empty(max_problems, 4, dtype=torch.int32, device=dev)
         expert_rows = torch.empty(n_local, 2, dtype=torch.int32, device=dev)  # (first grouped row, rows) per expert
         st = nv.stream_ptr(dev)
-        nv.check(l.pe_moe_plan(ids.data_ptr(), emap.data_ptr() if emap is not None else None, pairs, k, n_local, rpp,
+        nv.check(l.pe_moe_plan(ids.data_ptr(), emap.data_ptr() if emap is not None else None,
+                               int(emap.numel()) if emap is not None else 0, pairs, k, n_local, rpp,
                                max_problems, tok_sorted.data_ptr(), pos.data_ptr(), desc.data_ptr(), expert_rows.data_ptr(), st),
                  "pe_moe_plan")
         # many rows per expert: the tensor-core kernel over all experts (tile list built on the device);
@@ -234,8 +235,10 @@ class PolarQuantMoEMethod:
         x2 = x.reshape(-1, h)
         t, k = topk_ids.shape
         ids = topk_ids.reshape(-1)
-        if expert_map is not None:
-            ids = expert_map.to(ids.device)[ids.long()]
+        if expert_map is not None:  # ids outside the map belong to nobody (same rule as pe_moe_plan)
+            em = expert_map.to(ids.device)
+            inside = (ids >= 0) & (ids < em.numel())
+            ids = torch.where(inside, em[ids.long().clamp(0, em.numel() - 1)], torch.full_like(ids, -1))
         order = torch.argsort(ids, stable=True)
         sorted_ids = ids[order]
         n_local = layer.w13_codes.shape[0]

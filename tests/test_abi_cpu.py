@@ -81,6 +81,6 @@ def test_size_queries_of_the_grouped_and_exchange_entry_points():
     assert lib.pe_decode_attention_workspace_bytes(1, 32, 8, 64) == 0
     assert lib.pe_gemv_noalloc_max_bytes() == 8 << 20
     # NULL pointers are refused before anything touches a device
-    assert lib.pe_moe_plan(None, None, 8, 2, 4, 8, 8, None, None, None, None, None) == -1
+    assert lib.pe_moe_plan(None, None, 0, 8, 2, 4, 8, 8, None, None, None, None, None) == -1
     assert lib.pe_add_rmsnorm(None, None, 1, None, None, 1, 4096, 1e-6, None) == -1
     assert lib.pe_allreduce_add_rmsnorm(None, None, None, None, 1, 4096, 1e-6, None, 0, 1, 1, None, None, None) == -1

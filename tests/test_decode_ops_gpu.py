@@ -104,3 +104,48 @@ def test_exchange_with_one_rank_equals_add_rmsnorm(rows, hidden):
         assert torch.equal(x, x_ref) and torch.equal(out, ref)
     assert not xchg.timed_out()
     assert int(xchg.seq[0]) == 5
+
+
+def test_exchange_wait_runs_out_and_reports():
+    """A peer that never arrives costs a bounded time and a status word, not a hung GPU: a world of two whose
+    peer table points at two LOCAL buffers, with only rank 0 ever launched.  Rank 0 pushes its partial into
+    both buffers, waits for rank 1's flag (nothing sets it), gives up after the limit (10 ms here), records
+    status 1 and finishes with what it has (its own partial; rank 1's slot reads zero).  The next call on a
+    healthy exchange works."""
+    from polarengine_vllm_b200 import _native as nv
+    from polarengine_vllm_b200.decode_ops import add_rmsnorm
+    from polarengine_vllm_b200.parallel import PeerExchange
+    dev = torch.device("cuda")
+    lib = nv.lib()
+    rows, hidden, max_rows = 2, 4096, 4
+    g = torch.Generator(device="cuda").manual_seed(3)
+    nbytes = lib.pe_allreduce_buffer_bytes(2, max_rows, hidden)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    peers = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+    seq = torch.zeros(max_rows, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    w = (1 + 0.1 * torch.randn(hidden, device=dev, generator=g)).half()
+    x = torch.randn(rows, hidden, device=dev, generator=g).half()
+    x_ref = x.clone()
+    part = torch.randn(rows, hidden, device=dev, generator=g)
+    out = torch.empty_like(x)
+    assert lib.pe_set_wait_limit_us(10_000) == 0
+    try:
+        torch.cuda.synchronize()
+        import time
+        t0 = time.perf_counter()
+        nv.check(lib.pe_allreduce_add_rmsnorm(part.data_ptr(), x.data_ptr(), w.data_ptr(), out.data_ptr(), rows, hidden, 1e-6,
+                                              peers.data_ptr(), 0, 2, max_rows, seq.data_ptr(), status.data_ptr(),
+                                              nv.stream_ptr(dev)), "pe_allreduce_add_rmsnorm")
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 1.0           # the limit, not the default second
+    finally:
+        assert lib.pe_set_wait_limit_us(1_000_000) == 0
+    assert int(status.item()) == 1                      # the wait ran out and said so
+    ref = add_rmsnorm(x_ref, part, w, 1e-6)             # rank 1 contributed zeros
+    assert torch.equal(x, x_ref) and torch.equal(out, ref)
+    # the context is intact: a healthy exchange runs right after
+    xchg = PeerExchange(dev, 0, 1, 4, hidden)
+    out2 = xchg.allreduce_add_rmsnorm(part, x, w, 1e-6)
+    assert torch.equal(out2, add_rmsnorm(x_ref, part, w, 1e-6)) and not xchg.timed_out()
+    assert lib.pe_set_wait_limit_us(0) == -1

@@ -40,6 +40,27 @@ def test_gemm_matches_oracle(m, n, k, bits):
     assert cos > 0.9999
 
 
+@pytest.mark.parametrize("bits,n,k", [(4, 4096, 4096), (4, 12288, 4096), (4, 4096, 12288), (5, 4096, 4096), (6, 4096, 4096),
+                                      (3, 12288, 4096)])
+def test_gemm_prefill_sweep_shapes_m4096(bits, n, k):
+    """The prefill sweep's largest case: 4096 bf16 tokens into the decoder-layer shapes (the reference's own
+    self-test list is polar_gemm.py:541-615).  The kernel runs all 4096 tokens; the CPU oracle is evaluated
+    on every 16th token (all output columns), which covers every token tile and every weight tile."""
+    m = 4096
+    codes, norms, cts = rand_layer(n, k, bits, seed=n + k + bits)
+    x = rand_x(m, k, seed=12, dtype=torch.bfloat16)
+    y = run_gemm(codes, norms, cts, x, bits)
+    assert y.shape == (m, n) and torch.isfinite(y.float()).all()
+    rows = torch.arange(5, m, 16)
+    ref = oracle.linear_dequant(x[rows], codes, norms, cts)
+    assert max_rel(y[rows.cuda()], ref) <= TOL
+    cos, _ = ref_metrics(y[rows.cuda()], ref)
+    assert cos > 0.9999
+    # the first and the last token tile in full
+    edge = torch.cat([torch.arange(0, 64), torch.arange(m - 64, m)])
+    assert max_rel(y[edge.cuda()], oracle.linear_dequant(x[edge], codes, norms, cts)) <= TOL
+
+
 def test_gemm_ragged_in_features_bias_and_dtypes():
     n, k, in_f, bits, m = 512, 1920, 1856, 4, 200
     codes, norms, cts = rand_layer(n, k, bits, seed=9)

@@ -68,3 +68,45 @@ def test_moe_expert_parallel_partition_sums_to_full():
             setattr(sub, name, getattr(layer, name))
         parts += method.moe_forward(sub, x, w.cuda(), ids.cuda(), expert_map=emap.cuda()).float()
     assert max_rel(parts, full) <= 2e-3
+
+
+def build_random_codes(e, h, i, seed=0):
+    """Experts with uniformly random codes and |randn| norms (helpers.rand_layer): no quantizer run, so the
+    128-expert layer of the benchmark configuration builds in seconds."""
+    from helpers import rand_layer
+    from polarengine_vllm_b200.moe_method import PolarQuantMoEMethod
+    method = PolarQuantMoEMethod(3, 4)
+    layer = torch.nn.Module()
+    method.create_weights(layer, e, h, i, torch.float16)
+    layer = layer.cuda()
+    hp, ip = -(-h // 128) * 128, -(-i // 128) * 128
+    experts = []
+    for ex in range(e):
+        q = {}
+        for name, (n, kp, k), bits in (("gate", (i, hp, h), 3), ("up", (i, hp, h), 3), ("down", (h, ip, i), 4)):
+            codes, norms, cts = rand_layer(n, kp, bits, seed=seed + 3 * ex + len(q))
+            q[name] = {"codes": codes, "norms": norms, "ct_scaled": cts}
+        method.load_expert(layer, ex, q["gate"], q["up"], q["down"])
+        experts.append({n: (q[n]["codes"], q[n]["norms"], q[n]["ct_scaled"], None) for n in q})
+    method.process_weights_after_loading(layer)
+    return method, layer, experts
+
+
+@pytest.mark.parametrize("tokens", [1, 64, 2048])
+def test_moe_benchmark_configuration(tokens):
+    """128 experts, top-8, hidden 2688, intermediate 1856 (down-projection K pads to 1920): the shapes of the
+    expert-layer benchmark.  64 tokens run the decode-size grouped launches (pe_gemv_grouped), 2048 the
+    grouped tensor-core launches (pe_gemm_grouped, about 2000 device-built tiles).  The GPU computes every
+    token; the CPU oracle (routing, silu(gate)*up, down, weighted sum: nemotron_offload.py:180-226) is
+    evaluated on a sample of them."""
+    e, h, i, top_k = 128, 2688, 1856, 8
+    method, layer, experts = build_random_codes(e, h, i, seed=500)
+    g = torch.Generator().manual_seed(tokens)
+    x = torch.randn(tokens, h, generator=g).half()
+    gate_w = (torch.randn(e, h, generator=g) * 0.02).half()
+    w, ids = oracle.moe_route(x, gate_w, top_k)
+    y = method.apply(layer, x.cuda(), w.cuda(), ids.cuda())
+    assert y.shape == (tokens, h) and y.dtype == torch.float16 and torch.isfinite(y.float()).all()
+    sample = torch.arange(tokens) if tokens <= 64 else torch.randperm(tokens, generator=g)[:24].sort().values
+    ref = oracle.moe_forward(x[sample], w[sample], ids[sample], experts)
+    assert max_rel(y[sample.cuda()], ref) <= 1e-2
