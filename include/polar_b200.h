@@ -38,6 +38,13 @@ enum {
                        pads and rotates while staging (linear_method.py:186-197) */
 };
 
+/* glue ops that pe_gemv_pro computes while it stages its input */
+enum {
+  PE_PRO_NONE = 0,
+  PE_PRO_ADD_RMSNORM = 1, /* input = RMSNorm(x + delta) * norm_weight; the updated residual goes to resid_out */
+  PE_PRO_SILU_MUL = 2     /* x = [gate | up] (2 * in_f fp16): input = silu(gate) * up                      */
+};
+
 /* error codes */
 enum {
   PE_OK = 0,
@@ -108,7 +115,11 @@ int pe_embedding(const void* codes, int packed, int64_t ld_codes, const void* no
  *   out (batch, hq * head_dim) = softmax(q K^T / sqrt(head_dim)) V per query head, query head
  *   i reading kv head i / (hq / hkv).  head_dim = 128, hq / hkv in {1, 2, 4, 8}.  With a
  *   workspace (pe_decode_attention_workspace_bytes; its first 4 KB zero before the first call,
- *   left zero) the cache positions are split over up to 8 CTAs per kv head; NULL = one CTA. */
+ *   left zero) the cache positions are split over up to 16 CTAs per kv head; NULL = one CTA.
+ * pe_rope_attention: pe_rope_cache (t = 1) and pe_decode_attention as ONE launch: qkv (batch,
+ *   (hq + 2 hkv) * head_dim) holds the raw fused projection of the new token; queries and the new
+ *   key are rotated in registers, key and value are written into the caches at the position, and
+ *   the attention uses them without reading them back.  Same output as the two calls. */
 int pe_add_rmsnorm(void* x, const void* delta, int delta_dtype, const void* weight, void* out, int rows, int hidden,
                    float eps, void* stream);
 int pe_rope_cache(const void* qkv, int64_t ld_qkv, const int64_t* pos_dev, int64_t pos_host, void* q_out, void* k_cache,
@@ -118,6 +129,9 @@ size_t pe_decode_attention_workspace_bytes(int batch, int hq, int hkv, int head_
 int pe_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos_dev, int64_t pos_host,
                         void* out, int batch, int hq, int hkv, int head_dim, int max_len, void* workspace,
                         size_t workspace_bytes, void* stream);
+int pe_rope_attention(const void* qkv, int64_t ld_qkv, const int64_t* pos_dev, int64_t pos_host, void* k_cache, void* v_cache,
+                      void* out, int batch, int hq, int hkv, int head_dim, int max_len, float theta, void* workspace,
+                      size_t workspace_bytes, void* stream);
 
 /* ---- nibble packing ---------------------------------------------------------
  * int8 codes (out_f, in_f_padded) -> uint8 (out_f, in_f_padded/2), byte i of each
@@ -270,6 +284,23 @@ int pe_gemm(const void* codes, int packed, int64_t ld_codes, const void* norms, 
             const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int m, int out_f,
             int in_f_padded, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- one-token matmul with the preceding glue op folded in ---------------------------
+ * y (1, out_f) = pe_gemv of one fp16 activation row that is computed on the fly:
+ *   PE_PRO_ADD_RMSNORM  r = half(x + half(delta)) over in_f elements (delta fp16 / fp32, may be NULL);
+ *                       input = half(r * rsqrt(mean(r^2) + eps)) * norm_weight (the rounding steps of
+ *                       pe_add_rmsnorm); r is also stored to resid_out (fp16, may be NULL, must not be x)
+ *   PE_PRO_SILU_MUL     x = [gate | up], 2 * in_f fp16; input = half(silu(gate)) * up (pe_silu_mul)
+ * so that the residual-add + norm in front of q/k/v and gate/up, and the activation in front of down,
+ * cost no launch of their own at decode time.  in_f a multiple of 4 (8 for PE_PRO_SILU_MUL), all
+ * pointers 16-byte aligned.  Layers the batch-1 kernel does not take (few rows, rows that are not a
+ * multiple of 128 bytes, more than 64 chunks) return PE_ERR_SHAPE: run the glue op and pe_gemv then.
+ * The reference leaves these ops to the serving framework (linear_method.py:157-222 receives the
+ * already normalised activations); no counterpart there. */
+int pe_gemv_pro(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                const float* ct_scaled, int n_levels, int prologue, const void* x, int in_f, const void* delta,
+                int delta_dtype, const void* norm_weight, void* resid_out, float eps, void* y, int y_dtype,
+                const void* bias, int out_f, int in_f_padded, void* stream);
 
 /* ---- decode-size matmul without caller scratch ----------------------------------
  * Same computation and arguments as pe_gemv, minus workspace / workspace_bytes.  It has

@@ -17,6 +17,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 PE_F32, PE_F16, PE_BF16 = 0, 1, 2
 PE_X_ROTATED, PE_X_RAW = 0, 1
+PE_PRO_ADD_RMSNORM, PE_PRO_SILU_MUL = 1, 2
 
 _DTYPE = {torch.float32: PE_F32, torch.float16: PE_F16, torch.bfloat16: PE_BF16}
 
@@ -55,8 +56,10 @@ SIGNATURES = {
     "pe_silu_mul": (_i, [_vp, _i64, _vp, _i64, _i, _i, _vp]),
     "pe_decode_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pe_decode_attention": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "pe_gemv_pro": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, ctypes.c_float, _vp, _i, _vp, _i, _i, _vp]),
     "pe_gemv_status": (_i, [_vp, _sz, _i, _vp]),
     "pe_gemv_noalloc_status": (_i, [_i, _vp]),
+    "pe_rope_attention": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp, _sz, _vp]),
     "pe_gemv_noalloc_max_bytes": (_sz, []),
     "pe_gemv_noalloc": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                              _vp]),

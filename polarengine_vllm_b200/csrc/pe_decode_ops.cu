@@ -150,26 +150,258 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* gu, int64_t
 }
 
 
-// Single-query attention over the KV cache for one decode step (grouped-query form).
-// CTA (kv head, sequence, split): the G = hq / hkv query heads of a kv head share every K
-// and V row; the cache positions 0 .. L-1 are cut into `splits` equal ranges so that a
-// batch-1 step still fills many SMs.
-//  1. scores: thread = cache position (strided); the 16 16-byte pieces of its K row are
-//     requested together (one memory round trip per position), then the full 128-wide dot
-//     per query head with the queries broadcast from shared memory;
-//  2. per query head one warp: maximum, exponentials, their sum;
-//  3. weighted V rows: thread = (position stride 16, 16-byte piece of the row), eight rows
-//     in flight per thread; the 16 position groups meet in shared memory;
-//  4. one split: normalise and store.  Several: every CTA leaves (max, sum, weighted rows)
-//     in scratch and takes a ticket; the CTA that draws the last ticket merges the splits
-//     in split order (bit-reproducible) and returns the ticket counter to zero.  Nobody
-//     waits for anybody.
+// Single-query attention over the KV cache for one decode step (grouped-query form), optionally with the
+// rotary embedding and the KV-cache write of the new token folded in.
+// CTA (kv head, sequence, split): the G = hq / hkv query heads of a kv head share every K and V row; the
+// cache positions 0 .. L-1 are cut into `splits` equal ranges so that a one-sequence step still fills the SMs.
+//  * A warp owns the positions p_lo + w, p_lo + w + 8, ... of the CTA's range.  Lane l holds elements
+//    4l .. 4l+3 of a row: a K or V row is one coalesced 256-byte load per warp, the queries sit in registers.
+//    Per position: G dot products (five shuffles each), an online-softmax update of (max, sum, weighted V
+//    rows) per head; the rows of six positions are requested together.
+//  * The 8 warps meet in shared memory, rescaled to the CTA's maximum.  One split: normalise and store.
+//    Several: every CTA leaves (weighted rows, max, sum) in scratch and takes a ticket; the CTA that draws
+//    the last ticket merges the splits in split order (bit-reproducible) and returns the ticket counter to
+//    zero.  Nobody waits for anybody.
+//  * Fused form (qkv != null): q, k, v are the raw rows of the fused q/k/v projection.  Every warp rotates
+//    the G queries for itself (rotate-half pairs (j, j + 64) live in lanes l and l + 16); the CTA whose range
+//    holds the current position rotates the new key, writes key and value into the caches and uses its
+//    registers for that position instead of reading the row back.
 constexpr int kAttThreads = 256;
+constexpr int kAttWarps = kAttThreads / 32;
 constexpr int kAttMaxGroup = 8;
-constexpr int kAttMaxSplits = 8;
+constexpr int kAttMaxSplits = 16;
+constexpr int kAttInFlight = 6;  // positions whose K and V rows a warp requests together
+
+struct AttArgs {
+  const __half* q;      // (batch, hq, D) rotated queries, or null in the fused form
+  const __half* qkv; int64_t ld_qkv;  // fused form: rows of (hq + 2 hkv) * D raw projection outputs
+  __half* k_cache; __half* v_cache;   // (batch, hkv, max_len, D); written at the current position in the fused form
+  const int64_t* pos_dev; int64_t pos_host;
+  __half* out;          // (batch, hq * D)
+  int hq, hkv, max_len;
+  float scale, theta;
+  float* parts; unsigned* tickets;
+};
+
+__device__ __forceinline__ void half4_to_float(const uint2& u, float f[4]) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+// rotate-half rotary embedding of the 4 elements a lane holds (elements 4l..4l+3; the pair partner is 64 away,
+// in lane l ^ 16), rounded to fp16 as pe_rope_cache stores them
+__device__ __forceinline__ void rope4(float x[4], const float c[4], const float s[4], int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float o = __shfl_xor_sync(0xffffffffu, x[i], 16);
+    const float r = lane < 16 ? x[i] * c[i] - o * s[i] : x[i] * c[i] + o * s[i];
+    x[i] = __half2float(__float2half_rn(r));
+  }
+}
 
 template <int D, int G>
-__device__ __forceinline__ void attention_body(const __half* q, const __half* kb, const __half* vb, __half* out_row, float* att_smem,
+__device__ __forceinline__ void attention_body(const AttArgs& p, float* att_smem) {
+  static_assert(D == 128, "a row is 32 lanes x 4 elements");
+  __shared__ unsigned my_ticket;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, splits = gridDim.z;
+  const int64_t pos = p.pos_dev ? *p.pos_dev : p.pos_host;
+  const int64_t len64 = pos + 1;  // the current token counts
+  const int L = (int)(len64 < 1 ? 1 : (len64 > p.max_len ? p.max_len : len64));
+  const int chunk = (L + splits - 1) / splits;
+  const int p_lo = sp * chunk, p_hi = p_lo + chunk < L ? p_lo + chunk : L;
+  __half* kb = p.k_cache + ((int64_t)b * p.hkv + kvh) * (int64_t)p.max_len * D;
+  __half* vb = p.v_cache + ((int64_t)b * p.hkv + kvh) * (int64_t)p.max_len * D;
+  const bool fused = p.qkv != nullptr;
+  const int cur = fused && pos >= 0 && pos < p.max_len ? (int)pos : -1;  // position whose K/V rows come from qkv
+
+  // ---- queries (and, fused, the new key / value) in registers
+  float q[G][4], knew[4] = {0.f, 0.f, 0.f, 0.f}, vnew[4] = {0.f, 0.f, 0.f, 0.f};
+  if (fused) {
+    __shared__ float rope_c[D / 2], rope_s[D / 2];  // computed once per CTA: large angles take the slow path of cosf / sinf
+    if (tid < D / 2) {
+      const float inv = 1.f / powf(p.theta, (float)(2 * tid) / (float)D);
+      const float ang = (float)pos * inv;
+      rope_c[tid] = cosf(ang);
+      rope_s[tid] = sinf(ang);
+    }
+    __syncthreads();
+    float c[4], s[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      c[i] = rope_c[(lane & 15) * 4 + i];
+      s[i] = rope_s[(lane & 15) * 4 + i];
+    }
+    const __half* row = p.qkv + (int64_t)b * p.ld_qkv;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      half4_to_float(*reinterpret_cast<const uint2*>(row + ((int64_t)kvh * G + g) * D + lane * 4), q[g]);
+      rope4(q[g], c, s, lane);
+    }
+    half4_to_float(*reinterpret_cast<const uint2*>(row + ((int64_t)p.hq + kvh) * D + lane * 4), knew);
+    rope4(knew, c, s, lane);
+    const uint2 vraw = *reinterpret_cast<const uint2*>(row + ((int64_t)p.hq + p.hkv + kvh) * D + lane * 4);
+    half4_to_float(vraw, vnew);
+    if (w == 0 && cur >= p_lo && cur < p_hi) {  // this CTA owns the current position: one warp fills the caches
+      *reinterpret_cast<uint2*>(kb + (int64_t)cur * D + lane * 4) = make_uint2(pack_half2(knew[0], knew[1]), pack_half2(knew[2], knew[3]));
+      *reinterpret_cast<uint2*>(vb + (int64_t)cur * D + lane * 4) = vraw;
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+      half4_to_float(*reinterpret_cast<const uint2*>(p.q + ((int64_t)b * p.hq + (int64_t)kvh * G + g) * D + lane * 4), q[g]);
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[g][i] *= p.scale;
+
+  // ---- this warp's positions, online softmax
+  float m[G], l[G], acc[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
+  // Rows of kAttInFlight positions are requested together, before any of them is used: a warp's share of a
+  // 640-token cache (at most 5 positions with 16 ranges) costs one memory round trip, not one per position.
+  constexpr int U = kAttInFlight;
+  for (int p0 = p_lo + w; p0 < p_hi; p0 += kAttWarps * U) {
+    uint2 kr[U], vr[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int pp = p0 + u * kAttWarps;
+      kr[u] = vr[u] = make_uint2(0, 0);
+      if (pp < p_hi && pp != cur) {
+        kr[u] = *reinterpret_cast<const uint2*>(kb + (int64_t)pp * D + lane * 4);
+        vr[u] = *reinterpret_cast<const uint2*>(vb + (int64_t)pp * D + lane * 4);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int pp = p0 + u * kAttWarps;
+      if (pp < p_hi) {  // warp-uniform
+        float kf[4], vf[4];
+        if (pp == cur) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { kf[i] = knew[i]; vf[i] = vnew[i]; }
+        } else {
+          half4_to_float(kr[u], kf);
+          half4_to_float(vr[u], vf);
+        }
+        float sc[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) sc[g] = q[g][0] * kf[0] + q[g][1] * kf[1] + q[g][2] * kf[2] + q[g][3] * kf[3];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) sc[g] += __shfl_xor_sync(0xffffffffu, sc[g], o);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float mn = fmaxf(m[g], sc[g]);
+          const float corr = __expf(m[g] - mn), e = __expf(sc[g] - mn);
+          m[g] = mn;
+          l[g] = l[g] * corr + e;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[g][i] = acc[g][i] * corr + e * vf[i];
+        }
+      }
+    }
+  }
+
+  // ---- the warps meet: [warp][G][D] weighted rows, [warp][G] maxima and sums
+  float* racc = att_smem;                            // kAttWarps * G * D
+  float* rm = racc + kAttWarps * G * D;              // kAttWarps * G
+  float* rl = rm + kAttWarps * kAttMaxGroup;         // kAttWarps * G
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    *reinterpret_cast<float4*>(racc + (w * G + g) * D + lane * 4) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    if (lane == 0) { rm[w * kAttMaxGroup + g] = m[g]; rl[w * kAttMaxGroup + g] = l[g]; }
+  }
+  __syncthreads();
+  __half* op = p.out + ((int64_t)b * p.hq + (int64_t)kvh * G) * D;
+  const size_t head = (size_t)b * p.hkv + kvh;
+  float* part = p.parts ? p.parts + (head * splits + sp) * G * (D + 2) : nullptr;
+  for (int i = tid; i < G * D; i += kAttThreads) {
+    const int g = i / D, d = i % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int ww = 0; ww < kAttWarps; ++ww) mx = fmaxf(mx, rm[ww * kAttMaxGroup + g]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < kAttWarps; ++ww) {
+      const float lw = rl[ww * kAttMaxGroup + g];
+      if (lw > 0.f) {  // a warp without positions has no maximum
+        const float f = __expf(rm[ww * kAttMaxGroup + g] - mx);
+        num += racc[(ww * G + g) * D + d] * f;
+        den += lw * f;
+      }
+    }
+    if (splits == 1) {
+      op[i] = __float2half_rn(num / den);
+    } else {  // this split's record: [G][D + 2] = weighted rows, maximum, sum
+      part[g * (D + 2) + d] = num;
+      if (d == 0) { part[g * (D + 2) + D] = mx; part[g * (D + 2) + D + 1] = den; }
+    }
+  }
+  if (splits == 1) return;
+  unsigned* ticket = p.tickets + head;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) my_ticket = atomicAdd(ticket, 1u);
+  __syncthreads();
+  if (my_ticket != (unsigned)(splits - 1)) return;
+  __threadfence();
+  const float* all = part - (size_t)sp * G * (D + 2);  // record of split 0
+  for (int i = tid; i < G * D; i += kAttThreads) {
+    const int g = i / D, d = i % D;
+    // all three values of every split are requested before any is used: one memory round trip, not one per split
+    float mv[kAttMaxSplits], lv[kAttMaxSplits], nv[kAttMaxSplits];
+#pragma unroll
+    for (int s2 = 0; s2 < kAttMaxSplits; ++s2) {
+      const float* rec = all + ((size_t)(s2 < splits ? s2 : 0) * G + g) * (D + 2);
+      mv[s2] = __ldcg(rec + D);
+      lv[s2] = s2 < splits ? __ldcg(rec + D + 1) : 0.f;
+      nv[s2] = __ldcg(rec + d);
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s2 = 0; s2 < kAttMaxSplits; ++s2) mx = fmaxf(mx, lv[s2] > 0.f ? mv[s2] : -INFINITY);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < kAttMaxSplits; ++s2) {
+      const float f = lv[s2] > 0.f ? __expf(mv[s2] - mx) : 0.f;  // an empty split has no maximum
+      num += (lv[s2] > 0.f ? nv[s2] : 0.f) * f;
+      den += lv[s2] * f;
+    }
+    op[i] = __float2half_rn(num / den);
+  }
+  if (tid == 0) *ticket = 0u;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(const AttArgs p) {
+  extern __shared__ __align__(16) float att_smem[];
+  pdl_enter();
+  switch (p.hq / p.hkv) {
+    case 1: attention_body<D, 1>(p, att_smem); break;
+    case 2: attention_body<D, 2>(p, att_smem); break;
+    case 4: attention_body<D, 4>(p, att_smem); break;
+    case 8: attention_body<D, 8>(p, att_smem); break;
+    default: break;
+  }
+}
+
+// ---- many sequences: thread per cache position -------------------------------------------------------
+// With dozens of (sequence, kv head) pairs the launch fills the SMs without cutting the cache finely, and the
+// warp-per-position form above pays five shuffles per dot product for nothing.  Here a thread owns a cache
+// position for the scores (the 16 16-byte pieces of its K row requested together, the full 128-wide dot per
+// query head with the queries broadcast from shared memory), one warp per query head does the softmax, and
+// the V rows are summed with thread = (position stride 16, 16-byte piece), eight rows in flight per thread.
+// Same split / ticket / merge scheme and the same scratch layout.
+constexpr int kAttWideThreads = 256;
+constexpr int kAttWideMaxSplits = 8;
+
+template <int D, int G>
+__device__ __forceinline__ void attention_wide_body(const __half* q, const __half* kb, const __half* vb, __half* out_row, float* att_smem,
                                                int p_lo, int p_hi, int chunk_cap, float scale, int splits, float* part,
                                                unsigned* ticket) {
   static_assert(D == 128, "pieces and thread mapping are laid out for 128-wide heads");
@@ -180,9 +412,9 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
   float* qs = att_smem;                 // [G][D]
   float* sc = qs + kAttMaxGroup * D;    // [G][chunk_cap]
   float* red = sc + G * chunk_cap;      // [16 position groups][G][D]
-  for (int i = tid; i < G * D; i += kAttThreads) qs[i] = __half2float(q[i]) * scale;
+  for (int i = tid; i < G * D; i += kAttWideThreads) qs[i] = __half2float(q[i]) * scale;
   __syncthreads();
-  for (int i = tid; i < n; i += kAttThreads) {
+  for (int i = tid; i < n; i += kAttWideThreads) {
     uint4 u[D / 8];
     const uint4* row = reinterpret_cast<const uint4*>(kb + (int64_t)(p_lo + i) * D);
 #pragma unroll
@@ -273,7 +505,7 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
   }
   __syncthreads();
   if (splits == 1) {
-    for (int i = tid; i < G * D; i += kAttThreads) {
+    for (int i = tid; i < G * D; i += kAttWideThreads) {
       float v = 0.f;
 #pragma unroll
       for (int gs = 0; gs < 16; ++gs) v += red[gs * G * D + i];
@@ -282,7 +514,7 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
     return;
   }
   // this split's record: [G][D + 2] = weighted rows, maximum, sum
-  for (int i = tid; i < G * D; i += kAttThreads) {
+  for (int i = tid; i < G * D; i += kAttWideThreads) {
     float v = 0.f;
 #pragma unroll
     for (int gs = 0; gs < 16; ++gs) v += red[gs * G * D + i];
@@ -296,19 +528,25 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
   if (my_ticket != (unsigned)(splits - 1)) return;
   __threadfence();
   const float* all = part - (size_t)blockIdx.z * G * (D + 2);  // record of split 0
-  for (int i = tid; i < G * D; i += kAttThreads) {
+  for (int i = tid; i < G * D; i += kAttWideThreads) {
     const int g = i / D, d = i % D;
+    float mv[kAttWideMaxSplits], lv[kAttWideMaxSplits], nv[kAttWideMaxSplits];  // requested together: one memory round trip
+#pragma unroll
+    for (int s2 = 0; s2 < kAttWideMaxSplits; ++s2) {
+      const float* rec = all + ((size_t)(s2 < splits ? s2 : 0) * G + g) * (D + 2);
+      mv[s2] = __ldcg(rec + D);
+      lv[s2] = s2 < splits ? __ldcg(rec + D + 1) : 0.f;
+      nv[s2] = __ldcg(rec + d);
+    }
     float m = -INFINITY;
-    for (int sp = 0; sp < splits; ++sp) m = fmaxf(m, __ldcg(all + ((size_t)sp * G + g) * (D + 2) + D));
+#pragma unroll
+    for (int s2 = 0; s2 < kAttWideMaxSplits; ++s2) m = fmaxf(m, lv[s2] > 0.f ? mv[s2] : -INFINITY);
     float num = 0.f, den = 0.f;
-    for (int sp = 0; sp < splits; ++sp) {
-      const float* rec = all + ((size_t)sp * G + g) * (D + 2);
-      const float ls = __ldcg(rec + D + 1);
-      if (ls > 0.f) {  // an empty split has no maximum
-        const float f = __expf(__ldcg(rec + D) - m);
-        num += __ldcg(rec + d) * f;
-        den += ls * f;
-      }
+#pragma unroll
+    for (int s2 = 0; s2 < kAttWideMaxSplits; ++s2) {
+      const float f = lv[s2] > 0.f ? __expf(mv[s2] - m) : 0.f;  // an empty split has no maximum
+      num += (lv[s2] > 0.f ? nv[s2] : 0.f) * f;
+      den += lv[s2] * f;
     }
     out_row[i] = __float2half_rn(num / den);
   }
@@ -316,7 +554,7 @@ __device__ __forceinline__ void attention_body(const __half* q, const __half* kb
 }
 
 template <int D>
-__global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(const __half* q, const __half* k_cache, const __half* v_cache,
+__global__ void __launch_bounds__(kAttWideThreads) decode_attention_wide_kernel(const __half* q, const __half* k_cache, const __half* v_cache,
                                                                         const int64_t* pos_dev, int64_t pos_host, __half* out,
                                                                         int hq, int hkv, int max_len, float scale, float* parts,
                                                                         unsigned* tickets) {
@@ -337,10 +575,10 @@ __global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(const __h
   float* part = parts ? parts + (head * splits + sp) * G * (D + 2) : nullptr;
   unsigned* ticket = tickets ? tickets + head : nullptr;
   switch (G) {
-    case 1: attention_body<D, 1>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
-    case 2: attention_body<D, 2>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
-    case 4: attention_body<D, 4>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
-    case 8: attention_body<D, 8>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
+    case 1: attention_wide_body<D, 1>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
+    case 2: attention_wide_body<D, 2>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
+    case 4: attention_wide_body<D, 4>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
+    case 8: attention_wide_body<D, 8>(qp, kb, vb, op, att_smem, p_lo, p_hi, chunk_cap, scale, splits, part, ticket); break;
     default: break;
   }
 }
@@ -397,40 +635,94 @@ extern "C" size_t pe_decode_attention_workspace_bytes(int batch, int hq, int hkv
   return 4096 + (size_t)batch * hkv * kAttMaxSplits * (hq / hkv) * (head_dim + 2) * sizeof(float);
 }
 
+static int attention_launch(AttArgs a, int batch, int head_dim, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!a.k_cache || !a.v_cache || !a.out || batch < 1 || a.hq < 1 || a.hkv < 1 || a.max_len < 1) return PE_ERR_ARG;
+  if (head_dim != 128 || a.hq % a.hkv) return PE_ERR_SHAPE;
+  const int G = a.hq / a.hkv;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(a.k_cache) | reinterpret_cast<uintptr_t>(a.v_cache)) & 15) return PE_ERR_ALIGN;
+  if (batch > 65535) return PE_ERR_LIMIT;
+  // cut the cache positions so that the launch has about two CTAs per SM (at most 16 ranges of at least 32
+  // positions of the longest possible sequence, none without a scratch buffer)
+  int splits = 1;
+  const size_t need = pe_decode_attention_workspace_bytes(batch, a.hq, a.hkv, head_dim);
+  if (workspace && need && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 15)) {
+    const int sms = sm_count();
+    splits = sms > 0 ? (2 * sms) / (a.hkv * batch) : 1;
+    splits = splits < 1 ? 1 : (splits > kAttMaxSplits ? kAttMaxSplits : splits);
+    if (a.max_len < 32 * splits) splits = a.max_len / 32 < 1 ? 1 : a.max_len / 32;
+  }
+  const size_t smem = ((size_t)kAttWarps * G * 128 + 2 * (size_t)kAttWarps * kAttMaxGroup) * sizeof(float);
+  auto kfn = decode_attention_kernel<128>;
+  a.parts = splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 4096) : nullptr;
+  a.tickets = splits > 1 ? static_cast<unsigned*>(workspace) : nullptr;
+  a.scale = 1.f / sqrtf((float)head_dim);
+  PE_CUDA_TRY(launch_pdl(kfn, dim3((unsigned)a.hkv, (unsigned)batch, (unsigned)splits), dim3(kAttThreads), smem,
+                         static_cast<cudaStream_t>(stream), a));
+  return PE_OK;
+}
+
 extern "C" int pe_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos_dev,
                                    int64_t pos_host, void* out, int batch, int hq, int hkv, int head_dim, int max_len,
                                    void* workspace, size_t workspace_bytes, void* stream) {
-  if (!q || !k_cache || !v_cache || !out || batch < 1 || hq < 1 || hkv < 1 || max_len < 1) return PE_ERR_ARG;
-  if (head_dim != 128 || hq % hkv) return PE_ERR_SHAPE;
-  if (hq / hkv != 1 && hq / hkv != 2 && hq / hkv != 4 && hq / hkv != 8) return PE_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return PE_ERR_ALIGN;
-  const int G = hq / hkv;
-  // cut the cache positions so that the launch has about one CTA per SM (at most 8 ranges, none without a
-  // scratch buffer)
-  int splits = 1;
-  const size_t need = pe_decode_attention_workspace_bytes(batch, hq, hkv, head_dim);
-  if (workspace && need && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 15)) {
-    const int sms = sm_count();
-    splits = sms > 0 ? sms / (hkv * batch) : 1;
-    splits = splits < 1 ? 1 : (splits > kAttMaxSplits ? kAttMaxSplits : splits);
-    if (max_len < 64 * splits) splits = max_len / 64 < 1 ? 1 : max_len / 64;
+  if (!q) return PE_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(q) & 7) return PE_ERR_ALIGN;
+  AttArgs a = {};
+  a.q = static_cast<const __half*>(q);
+  a.k_cache = static_cast<__half*>(const_cast<void*>(k_cache));
+  a.v_cache = static_cast<__half*>(const_cast<void*>(v_cache));
+  a.pos_dev = pos_dev; a.pos_host = pos_host;
+  a.out = static_cast<__half*>(out);
+  a.hq = hq; a.hkv = hkv; a.max_len = max_len;
+  const int sms = sm_count();
+  if (sms > 0 && batch >= 1 && hkv >= 1 && (int64_t)batch * hkv * 4 >= sms && head_dim == 128 && hq % hkv == 0 &&
+      (hq / hkv == 1 || hq / hkv == 2 || hq / hkv == 4 || hq / hkv == 8) && k_cache && v_cache && out && max_len >= 1 &&
+      batch <= 65535 && !((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15)) {
+    // many (sequence, kv head) pairs: the thread-per-position kernel
+    const int G = hq / hkv;
+    int splits = 1;
+    const size_t need = pe_decode_attention_workspace_bytes(batch, hq, hkv, head_dim);
+    if (workspace && need && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 15)) {
+      splits = sms / (hkv * batch);
+      splits = splits < 1 ? 1 : (splits > kAttWideMaxSplits ? kAttWideMaxSplits : splits);
+      if (max_len < 64 * splits) splits = max_len / 64 < 1 ? 1 : max_len / 64;
+    }
+    const int chunk_cap = ((max_len + splits - 1) / splits + 3) & ~3;  // as in the kernel
+    const size_t smem = ((size_t)kAttMaxGroup * 128 + (size_t)G * chunk_cap + (size_t)16 * G * 128) * sizeof(float);
+    if (smem <= 200 * 1024) {
+      auto kfn = decode_attention_wide_kernel<128>;
+      static thread_local size_t configured[16] = {0};
+      int dev = 0;
+      PE_CUDA_TRY(cudaGetDevice(&dev));
+      if (smem > 48 * 1024 && (dev >= 16 || configured[dev] < smem)) {
+        PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev < 16) configured[dev] = smem;
+      }
+      float* parts = splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 4096) : nullptr;
+      unsigned* tickets = splits > 1 ? static_cast<unsigned*>(workspace) : nullptr;
+      PE_CUDA_TRY(launch_pdl(kfn, dim3((unsigned)hkv, (unsigned)batch, (unsigned)splits), dim3(kAttWideThreads), smem,
+                             static_cast<cudaStream_t>(stream), static_cast<const __half*>(q), static_cast<const __half*>(k_cache),
+                             static_cast<const __half*>(v_cache), pos_dev, pos_host, static_cast<__half*>(out), hq, hkv, max_len,
+                             1.f / sqrtf((float)head_dim), parts, tickets));
+      return PE_OK;
+    }
   }
-  const int chunk_cap = ((max_len + splits - 1) / splits + 3) & ~3;  // as in the kernel
-  const size_t smem = ((size_t)kAttMaxGroup * 128 + (size_t)G * chunk_cap + (size_t)16 * G * 128) * sizeof(float);
-  if (smem > 200 * 1024 || batch > 65535) return PE_ERR_LIMIT;
-  auto kfn = decode_attention_kernel<128>;
-  static thread_local size_t configured[16] = {0};
-  int dev = 0;
-  PE_CUDA_TRY(cudaGetDevice(&dev));
-  if (smem > 48 * 1024 && (dev >= 16 || configured[dev] < smem)) {
-    PE_CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (dev < 16) configured[dev] = smem;
-  }
-  float* parts = splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 4096) : nullptr;
-  unsigned* tickets = splits > 1 ? static_cast<unsigned*>(workspace) : nullptr;
-  PE_CUDA_TRY(launch_pdl(kfn, dim3((unsigned)hkv, (unsigned)batch, (unsigned)splits), dim3(kAttThreads), smem,
-                         static_cast<cudaStream_t>(stream), static_cast<const __half*>(q), static_cast<const __half*>(k_cache),
-                         static_cast<const __half*>(v_cache), pos_dev, pos_host, static_cast<__half*>(out), hq, hkv, max_len,
-                         1.f / sqrtf((float)head_dim), parts, tickets));
-  return PE_OK;
+  return attention_launch(a, batch, head_dim, workspace, workspace_bytes, stream);
+}
+
+extern "C" int pe_rope_attention(const void* qkv, int64_t ld_qkv, const int64_t* pos_dev, int64_t pos_host, void* k_cache,
+                                 void* v_cache, void* out, int batch, int hq, int hkv, int head_dim, int max_len, float theta,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (!qkv) return PE_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 7) || (ld_qkv & 3)) return PE_ERR_ALIGN;
+  if (hq >= 1 && hkv >= 1 && ld_qkv < (int64_t)(hq + 2 * hkv) * head_dim) return PE_ERR_ARG;
+  AttArgs a = {};
+  a.qkv = static_cast<const __half*>(qkv); a.ld_qkv = ld_qkv;
+  a.k_cache = static_cast<__half*>(k_cache);
+  a.v_cache = static_cast<__half*>(v_cache);
+  a.pos_dev = pos_dev; a.pos_host = pos_host;
+  a.out = static_cast<__half*>(out);
+  a.hq = hq; a.hkv = hkv; a.max_len = max_len;
+  a.theta = theta;
+  return attention_launch(a, batch, head_dim, workspace, workspace_bytes, stream);
 }

@@ -317,7 +317,59 @@ struct ColArgs {
   void* y; int y_dtype;
   const __half* bias;
   int N, K, n_chunks;
+  // activation prologue (PE_PRO_*): what turns `x` into the matmul input
+  int pro;
+  const void* delta; int delta_dtype;  // PE_PRO_ADD_RMSNORM: optional addend of the residual x (fp16 / fp32)
+  const __half* norm_w;                // PE_PRO_ADD_RMSNORM: norm weight
+  __half* resid_out;                   // PE_PRO_ADD_RMSNORM: the updated residual (written by CTA 0), may be null
+  float eps;
 };
+
+// ---- activation prologues: the glue op in front of a projection, computed while its input is staged ----
+// PE_PRO_ADD_RMSNORM  input = half(r * rsqrt(mean(r^2) + eps)) * w   with r = half(x + half(delta)), the rounding
+//                     steps of pe_add_rmsnorm;  PE_PRO_SILU_MUL  input = half(silu(gate)) * up, those of pe_silu_mul.
+// 4 consecutive elements starting at `col` (a multiple of 4), zero beyond in_f.
+__device__ __forceinline__ void resid4(const ColArgs& p, int col, float r[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const __half*>(p.x) + col);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  r[0] = a.x; r[1] = a.y; r[2] = b.x; r[3] = b.y;
+  if (p.delta) {
+    float d[4];
+    if (p.delta_dtype == PE_F32) {
+      const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(p.delta) + col);
+      d[0] = f.x; d[1] = f.y; d[2] = f.z; d[3] = f.w;
+    } else {
+      const uint2 du = *reinterpret_cast<const uint2*>(static_cast<const __half*>(p.delta) + col);
+      const float2 da = __half22float2(*reinterpret_cast<const __half2*>(&du.x)), db = __half22float2(*reinterpret_cast<const __half2*>(&du.y));
+      d[0] = da.x; d[1] = da.y; d[2] = db.x; d[3] = db.y;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = __half2float(__float2half_rn(r[i] + __half2float(__float2half_rn(d[i]))));
+  }
+}
+
+__device__ __forceinline__ void pro_load4(const ColArgs& p, int col, bool on, float scale, float v[4]) {
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  if (!on || col >= p.in_f) return;  // in_f is a multiple of 4 on this path
+  if (p.pro == PE_PRO_ADD_RMSNORM) {
+    float r[4];
+    resid4(p, col, r);
+    const uint2 wu = *reinterpret_cast<const uint2*>(p.norm_w + col);
+    const __half2 n0 = __hmul2(__floats2half2_rn(r[0] * scale, r[1] * scale), *reinterpret_cast<const __half2*>(&wu.x));
+    const __half2 n1 = __hmul2(__floats2half2_rn(r[2] * scale, r[3] * scale), *reinterpret_cast<const __half2*>(&wu.y));
+    const float2 a = __half22float2(n0), b = __half22float2(n1);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  } else {  // PE_PRO_SILU_MUL: x = [gate (in_f) | up (in_f)]
+    const uint2 g = *reinterpret_cast<const uint2*>(static_cast<const __half*>(p.x) + col);
+    const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const __half*>(p.x) + p.in_f + col);
+    const float2 g0 = __half22float2(*reinterpret_cast<const __half2*>(&g.x)), g1 = __half22float2(*reinterpret_cast<const __half2*>(&g.y));
+    const __half2 s0 = __floats2half2_rn(g0.x / (1.f + expf(-g0.x)), g0.y / (1.f + expf(-g0.y)));
+    const __half2 s1 = __floats2half2_rn(g1.x / (1.f + expf(-g1.x)), g1.y / (1.f + expf(-g1.y)));
+    const float2 a = __half22float2(__hmul2(s0, *reinterpret_cast<const __half2*>(&u.x)));
+    const float2 b = __half22float2(__hmul2(s1, *reinterpret_cast<const __half2*>(&u.y)));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+}
 
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
@@ -332,6 +384,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
   constexpr int kGroupRows = 4 * SUB;  // weight rows of one item
   static_assert(DEPTH % CPW == 0, "the ring holds whole row groups");
   extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ float pro_red[kRowWarps];
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int rs = lane >> 3, pc = lane & 7;  // row of the sub-item, 16-byte piece of the chunk
   const int G = gridDim.x, cta = blockIdx.x;
@@ -431,18 +484,47 @@ __global__ void __launch_bounds__(kRowThreads, 1) gemv_cols_kernel(const ColArgs
     const int limit = raw ? p.in_f : p.K;
     constexpr int BPC = PACKED ? 2 : 1;  // quantization blocks per chunk
     float v[CPW * BPC][4];
-    // All loads are issued before any of them is used: the issue order is the program
-    // order, so a conversion placed right behind its load would make every load wait for
-    // the one before it (one memory round trip per block instead of one in total).
-    Raw4 raw4[CPW * BPC];
+    if (p.pro == PE_PRO_NONE) {
+      // All loads are issued before any of them is used: the issue order is the program
+      // order, so a conversion placed right behind its load would make every load wait for
+      // the one before it (one memory round trip per block instead of one in total).
+      Raw4 raw4[CPW * BPC];
 #pragma unroll
-    for (int u = 0; u < CPW * BPC; ++u) {
-      const bool on = u / BPC < cnt;
-      const int col = (on ? (w + 16 * (u / BPC)) * BPC + (u % BPC) : 0) * kBlock + lane * 4;
-      raw4[u] = load4_raw(p.x, p.x_dtype, 0, col, on ? limit : 0, vec_ok);
+      for (int u = 0; u < CPW * BPC; ++u) {
+        const bool on = u / BPC < cnt;
+        const int col = (on ? (w + 16 * (u / BPC)) * BPC + (u % BPC) : 0) * kBlock + lane * 4;
+        raw4[u] = load4_raw(p.x, p.x_dtype, 0, col, on ? limit : 0, vec_ok);
+      }
+#pragma unroll
+      for (int u = 0; u < CPW * BPC; ++u) cvt4(raw4[u], p.x_dtype, v[u]);
+    } else {
+      float scale = 1.f;
+      if (p.pro == PE_PRO_ADD_RMSNORM) {
+        // mean square of the updated residual over the whole row: every CTA computes it for itself (8 KB from
+        // L2); CTA 0 also stores the updated residual for the launches that follow
+        float ss = 0.f;
+        for (int col = tid * 4; col < p.in_f; col += kRowThreads * 4) {
+          float r[4];
+          resid4(p, col, r);
+          if (cta == 0 && p.resid_out)
+            *reinterpret_cast<uint2*>(p.resid_out + col) = make_uint2(pack_half2(r[0], r[1]), pack_half2(r[2], r[3]));
+          ss += r[0] * r[0] + r[1] * r[1] + r[2] * r[2] + r[3] * r[3];
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) pro_red[w] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < kRowWarps; ++i) tot += pro_red[i];
+        scale = rsqrtf(tot / (float)p.in_f + p.eps);
+      }
+#pragma unroll
+      for (int u = 0; u < CPW * BPC; ++u) {
+        const bool on = u / BPC < cnt;
+        const int col = (on ? (w + 16 * (u / BPC)) * BPC + (u % BPC) : 0) * kBlock + lane * 4;
+        pro_load4(p, col, on, scale, v[u]);
+      }
     }
-#pragma unroll
-    for (int u = 0; u < CPW * BPC; ++u) cvt4(raw4[u], p.x_dtype, v[u]);
 #pragma unroll
     for (int u = 0; u < CPW * BPC; ++u) {
       if (u / BPC < cnt) {  // warp-uniform
@@ -570,10 +652,13 @@ static int launch_cols_cpw(const ColArgs& a, int cpw, int G, cudaStream_t st) {
   }
 }
 
+struct ProArgs { int pro; const void* delta; int delta_dtype; const void* norm_w; void* resid_out; float eps; };
+
 // batch 1: returns 1 if the shape is not this kernel's kind
 static int gemv_cols_try(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
                          const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int in_f, void* y,
-                         int y_dtype, const void* bias, int out_f, int K, int sms, cudaStream_t stream) {
+                         int y_dtype, const void* bias, int out_f, int K, int sms, cudaStream_t stream,
+                         const ProArgs* pro = nullptr) {
   const int64_t row_bytes = packed ? K / 2 : K;
   // norms are copied 4 bytes (two blocks) at a time: rows of norms must start 4-byte aligned and hold an even count
   if (row_bytes % 128 || (ld_norms & 1) || ((K / kBlock) & 1) || (reinterpret_cast<uintptr_t>(norms) & 3)) return 1;
@@ -592,6 +677,11 @@ static int gemv_cols_try(const void* codes, int packed, int64_t ld_codes, const 
   a.y = y; a.y_dtype = y_dtype;
   a.bias = static_cast<const __half*>(bias);
   a.N = out_f; a.K = K; a.n_chunks = n_chunks;
+  a.pro = pro ? pro->pro : PE_PRO_NONE;
+  a.delta = pro ? pro->delta : nullptr; a.delta_dtype = pro ? pro->delta_dtype : PE_F16;
+  a.norm_w = pro ? static_cast<const __half*>(pro->norm_w) : nullptr;
+  a.resid_out = pro ? static_cast<__half*>(pro->resid_out) : nullptr;
+  a.eps = pro ? pro->eps : 0.f;
   if (packed && n_levels <= 8) return launch_cols_cpw<true, true>(a, cpw, G, stream);
   if (packed) return launch_cols_cpw<true, false>(a, cpw, G, stream);
   return launch_cols_cpw<false, false>(a, cpw, G, stream);
@@ -673,3 +763,31 @@ int gemv_rows_try(const void* codes, int packed, int64_t ld_codes, const void* n
 }
 
 }  // namespace pe
+
+// ---- batch-1 matmul with the glue op in front of it computed while the input is staged ----
+extern "C" int pe_gemv_pro(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
+                           const float* ct_scaled, int n_levels, int prologue, const void* x, int in_f, const void* delta,
+                           int delta_dtype, const void* norm_weight, void* resid_out, float eps, void* y, int y_dtype,
+                           const void* bias, int out_f, int in_f_padded, void* stream) {
+  using namespace pe;
+  if (!codes || !norms || !ct_scaled || !x || !y) return PE_ERR_ARG;
+  if (prologue != PE_PRO_ADD_RMSNORM && prologue != PE_PRO_SILU_MUL) return PE_ERR_ARG;
+  if (prologue == PE_PRO_ADD_RMSNORM && (!norm_weight || (delta && delta_dtype != PE_F16 && delta_dtype != PE_F32))) return PE_ERR_ARG;
+  if (out_f < 1 || in_f < 4 || in_f > in_f_padded || y_dtype < PE_F32 || y_dtype > PE_BF16) return PE_ERR_ARG;
+  if (n_levels < 2 || n_levels > 256 || (packed && n_levels > 16)) return PE_ERR_ARG;
+  if (in_f_padded % kBlock || in_f % 4) return PE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (ld_codes & 15)) return PE_ERR_ALIGN;
+  // the prologue reads its operands 8 or 16 bytes at a time
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(norm_weight) |
+       reinterpret_cast<uintptr_t>(resid_out)) & 15)
+    return PE_ERR_ALIGN;
+  if (prologue == PE_PRO_SILU_MUL && (in_f % 8)) return PE_ERR_SHAPE;  // the `up` half starts in_f elements in: keep it 16-byte aligned
+  if (ld_codes < (packed ? in_f_padded / 2 : in_f_padded) || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  const int sms = sm_count();
+  if (sms <= 0) return PE_ERR_CUDA;
+  ProArgs pro = {prologue, delta, delta_dtype, norm_weight, resid_out, eps};
+  const int r = gemv_cols_try(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, PE_X_RAW, PE_F16, in_f, y, y_dtype,
+                              bias, out_f, in_f_padded, sms, static_cast<cudaStream_t>(stream), &pro);
+  return r == 1 ? PE_ERR_SHAPE : r;  // shapes the column-owner kernel does not take: the caller runs the separate launches
+}
+

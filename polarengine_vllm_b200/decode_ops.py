@@ -78,6 +78,27 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
+def rope_attention(qkv: torch.Tensor, pos: Union[int, torch.Tensor], k_cache: torch.Tensor, v_cache: torch.Tensor, hq: int, hkv: int,
+                   head_dim: int, theta: float) -> torch.Tensor:
+    """One new token per sequence, rotary embedding + KV-cache write + attention in one launch: qkv (batch,
+    (hq + 2 hkv) * head_dim) fp16 is the raw fused projection; returns (batch, hq * head_dim) fp16 and leaves the
+    rotated key and the value in the caches at ``pos``."""
+    dev = nv.require_cuda(qkv, k_cache, v_cache)
+    if qkv.dtype != torch.float16 or qkv.stride(1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise ValueError("rope_attention wants fp16 qkv rows and contiguous caches")
+    batch, max_len = qkv.shape[0], k_cache.shape[2]
+    out = torch.empty(batch, hq * head_dim, dtype=torch.float16, device=dev)
+    dev_pos = pos if torch.is_tensor(pos) else None
+    need = nv.lib().pe_decode_attention_workspace_bytes(batch, hq, hkv, head_dim)
+    ws = _attention_scratch(dev, need) if need else None
+    nv.check(nv.lib().pe_rope_attention(qkv.data_ptr(), qkv.stride(0), dev_pos.data_ptr() if dev_pos is not None else None,
+                                        0 if dev_pos is not None else int(pos), k_cache.data_ptr(), v_cache.data_ptr(),
+                                        out.data_ptr(), batch, hq, hkv, head_dim, max_len, float(theta),
+                                        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                        nv.stream_ptr(dev)), "pe_rope_attention")
+    return out
+
+
 _att_ws = {}
 
 

@@ -24,8 +24,9 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .decode_ops import add_rmsnorm, decode_attention, rope_cache, silu_mul
-from .kernels import quant_embedding, quant_matmul, retile
+from .decode_ops import add_rmsnorm, decode_attention, rope_attention, rope_cache, silu_mul
+from . import _native as nv
+from .kernels import quant_embedding, quant_matmul, quant_matmul_pro, retile
 from .packing import pack_codes_half_block
 from .parallel import PeerExchange, shard_codes_for_tp, shard_norms_for_tp
 from .utils import get_centroids, get_ct_scaled
@@ -78,6 +79,12 @@ class QWeight:
     @classmethod
     def synthetic(cls, out_f: int, in_f: int, bits: int, dev, gen: torch.Generator) -> "QWeight":
         return cls(*synth_weight(out_f, in_f, bits, dev, gen), bits)
+
+    def fused(self, prologue: int, x: torch.Tensor, out_dtype=torch.float16, **kw) -> Optional[torch.Tensor]:
+        """One token with the glue op in front of the projection folded into the launch; None if the layer's
+        shape is not one the batch-1 kernel takes."""
+        return quant_matmul_pro(self.codes, self.packed, self.norms, self.ct, prologue, x, self.in_f, self.out_f, self.in_f,
+                                out_dtype, **kw)
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
         if self.tiles is None and 3 <= x.shape[0] <= 16 and not torch.cuda.is_current_stream_capturing():
@@ -151,6 +158,8 @@ class QuantDecoder:
         del c, n
         self.final_ln = torch.ones(cfg.hidden, dtype=torch.float16, device=dev)
         self.max_len = max_len
+        self.n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.fuse_glue = True   # fold norm / activation into the projections' launches when one token is decoded
         self.fused_allreduce = fused_allreduce
         self.xchg = None
         self.alloc_cache(batch)
@@ -196,22 +205,50 @@ class QuantDecoder:
                 return self.xchg.allreduce_add_rmsnorm(partial, x, w, cfg.rms_eps)
             return add_rmsnorm(x, self._all_reduce(partial), w, cfg.rms_eps)
 
+        # One token on one rank: the residual add + RMSNorm in front of q/k/v and gate/up and the SiLU * up in
+        # front of down are computed by the projection's own launch (6 launches per layer instead of 9).  The
+        # residual alternates between two buffers because every CTA of such a launch reads the old one.
+        one = b * t == 1 and self.fuse_glue
+        fold_norm = one and self.tp == 1   # with several ranks the all-reduce kernel does the add + norm
+        x_alt = torch.empty_like(x) if fold_norm else None
+
+        def norm_proj(W, delta, w, out_dtype=torch.float16):   # W(norm(x += delta))
+            nonlocal x, x_alt
+            if fold_norm:
+                y = W.fused(nv.PE_PRO_ADD_RMSNORM, x, out_dtype, delta=delta, norm_weight=w, eps=cfg.rms_eps,
+                            resid_out=x_alt if delta is not None else None)
+                if y is not None:
+                    if delta is not None:
+                        x, x_alt = x_alt, x
+                    return y
+            h = add_rmsnorm(x, None, w, cfg.rms_eps) if delta is None else reduce_add_norm(delta, w)
+            return W(h, out_dtype)
+
         for li, L in enumerate(self.layers):
-            h = add_rmsnorm(x, None, L["ln1"], cfg.rms_eps) if delta is None else reduce_add_norm(delta, L["ln1"])
-            qkv = L["qkv"](h)
-            q = rope_cache(qkv, pos0, self.k_cache[li], self.v_cache[li], b, t, self.hq, self.hkv, d, cfg.rope_theta)
-            if t == 1 and d == 128:  # decode: one launch over the cache, length from the position scalar
+            qkv = norm_proj(L["qkv"], delta, L["ln1"])
+            if t == 1 and d == 128 and self.fuse_glue and b * self.hkv * 4 < self.n_sms:  # few sequences: rotary, cache write and attention in one launch
+                att = rope_attention(qkv, pos0, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, d, cfg.rope_theta)
+            elif t == 1 and d == 128:
+                q = rope_cache(qkv, pos0, self.k_cache[li], self.v_cache[li], b, t, self.hq, self.hkv, d, cfg.rope_theta)
                 att = decode_attention(q, self.k_cache[li], self.v_cache[li], pos0)
             else:
+                q = rope_cache(qkv, pos0, self.k_cache[li], self.v_cache[li], b, t, self.hq, self.hkv, d, cfg.rope_theta)
                 p0 = int(pos0)
                 att = F.scaled_dot_product_attention(q, self.k_cache[li][:, :, : p0 + t], self.v_cache[li][:, :, : p0 + t],
                                                      is_causal=(p0 == 0 and t > 1), enable_gqa=True)
                 att = att.transpose(1, 2).reshape(b * t, self.hq * d)
-            h = reduce_add_norm(L["o"](att, torch.float32), L["ln2"])
-            act = silu_mul(L["gate_up"](h), self.inter)
-            delta = L["down"](act, torch.float32)
-        h = reduce_add_norm(delta, self.final_ln).view(b, t, cfg.hidden)[:, -1]
-        logits = self.head(h, torch.float32)                      # (B, vocab / tp)
+            gate_up = norm_proj(L["gate_up"], L["o"](att, torch.float32), L["ln2"])
+            delta = L["down"].fused(nv.PE_PRO_SILU_MUL, gate_up, torch.float32) if one else None
+            if delta is None:
+                delta = L["down"](silu_mul(gate_up, self.inter), torch.float32)
+        if fold_norm:
+            logits = self.head.fused(nv.PE_PRO_ADD_RMSNORM, x, torch.float32, delta=delta, norm_weight=self.final_ln,
+                                     eps=cfg.rms_eps, resid_out=x_alt)
+        else:
+            logits = None
+        if logits is None:
+            h = reduce_add_norm(delta, self.final_ln).view(b, t, cfg.hidden)[:, -1]
+            logits = self.head(h, torch.float32)                  # (B, vocab / tp)
         if return_logits:
             if self.tp == 1:
                 return logits

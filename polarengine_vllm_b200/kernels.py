@@ -89,6 +89,44 @@ def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scal
     return quant_gemm(codes, packed, norms, ct, x, rotated, out_f, in_f, in_f_padded, y, bias)
 
 
+def quant_matmul_pro(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scaled: torch.Tensor, prologue: int,
+                     x: torch.Tensor, in_f: int, out_f: int, in_f_padded: int, out_dtype: torch.dtype = torch.float16, *,
+                     delta: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                     resid_out: Optional[torch.Tensor] = None, eps: float = 0.0,
+                     bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One-token matmul with the glue op in front of it folded into the launch (``pe_gemv_pro``).
+
+    ``prologue`` = ``PE_PRO_ADD_RMSNORM``: ``x`` is the fp16 residual row (in_f), ``delta`` (fp16 / fp32, optional) is
+    added to it, the sum goes to ``resid_out`` and its RMSNorm times ``norm_weight`` is the matmul input;
+    ``PE_PRO_SILU_MUL``: ``x`` is ``[gate | up]`` (2 * in_f) and the input is ``silu(gate) * up``.
+    Returns y (1, out_f), or None when the batch-1 kernel does not take the layer's shape (the caller then runs the
+    glue op and :func:`quant_matmul`)."""
+    dev = nv.require_cuda(codes, norms, ct_scaled, x)
+    nv.ensure_init(dev)
+    width = in_f if prologue == nv.PE_PRO_ADD_RMSNORM else 2 * in_f
+    if x.dtype != torch.float16 or x.numel() != width or not x.is_contiguous():
+        raise ValueError("the fused prologues take one contiguous fp16 activation row")
+    for t in (delta, resid_out):
+        if t is not None and (t.numel() != in_f or not t.is_contiguous()):
+            raise ValueError("delta / resid_out must be contiguous rows of in_f elements")
+    if resid_out is not None and (resid_out.dtype != torch.float16 or resid_out.data_ptr() == x.data_ptr()):
+        raise ValueError("resid_out must be an fp16 row other than x")
+    norms = norms.reshape(out_f, -1)
+    y = torch.empty(1, out_f, dtype=out_dtype, device=dev)
+    rc = nv.lib().pe_gemv_pro(codes.data_ptr(), int(packed), codes.stride(0) * codes.element_size(), norms.data_ptr(),
+                              norms.stride(0), ct_scaled.data_ptr(), ct_scaled.numel(), prologue, x.data_ptr(), in_f,
+                              delta.data_ptr() if delta is not None else None,
+                              nv.dtype_code(delta) if delta is not None else nv.PE_F16,
+                              norm_weight.data_ptr() if norm_weight is not None else None,
+                              resid_out.data_ptr() if resid_out is not None else None, float(eps), y.data_ptr(),
+                              nv.dtype_code(y), bias.data_ptr() if bias is not None else None, out_f, in_f_padded,
+                              nv.stream_ptr(dev))
+    if rc == -2:  # PE_ERR_SHAPE: not a layer of the batch-1 kernel
+        return None
+    nv.check(rc, "pe_gemv_pro")
+    return y
+
+
 def polar_matmul(codes: Optional[torch.Tensor], x_transformed: torch.Tensor, norms: torch.Tensor,
                  ct_scaled: torch.Tensor, out_f: int, in_f_padded: int, n_blocks: int, block_size: int = 128,
                  packed: bool = False, packed_codes: Optional[torch.Tensor] = None,

@@ -77,7 +77,7 @@ def test_size_queries_of_the_grouped_and_exchange_entry_points():
     # exchange buffer: flags + two parities of world x rows x hidden fp32
     assert lib.pe_allreduce_buffer_bytes(8, 32, 4096) == 4096 + 2 * 8 * 32 * 4096 * 4
     assert lib.pe_allreduce_buffer_bytes(17, 1, 4096) == 0 and lib.pe_allreduce_buffer_bytes(8, 256, 4096) == 0
-    assert lib.pe_decode_attention_workspace_bytes(1, 32, 8, 128) == 4096 + 8 * 8 * 4 * 130 * 4
+    assert lib.pe_decode_attention_workspace_bytes(1, 32, 8, 128) == 4096 + 8 * 16 * 4 * 130 * 4
     assert lib.pe_decode_attention_workspace_bytes(1, 32, 8, 64) == 0
     assert lib.pe_gemv_noalloc_max_bytes() == 8 << 20
     # NULL pointers are refused before anything touches a device

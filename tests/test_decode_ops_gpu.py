@@ -149,3 +149,84 @@ def test_exchange_wait_runs_out_and_reports():
     out2 = xchg.allreduce_add_rmsnorm(part, x, w, 1e-6)
     assert torch.equal(out2, add_rmsnorm(x_ref, part, w, 1e-6)) and not xchg.timed_out()
     assert lib.pe_set_wait_limit_us(0) == -1
+
+
+@pytest.mark.parametrize("bits,n,k", [(5, 6144, 4096), (3, 24576, 4096), (6, 151936 // 8, 4096), (4, 4096, 1024)])
+def test_projection_with_folded_add_rmsnorm(bits, n, k):
+    """pe_gemv_pro(PE_PRO_ADD_RMSNORM) = pe_add_rmsnorm followed by pe_gemv: same updated residual (bit for bit)
+    and the same projection within the fp16 rounding of the norm scale (the two kernels sum the squares in
+    different orders)."""
+    from helpers import rand_layer
+    from polarengine_vllm_b200 import _native as nv, kernels, packing
+    from polarengine_vllm_b200.decode_ops import add_rmsnorm
+    dev = torch.device("cuda")
+    codes, norms, cts = rand_layer(n, k, bits, seed=bits + n)
+    packed = bits <= 4
+    w = packing.pack_codes_half_block(codes.to(dev)) if packed else codes.to(dev)
+    nd, ctd = norms.to(dev), cts.to(dev)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(1, k, device=dev, generator=g).half()
+    lnw = (1 + 0.1 * torch.randn(k, device=dev, generator=g)).half()
+    for delta in (None, torch.randn(1, k, device=dev, generator=g), torch.randn(1, k, device=dev, generator=g).half()):
+        x_ref = x.clone()
+        h = add_rmsnorm(x_ref, delta, lnw, 1e-6)
+        y_ref = kernels.quant_matmul(w, packed, nd, ctd, h, False, n, k, k, torch.float32)
+        resid = torch.full_like(x, float("nan"))
+        y = kernels.quant_matmul_pro(w, packed, nd, ctd, nv.PE_PRO_ADD_RMSNORM, x, k, n, k, torch.float32, delta=delta,
+                                     norm_weight=lnw, eps=1e-6, resid_out=resid if delta is not None else None)
+        assert y is not None and y.shape == (1, n)
+        if delta is not None:
+            assert torch.equal(resid, x_ref)
+        assert float((y - y_ref).abs().max() / y_ref.abs().max()) <= 2e-3
+
+
+@pytest.mark.parametrize("bits,n,inter", [(4, 4096, 12288), (4, 4096, 1536), (3, 2048, 4096)])
+def test_projection_with_folded_silu_mul(bits, n, inter):
+    """pe_gemv_pro(PE_PRO_SILU_MUL) = pe_silu_mul followed by pe_gemv (same rounding steps: bit-identical)."""
+    from helpers import rand_layer
+    from polarengine_vllm_b200 import _native as nv, kernels, packing
+    from polarengine_vllm_b200.decode_ops import silu_mul
+    dev = torch.device("cuda")
+    codes, norms, cts = rand_layer(n, inter, bits, seed=inter)
+    w = packing.pack_codes_half_block(codes.to(dev))
+    nd, ctd = norms.to(dev), cts.to(dev)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    gu = torch.randn(1, 2 * inter, device=dev, generator=g).half()
+    y_ref = kernels.quant_matmul(w, True, nd, ctd, silu_mul(gu, inter), False, n, inter, inter, torch.float32)
+    y = kernels.quant_matmul_pro(w, True, nd, ctd, nv.PE_PRO_SILU_MUL, gu, inter, n, inter, torch.float32)
+    assert y is not None
+    assert torch.equal(y, y_ref)
+
+
+def test_folded_prologue_declines_shapes_of_other_kernels():
+    from helpers import rand_layer
+    from polarengine_vllm_b200 import _native as nv, kernels
+    codes, norms, cts = rand_layer(48, 256, 5, seed=1)
+    x = torch.randn(1, 256, device="cuda").half()
+    y = kernels.quant_matmul_pro(codes.cuda(), False, norms.cuda(), cts.cuda(), nv.PE_PRO_ADD_RMSNORM, x, 256, 48, 256,
+                                 norm_weight=torch.ones(256, device="cuda").half(), eps=1e-6)
+    assert y is None
+
+
+@pytest.mark.parametrize("batch,hq,hkv,pos,on_device", [(1, 32, 8, 512, True), (2, 4, 2, 20, True), (3, 8, 8, 0, False),
+                                                        (1, 4, 1, 639, True), (8, 32, 8, 100, False)])
+def test_rope_attention_equals_the_two_launches(batch, hq, hkv, pos, on_device):
+    """pe_rope_attention = pe_rope_cache (one token) followed by pe_decode_attention: same cache rows, and the
+    same attention output bit for bit where both run the warp-per-position kernel (with many sequences the
+    two-launch form takes the thread-per-position kernel: equal within fp16 rounding)."""
+    from polarengine_vllm_b200.decode_ops import decode_attention, rope_attention, rope_cache
+    d, max_len, theta = 128, 640, 1e6
+    g = torch.Generator(device="cuda").manual_seed(pos + hq + batch)
+    qkv = torch.randn(batch, (hq + 2 * hkv) * d, device="cuda", generator=g).half()
+    kc = torch.randn(batch, hkv, max_len, d, device="cuda", generator=g).half()
+    vc = torch.randn(batch, hkv, max_len, d, device="cuda", generator=g).half()
+    kc2, vc2 = kc.clone(), vc.clone()
+    p = torch.tensor(pos, device="cuda") if on_device else pos
+    q = rope_cache(qkv, p, kc, vc, batch, 1, hq, hkv, d, theta)
+    ref = decode_attention(q, kc, vc, p)
+    out = rope_attention(qkv, p, kc2, vc2, hq, hkv, d, theta)
+    assert torch.equal(kc2, kc) and torch.equal(vc2, vc)
+    if batch * hkv * 4 < torch.cuda.get_device_properties(0).multi_processor_count:
+        assert torch.equal(out, ref)
+    else:
+        assert torch.allclose(out.float(), ref.float(), rtol=2e-3, atol=2e-3)

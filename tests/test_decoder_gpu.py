@@ -60,3 +60,25 @@ def test_projection_matches_dense_layer():
         ref = xin.float().cpu() @ dense.T
         y = w(xin, torch.float32).cpu()
         assert float((y - ref).abs().max() / ref.abs().max()) <= 1e-2
+
+
+def test_folded_glue_ops_give_the_same_tokens():
+    """One-token decode with the norm / activation folded into the projections' launches against the same model
+    with every glue op as its own launch: same logits within fp16 rounding, same next tokens."""
+    from polarengine_vllm_b200.decoder import DecoderConfig, QuantDecoder
+    cfg = DecoderConfig(hidden=1024, n_heads=8, n_kv_heads=2, head_dim=128, intermediate=2048, n_layers=3, vocab=4096)
+    dev = torch.device("cuda")
+    a = QuantDecoder(cfg, dev, max_len=64, batch=1)
+    b = QuantDecoder(cfg, dev, max_len=64, batch=1)
+    b.fuse_glue = False
+    g = torch.Generator(device="cuda").manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab, (1, 12), device=dev, generator=g)
+    ia, ib = a.forward(prompt, 0), b.forward(prompt, 0)
+    assert torch.equal(ia, ib)
+    ids = ia.view(1, 1)
+    for s in range(4):
+        pos = torch.tensor(12 + s, device=dev)
+        la, lb = a.forward(ids, pos, return_logits=True), b.forward(ids, pos, return_logits=True)
+        assert float((la - lb).abs().max() / lb.abs().max()) <= 5e-3
+        assert torch.equal(la.argmax(-1), lb.argmax(-1))
+        ids = lb.argmax(-1).view(1, 1)
