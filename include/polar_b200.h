@@ -133,6 +133,17 @@ int pe_rope_attention(const void* qkv, int64_t ld_qkv, const int64_t* pos_dev, i
                       void* out, int batch, int hq, int hkv, int head_dim, int max_len, float theta, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* ---- quantizer --------------------------------------------------------------
+ * weight (out_f, in_f) fp32/fp16/bf16 -> codes int8 (out_f, in_f_padded), norms fp16 (out_f, in_f_padded/128):
+ * per 128-block zero-pad, L2 norm (clamped at 1e-10), divide, rotate, scale by sqrt(128), index of the nearest of
+ * `levels` (the UNscaled Lloyd-Max centroids; first minimum wins).  The arithmetic of
+ * PolarQuantizer.quantize_tensor (quantizer.py:206-257) on the device; rotation and norm are summed in another
+ * order than the reference's matrix product, so codes on a cell boundary may differ (a few per million).
+ * Follow with pe_pack_nibble for widths <= 4 bits. */
+int pe_quantize(const void* weight, int w_dtype, int64_t ld_w, int64_t out_f, int in_f, int in_f_padded,
+                const float* levels, int n_levels, int8_t* codes, int64_t ld_codes, void* norms, int64_t ld_norms,
+                void* stream);
+
 /* ---- nibble packing ---------------------------------------------------------
  * int8 codes (out_f, in_f_padded) -> uint8 (out_f, in_f_padded/2), byte i of each
  * 128-block = code[64+i] << 4 | code[i].  Replaces pack_codes_int4

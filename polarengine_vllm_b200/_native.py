@@ -31,6 +31,7 @@ SIGNATURES = {
     "pe_set_wait_limit_us": (_i, [_i64]),
     "pe_fwht128": (_i, [_vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "pe_embedding": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
+    "pe_quantize": (_i, [_vp, _i, _i64, _i64, _i, _i, _vp, _i, _vp, _i64, _vp, _i64, _vp]),
     "pe_pack_nibble": (_i, [_vp, _vp, _i64, _i64, _vp]),
     "pe_gemv_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,

@@ -45,6 +45,49 @@ __global__ void __launch_bounds__(256) pack_nibble_kernel(const int8_t* codes, u
   *reinterpret_cast<uint4*>(packed + i * 16) = r;
 }
 
+// Quantizer: one warp per (weight row, 128-block).  Zero-pad, L2 norm clamped at 1e-10, divide, rotate, scale by
+// sqrt(128), nearest Lloyd-Max level by distance (first minimum wins, as the reference's argmin does), int8 code
+// and fp16 norm out.  The butterfly rotation and the warp-order sum of squares round differently from the
+// reference's matrix product and torch.norm, so a value that sits on a cell boundary to within fp32 rounding can
+// land on the other side: a few codes per million differ from the CPU quantizer.
+__global__ void __launch_bounds__(256) quantize_kernel(const void* w, int w_dtype, int64_t ld_w, int64_t rows, int in_f, int nb,
+                                                       const float* levels, int n_levels, int8_t* codes, int64_t ld_codes,
+                                                       __half* norms, int64_t ld_norms) {
+  extern __shared__ float lv[];
+  for (int i = threadIdx.x; i < n_levels; i += blockDim.x) lv[i] = levels[i];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp >= rows * nb) return;  // whole warps leave together
+  const int64_t r = warp / nb;
+  const int blk = (int)(warp - r * nb);
+  const bool vin = (ld_w % 4 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+  float v[4];
+  load4_as_float(w, w_dtype, r * ld_w, blk * kBlock + lane * 4, in_f, vin, v);
+  float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+  const float nrm = fmaxf(sqrtf(ss), 1e-10f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __fdiv_rn(v[i], nrm);
+  warp_fwht128(v, lane);  // includes the 1/sqrt(128) of the normalised Hadamard matrix
+  const float root = 11.313708498984761f;  // sqrt(128)
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float x = v[i] * root;
+    int best = 0;
+    float bd = fabsf(x - lv[0]);
+    for (int j = 1; j < n_levels; ++j) {
+      const float d = fabsf(x - lv[j]);
+      if (d < bd) { bd = d; best = j; }
+    }
+    packed |= (uint32_t)(best & 0xff) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(codes + r * ld_codes + blk * kBlock + lane * 4) = packed;
+  if (lane == 0) norms[r * ld_norms + blk] = __float2half_rn(nrm);
+}
+
 // Quantized embedding lookup: row ids[t] of the table is dequantised on the fly.
 // One warp per (token, 128-block): centroid gather, inverse rotation (the rotation is its
 // own inverse), block norm, cast.
@@ -133,6 +176,24 @@ extern "C" int pe_pack_nibble(const int8_t* codes, uint8_t* packed, int64_t out_
   const int64_t blocks = (n_chunks + 255) / 256;
   if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
   pack_nibble_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, packed, n_chunks);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
+
+extern "C" int pe_quantize(const void* weight, int w_dtype, int64_t ld_w, int64_t out_f, int in_f, int in_f_padded,
+                           const float* levels, int n_levels, int8_t* codes, int64_t ld_codes, void* norms, int64_t ld_norms,
+                           void* stream) {
+  if (!weight || !levels || !codes || !norms || out_f < 1 || in_f < 1 || in_f > in_f_padded) return PE_ERR_ARG;
+  if (w_dtype < PE_F32 || w_dtype > PE_BF16 || n_levels < 2 || n_levels > 256) return PE_ERR_ARG;
+  if (in_f_padded % kBlock) return PE_ERR_SHAPE;
+  if (ld_w < in_f || ld_codes < in_f_padded || ld_norms < in_f_padded / kBlock) return PE_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(codes) & 3) || (ld_codes & 3)) return PE_ERR_ALIGN;
+  const int nb = in_f_padded / kBlock;
+  const int64_t warps = out_f * nb;
+  const int64_t blocks = (warps + 7) / 8;
+  if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
+  quantize_kernel<<<(unsigned)blocks, 256, n_levels * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+      weight, w_dtype, ld_w, out_f, in_f, nb, levels, n_levels, codes, ld_codes, static_cast<__half*>(norms), ld_norms);
   PE_CUDA_TRY(cudaGetLastError());
   return PE_OK;
 }

@@ -51,7 +51,6 @@ struct GemmArgs {
   int lut_bytes;  // n_levels (256 for nibble pairs) x 128 B
   int nc;         // code stages
   int* status;
-  unsigned long long* prof;  // developer builds (-DPE_PROFILE): cycles spent in each wait, per CTA
   // grouped launch over a stack of matrices (the experts of a mixture layer): tile list on the device
   const int4* gtiles;        // per tile: (first activation row, rows, first weight row inside the expert, expert)
   const int* n_gtiles;       // number of tiles in the list
@@ -93,20 +92,13 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false if the CTA is aborting (somebody timed out, maybe us).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
-                                          unsigned long long* prof = nullptr) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
-      if (mbar_try(bar, parity)) {
-#ifdef PE_PROFILE
-        if (prof && (threadIdx.x & 31) == 0 && (threadIdx.x < 96))
-          atomicAdd(prof + blockIdx.x * 8 + code, (unsigned long long)(clock64() - t0));
-#endif
-        return true;
-      }
+      if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kTimeoutCycles) {
       *abort_flag = 1;
@@ -252,11 +244,11 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
         const bool two = m0 + 128 < tc.m_end;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int sc = it % p.nc;
-          if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6, p.prof)) goto done_producer;
+          if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6)) goto done_producer;
           mbar_expect_tx(full_c(sc), kCodeStage);
           tma_load_2d(base + c_off + sc * kCodeStage, &cmap, ks * kCodeRow, tc.crow0, full_c(sc));
           const int sx = it % kXStages;
-          if (!mbar_wait(empty_x(sx), ((it / kXStages) & 1) ^ 1, abort_flag, p.status, 1, p.prof)) goto done_producer;
+          if (!mbar_wait(empty_x(sx), ((it / kXStages) & 1) ^ 1, abort_flag, p.status, 1)) goto done_producer;
           mbar_expect_tx(full_x(sx), two ? 2 * kXTileBytes : kXTileBytes);
           tma_load_2d(base + sx * kXStage, &xmap, ks * kStepK, m0, full_x(sx));
           if (two) tma_load_2d(base + sx * kXStage + kXTileBytes, &xmap, ks * kStepK, m0 + 128, full_x(sx));
@@ -273,8 +265,8 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
         const bool two = tc.m0 + 128 < tc.m_end;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int sx = it % kXStages, sw = it % kWStages;
-          if (!mbar_wait(full_x(sx), (it / kXStages) & 1, abort_flag, p.status, 2, p.prof)) goto done_mma;
-          if (!mbar_wait(full_w(sw), (it / kWStages) & 1, abort_flag, p.status, 3, p.prof)) goto done_mma;
+          if (!mbar_wait(full_x(sx), (it / kXStages) & 1, abort_flag, p.status, 2)) goto done_mma;
+          if (!mbar_wait(full_w(sw), (it / kWStages) & 1, abort_flag, p.status, 3)) goto done_mma;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t xa = base + sx * kXStage, wb = base + kWOff + sw * kWTileBytes;
 #pragma unroll
@@ -336,7 +328,7 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
         // this step's codes from the TMA-filled stage, then hand the stage back
         const int sc = it % p.nc;
         {
-          const bool ok = mbar_wait(full_c(sc), (it / p.nc) & 1, abort_flag, p.status, 7, p.prof);
+          const bool ok = mbar_wait(full_c(sc), (it / p.nc) & 1, abort_flag, p.status, 7);
           if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }  // leave together or not at all
         }
         constexpr int CW = PACKED ? 1 : 2;
@@ -348,7 +340,7 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
         if (lane == 0) mbar_arrive(empty_c(sc));
         const int sw = it % kWStages;
         {
-          const bool ok = mbar_wait(empty_w(sw), ((it / kWStages) & 1) ^ 1, abort_flag, p.status, 4, p.prof);
+          const bool ok = mbar_wait(empty_w(sw), ((it / kWStages) & 1) ^ 1, abort_flag, p.status, 4);
           if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }
         }
         uint8_t* wt = sm + kWOff + sw * kWTileBytes + wrow;
@@ -388,7 +380,7 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
       if (dead) break;
       // ---------------- epilogue: TMEM -> registers -> global ----------------
       {
-        const bool ok = mbar_wait(acc_full, tcount & 1, abort_flag, p.status, 5, p.prof);
+        const bool ok = mbar_wait(acc_full, tcount & 1, abort_flag, p.status, 5);
         if (!__all_sync(0xffffffffu, ok)) break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -526,11 +518,6 @@ static EncodeTiledFn encode_fn() {
 
 using namespace pe;
 
-static unsigned long long* g_gemm_prof = nullptr;
-#ifdef PE_PROFILE
-extern "C" void pe_debug_set_gemm_profile_buffer(void* p) { g_gemm_prof = static_cast<unsigned long long*>(p); }
-#endif
-
 // workspace: [status word, padded to 256 B][bf16 activations M x K]
 extern "C" size_t pe_gemm_workspace_bytes(int m, int in_f_padded) {
   if (m < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
@@ -586,7 +573,6 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   a.tiles_m = (m + kTileM - 1) / kTileM;
   a.tiles_n = (out_f + kTileN - 1) / kTileN;
   a.status = status;
-  a.prof = g_gemm_prof;
   a.gtiles = nullptr; a.n_gtiles = nullptr; a.grp_norm_stride = 0;
   a.lut_bytes = (packed ? 256 : n_levels) * 128;
   const int code_row = packed ? 32 : 64;
@@ -693,7 +679,6 @@ extern "C" int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, 
   a.M = rows; a.N = out_f; a.K = in_f_padded;
   a.tiles_m = 1; a.tiles_n = tiles_n;
   a.status = status;
-  a.prof = nullptr;
   a.gtiles = tiles; a.n_gtiles = n_tiles; a.grp_norm_stride = norms_stride;
   a.lut_bytes = (packed ? 256 : n_levels) * 128;
   const int code_row = packed ? 32 : 64;

@@ -23,6 +23,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from .kernels import pack_codes_int4, quant_matmul, retile
+from .packing import unpack_codes_half_block, unpack_codes_q5
 from .utils import get_ct_scaled
 
 try:  # vLLM is optional: the class must stay importable for offline tooling
@@ -35,6 +36,41 @@ except Exception:  # pragma: no cover - exercised only without vLLM
     def set_weight_attrs(weight: torch.Tensor, attrs: Optional[Dict[str, Any]]) -> None:
         for k, v in (attrs or {}).items():
             setattr(weight, k, v)
+
+
+def codes_to_int8(w: torch.Tensor, in_f_padded: int) -> torch.Tensor:
+    """One byte per code from any of the on-disk layouts of a ``<prefix>.codes`` tensor: half-block nibbles
+    (uint8, K/2 columns: quantizer.py:349-351), LSB-first 5-bit packing (uint8, 5K/8 columns: quantizer.py:352-354;
+    the reference unpacks it at load, loader.py:412-417) or int8 as is."""
+    cols = w.shape[-1]
+    if cols == in_f_padded:
+        return w.view(torch.int8) if w.dtype == torch.uint8 else w.to(torch.int8)
+    if cols * 2 == in_f_padded:
+        return unpack_codes_half_block(w.view(torch.uint8) if w.dtype == torch.int8 else w).to(torch.int8)
+    if cols * 8 == in_f_padded * 5:
+        return unpack_codes_q5(w.view(torch.uint8) if w.dtype == torch.int8 else w).to(torch.int8)
+    raise ValueError(f"codes tensor of width {cols} fits none of the layouts of a layer with {in_f_padded} padded input features")
+
+
+def _checkpoint_loader(inner, kind: str, in_f_padded: int):
+    """The ``weight_loader`` vLLM calls for a parameter of a quantized layer: brings the checkpoint tensor into
+    the parameter's layout, then hands it to the layer's own loader (``inner``: vLLM's, which narrows to the
+    rank's shard along ``output_dim`` / ``input_dim`` and places fused q/k/v or gate/up sections), or copies it
+    when the layer has none.  The centroid table is the same for every section of a fused layer."""
+    def loader(param: torch.nn.Parameter, loaded_weight: torch.Tensor, *args: Any, **kwargs: Any) -> None:
+        w = loaded_weight
+        if kind == "codes":
+            w = codes_to_int8(w, in_f_padded)
+        elif kind == "norms":
+            w = w.to(torch.float16)
+        else:  # ct_scaled
+            param.data.copy_(w.to(param.dtype).reshape(param.shape))
+            return
+        if inner is not None:
+            inner(param, w, *args, **kwargs)
+        else:
+            param.data.copy_(w)
+    return loader
 
 
 class PolarQuantLinearMethod(_Base):
@@ -62,14 +98,21 @@ class PolarQuantLinearMethod(_Base):
         nblk = padded // bs
         codes = torch.nn.Parameter(torch.zeros(out_f, padded, dtype=torch.int8), requires_grad=False)
         norms = torch.nn.Parameter(torch.zeros(out_f, nblk, dtype=torch.float16), requires_grad=False)
-        attrs = {"input_dim": 1, "output_dim": 0}
-        if "weight_loader" in extra_weight_attrs:
-            attrs["weight_loader"] = extra_weight_attrs["weight_loader"]
-        set_weight_attrs(codes, attrs)
-        set_weight_attrs(norms, attrs)
+        # vLLM's model loaders look parameters up by checkpoint name (`<prefix>.codes`, `.norms`, `.ct_scaled`) and
+        # call their `weight_loader`: ours unpacks the on-disk code layouts first (the reference unpacks in its own
+        # loader, loader.py:300-445, which vLLM never calls), then vLLM's shards and places the tensor.  The
+        # full (un-sharded) padded width tells the layouts apart whatever the rank's slice is.
+        inner = extra_weight_attrs.get("weight_loader")
+        full_padded = -(-int(input_size) // bs) * bs
+        ct = torch.nn.Parameter(get_ct_scaled(self.bits, bs).clone(), requires_grad=False)
+        for prm, kind in ((codes, "codes"), (norms, "norms"), (ct, "ct_scaled")):
+            attrs = {"weight_loader": _checkpoint_loader(inner if kind != "ct_scaled" else None, kind, full_padded)}
+            if kind != "ct_scaled":
+                attrs.update(input_dim=1, output_dim=0)
+            set_weight_attrs(prm, attrs)
         layer.register_parameter("codes", codes)
         layer.register_parameter("norms", norms)
-        layer.register_buffer("ct_scaled", get_ct_scaled(self.bits, bs).clone())
+        layer.register_parameter("ct_scaled", ct)
         layer.in_f, layer.out_f = in_f, out_f
         layer.in_f_padded, layer.n_blocks = padded, nblk
         layer.bits, layer.block_size, layer.packed = self.bits, bs, False
@@ -77,7 +120,8 @@ class PolarQuantLinearMethod(_Base):
     def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
         """Move the table next to the codes and nibble-pack widths <= 4 (native kernel)."""
         dev = layer.codes.device if hasattr(layer, "codes") else layer.codes_packed.device
-        layer.ct_scaled = layer.ct_scaled.to(dev)
+        if layer.ct_scaled.device != dev:
+            layer.ct_scaled.data = layer.ct_scaled.data.to(dev)
         if layer.bits <= 4 and not getattr(layer, "packed", False):
             packed = pack_codes_int4(layer.codes.data, layer.block_size)
             if "codes" in layer._parameters:

@@ -15,7 +15,7 @@ import torch
 import torch.nn.functional as F
 
 from .fwht import build_hadamard
-from .utils import DEFAULT_BIT_ASSIGNMENT, get_bits_for_layer, get_centroids
+from .utils import DEFAULT_BIT_ASSIGNMENT, get_bits_for_layer, get_centroids, get_ct_scaled
 from .packing import pack_codes_half_block, pack_codes_q5
 
 
@@ -48,6 +48,31 @@ class PolarQuantizer:
             rot = ((unit[lo:hi].reshape(-1, bs) @ had) * root).view(hi - lo, nblk, bs)
             codes[lo:hi] = (rot.unsqueeze(-1) - lv).abs().argmin(dim=-1).to(torch.int8)
         return {"codes": codes.reshape(rows, padded), "norms": norms.half(), "ct_scaled": levels / root}
+
+    def quantize_tensor_gpu(self, weight: torch.Tensor, bits: int) -> Dict[str, torch.Tensor]:
+        """:meth:`quantize_tensor` as one native launch (``pe_quantize``) for a CUDA tensor: same outputs, seconds
+        instead of minutes for a whole model.  Summation orders differ from the CPU path, so codes that sit on a
+        cell boundary can differ (measured: a few per million); checkpoints that must match the reference bit for
+        bit are made with :meth:`quantize_tensor` on the CPU."""
+        from . import _native as nv
+        if self.block_size != 128:
+            raise ValueError("the native quantizer supports block_size 128 only")
+        dev = nv.require_cuda(weight)
+        nv.ensure_init(dev)
+        w = weight.detach()
+        if w.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            w = w.float()
+        if w.stride(1) != 1:
+            w = w.contiguous()
+        rows, cols = w.shape
+        padded = -(-cols // 128) * 128
+        levels = get_centroids(bits).to(dev)
+        codes = torch.empty(rows, padded, dtype=torch.int8, device=dev)
+        norms = torch.empty(rows, padded // 128, dtype=torch.float16, device=dev)
+        nv.check(nv.lib().pe_quantize(w.data_ptr(), nv.dtype_code(w), w.stride(0), rows, cols, padded, levels.data_ptr(),
+                                      levels.numel(), codes.data_ptr(), codes.stride(0), norms.data_ptr(), norms.stride(0),
+                                      nv.stream_ptr(dev)), "pe_quantize")
+        return {"codes": codes, "norms": norms, "ct_scaled": get_ct_scaled(bits, 128).to(dev)}  # table divided on the host, as the CPU path has it
 
     def quantize_state_dict(self, state: Mapping[str, torch.Tensor], pack: bool = True):
         """Quantize every eligible 2-D ``*.weight``; returns (tensors, polar_config dict)

@@ -174,3 +174,77 @@ def test_quantize_save_load_round_trip(tmp_path):
             assert t["in_f"] == w.shape[1] and ck.layer_bits(prefix) == bits
         assert torch.equal(ck.load_layer("model.layers.0.input_layernorm")["weight"], torch.ones(256).half())
         assert "bias" in ck.load_layer("model.layers.0.mlp.down_proj")
+
+
+def _vllm_like_layer_loader(sections, tp_rank, tp_size, row_parallel=False):
+    """What vLLM's linear layers hand to ``create_weights`` as ``weight_loader`` (linear.py: MergedColumnParallel /
+    QKVParallel / RowParallel ``weight_loader``): narrow the loaded tensor to this rank's slice along the
+    parameter's ``output_dim`` (or ``input_dim`` for row-parallel layers) and copy it into the section that
+    ``loaded_shard_id`` names."""
+    def loader(param, loaded_weight, loaded_shard_id=None):
+        data = param.data
+        if row_parallel:
+            dim = param.input_dim
+            size = data.shape[dim]
+            data.copy_(loaded_weight.narrow(dim, tp_rank * size, size))
+            return
+        dim = param.output_dim
+        names = list(sections)
+        if loaded_shard_id is None:
+            offset, size = 0, data.shape[dim]
+        else:
+            i = names.index(loaded_shard_id)
+            size = sections[loaded_shard_id] // tp_size
+            offset = sum(sections[n] for n in names[:i]) // tp_size
+        data.narrow(dim, offset, size).copy_(loaded_weight.narrow(dim, tp_rank * size, size))
+    return loader
+
+
+def test_checkpoint_tensors_through_the_vllm_weight_loader_callbacks():
+    """`<prefix>.codes / .norms / .ct_scaled` as vLLM's model loader delivers them (by parameter name, one call per
+    checkpoint tensor, fused q/k/v sections by shard id, tensor-parallel narrowing by the layer's own loader) land in
+    the parameters `create_weights` registered: nibble-packed and 5-bit-packed codes are unpacked on the way, so the
+    result equals the rank's slice of the quantizer's int8 codes."""
+    from polarengine_vllm_b200.linear_method import PolarQuantLinearMethod
+    from polarengine_vllm_b200.packing import pack_codes_half_block, pack_codes_q5
+    g = torch.Generator().manual_seed(5)
+    hidden, tp = 512, 2
+    # fused q/k/v (Q5, stored 5-bit packed), column parallel
+    sections = {"q": 256, "k": 128, "v": 128}
+    q5 = {n: oracle.quantize_tensor(torch.randn(rows, hidden, generator=g) * 0.02, 5) for n, rows in sections.items()}
+    for rank in range(tp):
+        m = PolarQuantLinearMethod(128, 5)
+        layer = torch.nn.Module()
+        m.create_weights(layer, hidden, [r // tp for r in sections.values()], hidden, sum(sections.values()), torch.float16,
+                         weight_loader=_vllm_like_layer_loader(sections, rank, tp))
+        params = dict(layer.named_parameters())
+        assert set(params) == {"codes", "norms", "ct_scaled"}
+        for n in sections:   # three checkpoint layers feed one fused parameter
+            params["codes"].weight_loader(params["codes"], pack_codes_q5(q5[n]["codes"]), n)
+            params["norms"].weight_loader(params["norms"], q5[n]["norms"], n)
+            params["ct_scaled"].weight_loader(params["ct_scaled"], q5[n]["ct_scaled"], n)
+        want_c = torch.cat([q5[n]["codes"].chunk(tp, 0)[rank] for n in sections])
+        want_n = torch.cat([q5[n]["norms"].chunk(tp, 0)[rank] for n in sections])
+        assert torch.equal(layer.codes.data, want_c) and torch.equal(layer.norms.data, want_n)
+        assert torch.equal(layer.ct_scaled.data, q5["q"]["ct_scaled"])
+    # down projection (Q4, stored nibble-packed), row parallel: whole blocks of K per rank
+    q4 = oracle.quantize_tensor(torch.randn(192, hidden, generator=g) * 0.02, 4)
+    for rank in range(tp):
+        m = PolarQuantLinearMethod(128, 4)
+        layer = torch.nn.Module()
+        m.create_weights(layer, hidden // tp, [192], hidden, 192, torch.float16,
+                         weight_loader=_vllm_like_layer_loader({}, rank, tp, row_parallel=True))
+        layer.codes.weight_loader(layer.codes, pack_codes_half_block(q4["codes"]))
+        layer.norms.weight_loader(layer.norms, q4["norms"])
+        layer.ct_scaled.weight_loader(layer.ct_scaled, q4["ct_scaled"])
+        k0 = rank * hidden // tp
+        assert torch.equal(layer.codes.data, q4["codes"][:, k0:k0 + hidden // tp])
+        assert torch.equal(layer.norms.data, q4["norms"][:, rank * 2:(rank + 1) * 2])
+    # a layer without a framework loader (offline use): plain copies, int8 codes as they are
+    m = PolarQuantLinearMethod(128, 4)
+    layer = torch.nn.Module()
+    m.create_weights(layer, hidden, [192], hidden, 192, torch.float16)
+    layer.codes.weight_loader(layer.codes, q4["codes"])
+    assert torch.equal(layer.codes.data, q4["codes"])
+    with pytest.raises(ValueError):
+        layer.codes.weight_loader(layer.codes, torch.zeros(192, 100, dtype=torch.uint8))
