@@ -50,6 +50,7 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int lut_bytes;  // n_levels (256 for nibble pairs) x 128 B
   int nc;         // code stages
+  int y_tma;      // paired kernel: the output leaves through TMA stores (16-bit output, 16-byte aligned rows)
   int* status;
   // grouped launch over a stack of matrices (the experts of a mixture layer): tile list on the device
   const int4* gtiles;        // per tile: (first activation row, rows, first weight row inside the expert, expert)
@@ -439,6 +440,423 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
   }
 }
 
+// ---- paired form: two CTAs of a cluster share one tensor-core operation (cta_group::2) -----------------
+// A pair owns 512 tokens x 256 weight rows.  Each CTA keeps ITS 128-token halves of the two 256-token
+// accumulators in its own TMEM, stages its own activation tiles and decodes only 128 of the 256 weight
+// rows: the tensor core of each SM reads that half from its own shared memory, so the decode work and the
+// weight-operand traffic per SM are half of the single-CTA form (which is bound by them: with the decode
+// and the activation copies switched off it still ran at three quarters of the dense-GEMM rate).
+// The even CTA of the pair issues the MMAs.  It learns that the odd CTA's stages are full through
+// arrivals on its own barriers (a relay thread for the TMA-filled activation stages, the decode warps
+// directly for the weight stages) and hands stages back with one tcgen05.commit per CTA.
+constexpr int kPairXStages = 4;                      // 32 KB each: this CTA's two 128-token tiles
+constexpr int kPairWStages = 3;                      // 16 KB each: this CTA's 128 weight rows
+constexpr int kPairWTileBytes = 128 * kStepK * 2;
+constexpr int kPairTileM = 512;
+constexpr int kPairGroups = 4;                       // decode warp groups, one K step each
+constexpr int kPairGroupWarps = kDecodeThreads / 32 / kPairGroups;
+constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | ((256u >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared-memory address of the same variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait on a barrier that CTAs of the cluster arrive on
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kTimeoutCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void umma_pair_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0)
+      : "memory");
+}
+// arrival on ONE barrier (of this CTA or, with a mapped address, of the other) once the MMAs issued so far are done
+__device__ __forceinline__ void umma_pair_commit(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+template <bool PACKED>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap cmap,
+                 const __grid_constant__ CUtensorMap ymap) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  // [X stages 4 x 32 KB][W stages 3 x 16 KB][table][code stages nc x (128 rows x 32|64 B)][barriers]
+  constexpr int kXStage = 2 * kXTileBytes;
+  constexpr uint32_t kWOff = kPairXStages * kXStage;
+  constexpr uint32_t kLutOff = kWOff + kPairWStages * kPairWTileBytes;
+  constexpr int kCodeRow = PACKED ? 32 : 64;
+  constexpr int kCodeStage = 128 * kCodeRow;
+  const uint32_t c_off = kLutOff + p.lut_bytes;
+  const uint32_t bar_off = c_off + p.nc * kCodeStage;
+  const uint32_t lut_s = base + kLutOff;
+  uint8_t* lut_g = sm + kLutOff;
+  const uint32_t bars = base + bar_off;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + bar_off + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + bar_off + 196);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  auto full_x = [&](int s) { return bars + 8 * s; };          // 4
+  auto empty_x = [&](int s) { return bars + 32 + 8 * s; };    // 4
+  auto full_w = [&](int s) { return bars + 64 + 8 * s; };     // 3 (used in the even CTA)
+  auto empty_w = [&](int s) { return bars + 88 + 8 * s; };    // 3
+  auto full_c = [&](int s) { return bars + 112 + 8 * s; };    // up to 4
+  auto empty_c = [&](int s) { return bars + 144 + 8 * s; };   // up to 4
+  const uint32_t acc_full = bars + 176;
+  const uint32_t acc_empty = bars + 184;  // used in the even CTA: both CTAs have read the accumulators of a tile
+  const uint32_t stg_free = bars + 208;   // the output staging (inside the weight stages) has been read by the TMA stores
+
+  if (tid == 0) {
+    // activation stage of the even CTA: its own copy and the relayed arrival of the odd CTA's
+    for (int s = 0; s < kPairXStages; ++s) { mbar_init(full_x(s), leader ? 2 : 1); mbar_init(empty_x(s), 1); }
+    // weight stage: the decode warps of both CTAs
+    for (int s = 0; s < kPairWStages; ++s) { mbar_init(full_w(s), 2 * kPairGroupWarps); mbar_init(empty_w(s), 1); }
+    for (int s = 0; s < p.nc; ++s) { mbar_init(full_c(s), 1); mbar_init(empty_c(s), kPairGroupWarps); }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 2 * (kDecodeThreads / 32));  // every decode warp of both CTAs, once per tile
+    mbar_init(stg_free, kDecodeThreads / 32);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp >= 2) {
+    const int d = tid - 64;
+    for (int e = d >> 5; e < (PACKED ? 256 : p.n_levels); e += kDecodeThreads / 32) {
+      uint32_t v;
+      if (PACKED) {
+        const int lo = e & 15, hi = e >> 4;
+        v = pack_bf16(lo < p.n_levels ? p.ct[lo] : 0.f, hi < p.n_levels ? p.ct[hi] : 0.f);
+      } else {
+        v = pack_bf16(p.ct[e], p.ct[e]);
+      }
+      *reinterpret_cast<uint32_t*>(lut_g + e * 128 + lane * 4) = v;
+    }
+  }
+  if (warp == 1) {  // one warp of EACH CTA of the pair allocates (all 512 columns) and later frees
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs exist before anybody arrives on them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  const int ksteps = p.K / kStepK;
+  const int n_tiles = p.tiles_m * p.tiles_n;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: this CTA's activation tiles and code rows ----------------
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
+        const int m0 = (tile % p.tiles_m) * kPairTileM, n0 = (tile / p.tiles_m) * kTileN;
+        const bool two = m0 + 256 < p.M;
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int sc = it % p.nc;
+          if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6)) goto done_producer;
+          mbar_expect_tx(full_c(sc), kCodeStage);
+          tma_load_2d(base + c_off + sc * kCodeStage, &cmap, ks * kCodeRow, n0 + (int)rank * 128, full_c(sc));
+          const int sx = it % kPairXStages;
+          if (!mbar_wait(empty_x(sx), ((it / kPairXStages) & 1) ^ 1, abort_flag, p.status, 1)) goto done_producer;
+          mbar_expect_tx(full_x(sx), two ? 2 * kXTileBytes : kXTileBytes);
+          tma_load_2d(base + sx * kXStage, &xmap, ks * kStepK, m0 + (int)rank * 128, full_x(sx));
+          if (two) tma_load_2d(base + sx * kXStage + kXTileBytes, &xmap, ks * kStepK, m0 + 256 + (int)rank * 128, full_x(sx));
+        }
+      }
+    done_producer:;
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ---------------- MMA issuer (even CTA) ----------------
+      const uint32_t peer = map_to_cta(bars, 1) - bars;  // same barrier, odd CTA
+      const uint32_t peer_acc_full = acc_full + peer;
+      int it = 0, tcount = 0;
+      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
+        const int m0 = (tile % p.tiles_m) * kPairTileM;
+        const bool two = m0 + 256 < p.M;
+        if (tcount > 0 && !mbar_wait_cluster(acc_empty, (tcount - 1) & 1, abort_flag, p.status, 9)) goto done_mma;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int sx = it % kPairXStages, sw = it % kPairWStages;
+          if (!mbar_wait_cluster(full_x(sx), (it / kPairXStages) & 1, abort_flag, p.status, 2)) goto done_mma;
+          if (!mbar_wait_cluster(full_w(sw), (it / kPairWStages) & 1, abort_flag, p.status, 3)) goto done_mma;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t xa = base + sx * kXStage, wb = base + kWOff + sw * kPairWTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < kStepK / 16; ++kk) {
+            const uint64_t db = smem_desc_sw128(wb + kk * 32);
+            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+            umma_pair_bf16(tmem, smem_desc_sw128(xa + kk * 32), db, kIdescPair, acc);
+            if (two) umma_pair_bf16(tmem + 256, smem_desc_sw128(xa + kXTileBytes + kk * 32), db, kIdescPair, acc);
+          }
+          umma_pair_commit(empty_x(sx));
+          umma_pair_commit(empty_x(sx) + peer);
+          umma_pair_commit(empty_w(sw));
+          umma_pair_commit(empty_w(sw) + peer);
+        }
+        umma_pair_commit(acc_full);
+        umma_pair_commit(peer_acc_full);
+      }
+    done_mma:;
+    } else if (lane == 0) {
+      // ---------------- relay (odd CTA): "my activation stage is full" to the even CTA ----------------
+      const uint32_t lead = map_to_cta(bars, 0) - bars;  // same barrier, even CTA
+      int it = 0;
+      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int sx = it % kPairXStages;
+          if (!mbar_wait(full_x(sx), (it / kPairXStages) & 1, abort_flag, p.status, 8)) goto done_relay;
+          mbar_arrive_remote(full_x(sx) + lead);
+        }
+      }
+    done_relay:;
+    }
+  } else {
+    // ---------------- decode + epilogue warps ----------------
+    // A warp's trip through one K step is a chain of barrier round trips (codes full, weight stage empty,
+    // proxy fence, arrival) that costs more than the MMAs of the step, however little it decodes.  So the 16
+    // warps form four groups and group g takes the steps with it % 4 == g, a whole 128-row stage each
+    // (thread = one weight row, all 64 K elements): four steps are in the decode pipeline at a time.
+    const int d = tid - 64;
+    const int r = d & 127, g = d >> 7;
+    const uint32_t lane_base = lut_s + lane * 4;
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
+    const int half = grp & 1;
+    const int chalf = grp >> 1;
+    const uint32_t wrow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+    const int sw7 = r & 7;
+    const uint32_t lead = map_to_cta(bars, 0) - bars;
+    int it = 0, tcount = 0;
+    for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
+      const int m0 = (tile % p.tiles_m) * kPairTileM, n0 = (tile / p.tiles_m) * kTileN;
+      const bool two = m0 + 256 < p.M;
+      int row = n0 + (int)rank * 128 + r;
+      const bool row_ok = row < p.N;
+      if (!row_ok) row = p.N - 1;
+      const unsigned short* nrow = reinterpret_cast<const unsigned short*>(p.norms + (int64_t)row * p.ld_norms);
+      bool dead = false;
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        if ((it & (kPairGroups - 1)) != g) continue;  // warp-uniform
+        const float nf = row_ok ? __half2float(__ushort_as_half(__ldg(nrow + (ks >> 1)))) : 0.f;  // in flight across the waits
+        const int sc = it % p.nc;
+        {
+          const bool ok = mbar_wait(full_c(sc), (it / p.nc) & 1, abort_flag, p.status, 7);
+          if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }
+        }
+        constexpr int CW = PACKED ? 2 : 4;  // 16-byte pieces of this row's codes
+        uint4 c[CW];
+        const uint8_t* csrc = sm + c_off + sc * kCodeStage + r * kCodeRow;
+#pragma unroll
+        for (int i = 0; i < CW; ++i) c[i] = *reinterpret_cast<const uint4*>(csrc + 16 * i);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_c(sc));
+        const uint32_t n2 = pack_bf16(nf, nf);
+        const int sw = it % kPairWStages;
+        {
+          const bool ok = mbar_wait(empty_w(sw), ((it / kPairWStages) & 1) ^ 1, abort_flag, p.status, 4);
+          if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }
+        }
+        uint8_t* wt = sm + kWOff + sw * kPairWTileBytes + wrow;
+#pragma unroll
+        for (int i = 0; i < CW; ++i) {
+          const uint32_t wq[4] = {c[i].x, c[i].y, c[i].z, c[i].w};
+          if (PACKED) {  // one code byte -> two adjacent K elements; word j of piece i -> chunk 4 i + j
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w = wq[j];
+              uint4 o;
+              o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
+              o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
+              o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
+              o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+              *reinterpret_cast<uint4*>(wt + (((4 * i + j) ^ sw7) << 4)) = o;
+            }
+          } else {       // one code byte -> one K element; words 2j, 2j+1 of piece i -> chunk 2 i + j
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const uint32_t wa = wq[2 * j], wb = wq[2 * j + 1];
+              uint4 o;
+              o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
+              o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
+              o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
+              o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
+              *reinterpret_cast<uint4*>(wt + (((2 * i + j) ^ sw7) << 4)) = o;
+            }
+          }
+        }
+        // visible to the tensor core of this SM, then one arrival per warp on the even CTA's barrier
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(full_w(sw));
+          else mbar_arrive_remote(full_w(sw) + lead);
+        }
+      }
+      if (dead) break;
+      // ---------------- epilogue: this CTA's 128 token rows of both accumulators ----------------
+      {
+        const bool ok = mbar_wait_cluster(acc_full, tcount & 1, abort_flag, p.status, 5);
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (p.y_tma) {
+        // 16-bit output: every warp stages its 32 rows x 32 columns (2 KB, 64-byte swizzle) in its own piece of the
+        // weight stages -- idle now: all MMAs are done and no warp decodes before the staging barrier below -- and one
+        // lane sends it off as a TMA store, which writes whole 64-byte row pieces and clips at the matrix edges.
+        // Per-lane 16-byte stores straight to global memory, 32 rows per instruction, took a quarter of the kernel.
+        const uint32_t stg = base + kWOff + (uint32_t)(warp - 2) * 2048u + (uint32_t)lane * 64u;
+        const int swz = (lane >> 1) & 3;
+        if (half == 0 || two) {
+          const int mrow0 = m0 + half * 256 + (int)rank * 128 + q * 32;
+          const uint32_t trow = tmem + half * 256 + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+          for (int cc = chalf * 4; cc < chalf * 4 + 4; ++cc) {
+            uint32_t rr[32];
+            tmem_ld32(trow + cc * 32, rr);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const int nb0 = n0 + cc * 32;
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float a = __uint_as_float(rr[2 * j]), b = __uint_as_float(rr[2 * j + 1]);
+              if (p.bias) {
+                if (nb0 + 2 * j < p.N) a += __half2float(p.bias[nb0 + 2 * j]);
+                if (nb0 + 2 * j + 1 < p.N) b += __half2float(p.bias[nb0 + 2 * j + 1]);
+              }
+              o[j] = p.y_dtype == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
+            }
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous store has read the buffer
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stg + (uint32_t)((j ^ swz) << 4)), "r"(o[4 * j]),
+                           "r"(o[4 * j + 1]), "r"(o[4 * j + 2]), "r"(o[4 * j + 3]) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && mrow0 < p.M && nb0 < p.N) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&ymap), "r"(stg), "r"(nb0), "r"(mrow0) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        }
+      } else {
+      if (half == 0 || two) {
+        const int m = m0 + half * 256 + (int)rank * 128 + q * 32 + lane;
+        const uint32_t trow = tmem + half * 256 + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+        for (int cc = chalf * 4; cc < chalf * 4 + 4; ++cc) {
+          uint32_t rr[32];
+          tmem_ld32(trow + cc * 32, rr);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int nb0 = n0 + cc * 32;
+          if (m < p.M && nb0 < p.N) {
+            const bool full = nb0 + 32 <= p.N && (p.ld_y % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
+            if (full && p.y_dtype != PE_F32) {
+              uint32_t o[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float a = __uint_as_float(rr[2 * j]), b = __uint_as_float(rr[2 * j + 1]);
+                if (p.bias) { a += __half2float(p.bias[nb0 + 2 * j]); b += __half2float(p.bias[nb0 + 2 * j + 1]); }
+                o[j] = p.y_dtype == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.y) + (int64_t)m * p.ld_y + nb0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (nb0 + j < p.N) {
+                  float a = __uint_as_float(rr[j]);
+                  if (p.bias) a += __half2float(p.bias[nb0 + j]);
+                  store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + nb0 + j, a);
+                }
+              }
+            }
+          }
+        }
+      }
+      }
+      // the next tile's first MMA overwrites the accumulators: it waits for every decode warp of the pair
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(acc_empty);
+        else mbar_arrive_remote(acc_empty + lead);
+      }
+      if (p.y_tma) {
+        // no warp writes a weight stage of the next tile before every warp's staging has been read
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          mbar_arrive(stg_free);
+        }
+        const bool ok = mbar_wait(stg_free, tcount & 1, abort_flag, p.status, 10);
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores complete before the CTA leaves
+  }
+
+  // ---------------- common exit: nobody leaves while the other CTA may still signal or read here ----------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag && tid == 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+  }
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+  }
+}
+
 // Activation preparation: (pad + FWHT for raw input), bf16, kernel K order.
 // One warp per (row, 128-block).
 // Grouped launches: row m of the prepared matrix is row x_rows[m] of x (a gather by token id), and only the first
@@ -573,7 +991,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   a.tiles_m = (m + kTileM - 1) / kTileM;
   a.tiles_n = (out_f + kTileN - 1) / kTileN;
   a.status = status;
-  a.gtiles = nullptr; a.n_gtiles = nullptr; a.grp_norm_stride = 0;
+  a.gtiles = nullptr; a.n_gtiles = nullptr; a.grp_norm_stride = 0; a.y_tma = 0;
   a.lut_bytes = (packed ? 256 : n_levels) * 128;
   const int code_row = packed ? 32 : 64;
   const int code_stage = kTileN * code_row;
@@ -591,6 +1009,55 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return PE_ERR_CUDA;
 
+  if (m > 256 && sms >= 2) {
+    // more than one 256-token tile: pairs of CTAs, each decoding half of the weight tile
+    a.tiles_m = (m + kPairTileM - 1) / kPairTileM;
+    const int pair_code_stage = 128 * code_row;
+    const unsigned pair_fixed = kPairXStages * 2 * kXTileBytes + kPairWStages * kPairWTileBytes + a.lut_bytes + 256 + 1024;
+    a.nc = 4;
+    while (a.nc > 2 && pair_fixed + a.nc * pair_code_stage > 232448u) --a.nc;
+    const unsigned pair_smem = pair_fixed + a.nc * pair_code_stage;
+    if (pair_smem <= 232448u) {
+      CUtensorMap pmap;
+      const cuuint32_t pbox[2] = {(cuuint32_t)code_row, 128};
+      if (enc(&pmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(codes), cdims, cstrides, pbox, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return PE_ERR_CUDA;
+      CUtensorMap ymap = pmap;  // a valid map also when the kernel does not use it
+      a.y_tma = (y_dtype != PE_F32 && ld_y % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) ? 1 : 0;
+      if (a.y_tma) {
+        const cuuint64_t ydims[2] = {(cuuint64_t)out_f, (cuuint64_t)m};
+        const cuuint64_t ystrides[1] = {(cuuint64_t)ld_y * 2};
+        const cuuint32_t ybox[2] = {32, 32};
+        if (enc(&ymap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, y, ydims, ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+          return PE_ERR_CUDA;
+      }
+      const int pair_tiles = a.tiles_m * a.tiles_n;
+      const int pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * pairs);
+      cfg.blockDim = dim3(kGemmThreads);
+      cfg.dynamicSmemBytes = pair_smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      if (packed) {
+        PE_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        PE_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<true>, a, map, pmap, ymap));
+      } else {
+        PE_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        PE_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<false>, a, map, pmap, ymap));
+      }
+      return PE_OK;
+    }
+    a.tiles_m = (m + kTileM - 1) / kTileM;
+    a.nc = (fixed + 3 * code_stage <= 232448u) ? 3 : 2;
+  }
   const int tiles = a.tiles_m * a.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
   if (packed) {
@@ -679,7 +1146,7 @@ extern "C" int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, 
   a.M = rows; a.N = out_f; a.K = in_f_padded;
   a.tiles_m = 1; a.tiles_n = tiles_n;
   a.status = status;
-  a.gtiles = tiles; a.n_gtiles = n_tiles; a.grp_norm_stride = norms_stride;
+  a.gtiles = tiles; a.n_gtiles = n_tiles; a.grp_norm_stride = norms_stride; a.y_tma = 0;
   a.lut_bytes = (packed ? 256 : n_levels) * 128;
   const int code_row = packed ? 32 : 64;
   const int code_stage = kTileN * code_row;

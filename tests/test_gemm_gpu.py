@@ -73,6 +73,24 @@ def test_gemm_ragged_in_features_bias_and_dtypes():
             assert y.dtype == ydt and max_rel(y, ref) <= TOL
 
 
+@pytest.mark.parametrize("m,n", [(257, 256), (700, 1000), (513, 2688), (1100, 130)])
+def test_gemm_paired_ctas_ragged_edges_bias_and_dtypes(m, n):
+    """More than 256 tokens run on pairs of CTAs (512-token tiles, each CTA decoding half of the weight tile)
+    with the output leaving through clipped TMA stores: token and weight-row counts off every tile, box and
+    vector boundary, padded K, bias, all output types (fp32 output takes the direct-store path)."""
+    k, in_f, bits = 1920, 1856, 4
+    codes, norms, cts = rand_layer(n, k, bits, seed=m + n)
+    bias = rand_x(1, n, seed=4).reshape(n)
+    x = rand_x(m, in_f, seed=5, dtype=torch.bfloat16)
+    ref = oracle.linear_dequant(x, codes, norms, cts, in_f=in_f) + bias.float()
+    for ydt in (torch.float16, torch.bfloat16, torch.float32):
+        y = run_gemm(codes, norms, cts, x, bits, out_dtype=ydt, bias=bias, in_f=in_f)
+        assert y.dtype == ydt and y.shape == (m, n) and max_rel(y, ref) <= TOL
+    y5 = run_gemm(*rand_layer(n, k, 5, seed=n)[:3], x, 5, in_f=in_f)
+    c5, n5, t5 = rand_layer(n, k, 5, seed=n)
+    assert max_rel(y5, oracle.linear_dequant(x, c5, n5, t5, in_f=in_f)) <= TOL
+
+
 def test_gemm_rotated_input_and_reference_signature():
     """polar_gemm / polar_gemm_packed of the reference take fp32 x_transformed
     (polar_gemm.py:312-418) and agree with the decode kernel (reference self-test
