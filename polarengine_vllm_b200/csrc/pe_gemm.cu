@@ -337,6 +337,14 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
         const uint8_t* csrc = sm + c_off + sc * kCodeStage + r * kCodeRow + kh * (kCodeRow / 2);
 #pragma unroll
         for (int i = 0; i < CW; ++i) c[i] = *reinterpret_cast<const uint4*>(csrc + 16 * i);
+        // the stage goes back only after the loads have delivered: an arrival issued straight behind
+        // (bank-conflicted, multi-pass) loads can overtake them, and the refill then lands on unread rows
+        {
+          uint32_t seen = 0;
+#pragma unroll
+          for (int i = 0; i < CW; ++i) seen |= c[i].x | c[i].y | c[i].z | c[i].w;
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(bars + 224), "r"(seen) : "memory");
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_c(sc));
         const int sw = it % kWStages;
@@ -449,11 +457,17 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
 // The even CTA of the pair issues the MMAs.  It learns that the odd CTA's stages are full through
 // arrivals on its own barriers (a relay thread for the TMA-filled activation stages, the decode warps
 // directly for the weight stages) and hands stages back with one tcgen05.commit per CTA.
-constexpr int kPairXStages = 4;                      // 32 KB each: this CTA's two 128-token tiles
-constexpr int kPairWStages = 3;                      // 16 KB each: this CTA's 128 weight rows
+constexpr int kPairWStages = 4;                      // 16 KB each: this CTA's 128 weight rows; one per decode group
+constexpr int kPairCodeStages = 4;                   // one per decode group
+constexpr int kPairLutStride = 64;                   // nibble layers: 16 copies of the 256-entry pair table (16 KB)
 constexpr int kPairWTileBytes = 128 * kStepK * 2;
 constexpr int kPairTileM = 512;
-constexpr int kPairGroups = 4;                       // decode warp groups, one K step each
+constexpr int kPairThreads = kGemmThreads + 32;     // 19 warps: activation TMA, MMA, 16 decode/epilogue, code TMA
+constexpr int kPairGroups = 4;                       // decode warp groups, one K step each.  A group owns weight stage g and
+                                                     // code stage g: a parity wait is only sound while the waiter is
+                                                     // less than two phases ahead of the barrier, which sharing a stage
+                                                     // between groups does not guarantee
+static_assert(kPairWStages == kPairGroups && kPairCodeStages == kPairGroups, "one stage of each ring per decode group");
 constexpr int kPairGroupWarps = kDecodeThreads / 32 / kPairGroups;
 constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | ((256u >> 4) << 24);
 
@@ -514,15 +528,27 @@ __device__ __forceinline__ void umma_pair_commit(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+// table entry address: lut + byte * STRIDE + copy * 4
+template <int BYTE, int STRIDE>
+__device__ __forceinline__ uint32_t glut_s(uint32_t word, uint32_t lane_base) {
+  uint32_t b, v;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(b) : "r"(word), "r"(0), "n"(0x4440 | BYTE));
+  const uint32_t addr = b * (uint32_t)STRIDE + lane_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
 template <bool PACKED>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap cmap,
                  const __grid_constant__ CUtensorMap ymap) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
-  // [X stages 4 x 32 KB][W stages 3 x 16 KB][table][code stages nc x (128 rows x 32|64 B)][barriers]
+  // [X stages 4|3 x 32 KB][W stages 4 x 16 KB][table][code stages 4 x (128 rows x 32|64 B)][barriers]
+  constexpr int kPairXStages = PACKED ? 4 : 3;  // byte codes need twice the code stages' room
+  constexpr int kLutStride = PACKED ? kPairLutStride : 128;
   constexpr int kXStage = 2 * kXTileBytes;
   constexpr uint32_t kWOff = kPairXStages * kXStage;
   constexpr uint32_t kLutOff = kWOff + kPairWStages * kPairWTileBytes;
@@ -533,20 +559,20 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
   const uint32_t lut_s = base + kLutOff;
   uint8_t* lut_g = sm + kLutOff;
   const uint32_t bars = base + bar_off;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + bar_off + 192);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + bar_off + 196);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + bar_off + 216);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + bar_off + 220);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  auto full_x = [&](int s) { return bars + 8 * s; };          // 4
-  auto empty_x = [&](int s) { return bars + 32 + 8 * s; };    // 4
-  auto full_w = [&](int s) { return bars + 64 + 8 * s; };     // 3 (used in the even CTA)
-  auto empty_w = [&](int s) { return bars + 88 + 8 * s; };    // 3
-  auto full_c = [&](int s) { return bars + 112 + 8 * s; };    // up to 4
-  auto empty_c = [&](int s) { return bars + 144 + 8 * s; };   // up to 4
-  const uint32_t acc_full = bars + 176;
-  const uint32_t acc_empty = bars + 184;  // used in the even CTA: both CTAs have read the accumulators of a tile
+  auto full_x = [&](int s) { return bars + 8 * s; };          // up to 4
+  auto empty_x = [&](int s) { return bars + 32 + 8 * s; };    // up to 4
+  auto full_w = [&](int s) { return bars + 64 + 8 * s; };     // 4 (used in the even CTA)
+  auto empty_w = [&](int s) { return bars + 96 + 8 * s; };    // 4
+  auto full_c = [&](int s) { return bars + 128 + 8 * s; };    // 4
+  auto empty_c = [&](int s) { return bars + 160 + 8 * s; };   // 4
+  const uint32_t acc_full = bars + 192;
+  const uint32_t acc_empty = bars + 200;  // used in the even CTA: both CTAs have read the accumulators of a tile
   const uint32_t stg_free = bars + 208;   // the output staging (inside the weight stages) has been read by the TMA stores
 
   if (tid == 0) {
@@ -561,7 +587,7 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp >= 2) {
+  if (warp >= 2 && warp < 18) {
     const int d = tid - 64;
     for (int e = d >> 5; e < (PACKED ? 256 : p.n_levels); e += kDecodeThreads / 32) {
       uint32_t v;
@@ -571,7 +597,7 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
       } else {
         v = pack_bf16(p.ct[e], p.ct[e]);
       }
-      *reinterpret_cast<uint32_t*>(lut_g + e * 128 + lane * 4) = v;
+      if (lane * 4 < kLutStride) *reinterpret_cast<uint32_t*>(lut_g + e * kLutStride + lane * 4) = v;
     }
   }
   if (warp == 1) {  // one warp of EACH CTA of the pair allocates (all 512 columns) and later frees
@@ -589,17 +615,13 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
   if (warp == 0) {
-    // ---------------- TMA producer: this CTA's activation tiles and code rows ----------------
+    // ---------------- TMA producer: this CTA's activation tiles ----------------
     if (lane == 0) {
       int it = 0;
       for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
-        const int m0 = (tile % p.tiles_m) * kPairTileM, n0 = (tile / p.tiles_m) * kTileN;
+        const int m0 = (tile % p.tiles_m) * kPairTileM;
         const bool two = m0 + 256 < p.M;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
-          const int sc = it % p.nc;
-          if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6)) goto done_producer;
-          mbar_expect_tx(full_c(sc), kCodeStage);
-          tma_load_2d(base + c_off + sc * kCodeStage, &cmap, ks * kCodeRow, n0 + (int)rank * 128, full_c(sc));
           const int sx = it % kPairXStages;
           if (!mbar_wait(empty_x(sx), ((it / kPairXStages) & 1) ^ 1, abort_flag, p.status, 1)) goto done_producer;
           mbar_expect_tx(full_x(sx), two ? 2 * kXTileBytes : kXTileBytes);
@@ -608,6 +630,21 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
         }
       }
     done_producer:;
+    }
+  } else if (warp == 18) {
+    // ---------------- TMA producer: this CTA's code rows (a thread of its own: it runs ahead of the activations) ----------------
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
+        const int n0 = (tile / p.tiles_m) * kTileN;
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int sc = it % p.nc;
+          if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6)) goto done_codes;
+          mbar_expect_tx(full_c(sc), kCodeStage);
+          tma_load_2d(base + c_off + sc * kCodeStage, &cmap, ks * kCodeRow, n0 + (int)rank * 128, full_c(sc));
+        }
+      }
+    done_codes:;
     }
   } else if (warp == 1) {
     if (lane == 0 && leader) {
@@ -644,6 +681,7 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     done_mma:;
     } else if (lane == 0) {
       // ---------------- relay (odd CTA): "my activation stage is full" to the even CTA ----------------
+      // (a pair-wide TMA load counted on the even CTA's barrier would save this hop; it stalled when tried)
       const uint32_t lead = map_to_cta(bars, 0) - bars;  // same barrier, even CTA
       int it = 0;
       for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
@@ -663,7 +701,9 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     // (thread = one weight row, all 64 K elements): four steps are in the decode pipeline at a time.
     const int d = tid - 64;
     const int r = d & 127, g = d >> 7;
-    const uint32_t lane_base = lut_s + lane * 4;
+    // nibble layers: lanes l and l + 16 share a copy of the table (a two-way bank conflict when their
+    // entries differ but have the same parity; the decode warps have the time)
+    const uint32_t lane_base = lut_s + (uint32_t)(lane * 4 & (kLutStride - 1));
     const int q = warp & 3;
     const int grp = (warp - 2) >> 2;
     const int half = grp & 1;
@@ -693,6 +733,15 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
         const uint8_t* csrc = sm + c_off + sc * kCodeStage + r * kCodeRow;
 #pragma unroll
         for (int i = 0; i < CW; ++i) c[i] = *reinterpret_cast<const uint4*>(csrc + 16 * i);
+        // The stage is handed back (and refilled at once by the code producer) only after the loads have
+        // DELIVERED: a store that consumes every loaded register sits between them and the arrival.  Without
+        // it rows of byte codes (64-byte row pitch, four-way bank conflicts) were overwritten before they were read.
+        {
+          uint32_t seen = 0;
+#pragma unroll
+          for (int i = 0; i < CW; ++i) seen |= c[i].x | c[i].y | c[i].z | c[i].w;
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(bars + 224), "r"(seen) : "memory");
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_c(sc));
         const uint32_t n2 = pack_bf16(nf, nf);
@@ -710,10 +759,10 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
             for (int j = 0; j < 4; ++j) {
               const uint32_t w = wq[j];
               uint4 o;
-              o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
-              o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
-              o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
-              o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+              o.x = bf16x2_mul(glut_s<0, kLutStride>(w, lane_base), n2);
+              o.y = bf16x2_mul(glut_s<1, kLutStride>(w, lane_base), n2);
+              o.z = bf16x2_mul(glut_s<2, kLutStride>(w, lane_base), n2);
+              o.w = bf16x2_mul(glut_s<3, kLutStride>(w, lane_base), n2);
               *reinterpret_cast<uint4*>(wt + (((4 * i + j) ^ sw7) << 4)) = o;
             }
           } else {       // one code byte -> one K element; words 2j, 2j+1 of piece i -> chunk 2 i + j
@@ -721,10 +770,10 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
             for (int j = 0; j < 2; ++j) {
               const uint32_t wa = wq[2 * j], wb = wq[2 * j + 1];
               uint4 o;
-              o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
-              o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
-              o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
-              o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
+              o.x = bf16x2_mul(lo_hi16(glut_s<0, kLutStride>(wa, lane_base), glut_s<1, kLutStride>(wa, lane_base)), n2);
+              o.y = bf16x2_mul(lo_hi16(glut_s<2, kLutStride>(wa, lane_base), glut_s<3, kLutStride>(wa, lane_base)), n2);
+              o.z = bf16x2_mul(lo_hi16(glut_s<0, kLutStride>(wb, lane_base), glut_s<1, kLutStride>(wb, lane_base)), n2);
+              o.w = bf16x2_mul(lo_hi16(glut_s<2, kLutStride>(wb, lane_base), glut_s<3, kLutStride>(wb, lane_base)), n2);
               *reinterpret_cast<uint4*>(wt + (((2 * i + j) ^ sw7) << 4)) = o;
             }
           }
@@ -1013,9 +1062,9 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
     // more than one 256-token tile: pairs of CTAs, each decoding half of the weight tile
     a.tiles_m = (m + kPairTileM - 1) / kPairTileM;
     const int pair_code_stage = 128 * code_row;
-    const unsigned pair_fixed = kPairXStages * 2 * kXTileBytes + kPairWStages * kPairWTileBytes + a.lut_bytes + 256 + 1024;
-    a.nc = 4;
-    while (a.nc > 2 && pair_fixed + a.nc * pair_code_stage > 232448u) --a.nc;
+    if (packed) a.lut_bytes = 256 * kPairLutStride;
+    const unsigned pair_fixed = (packed ? 4 : 3) * 2 * kXTileBytes + kPairWStages * kPairWTileBytes + a.lut_bytes + 256 + 1024;
+    a.nc = kPairCodeStages;
     const unsigned pair_smem = pair_fixed + a.nc * pair_code_stage;
     if (pair_smem <= 232448u) {
       CUtensorMap pmap;
@@ -1038,7 +1087,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
       const int pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * pairs);
-      cfg.blockDim = dim3(kGemmThreads);
+      cfg.blockDim = dim3(kPairThreads);
       cfg.dynamicSmemBytes = pair_smem;
       cfg.stream = st;
       cudaLaunchAttribute attr[1];
@@ -1057,6 +1106,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
     }
     a.tiles_m = (m + kTileM - 1) / kTileM;
     a.nc = (fixed + 3 * code_stage <= 232448u) ? 3 : 2;
+    a.lut_bytes = (packed ? 256 : n_levels) * 128;
   }
   const int tiles = a.tiles_m * a.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
