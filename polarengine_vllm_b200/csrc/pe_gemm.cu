@@ -38,6 +38,9 @@ constexpr int kXTileBytes = 128 * kStepK * 2;        // 16 KB
 constexpr int kWTileBytes = kTileN * kStepK * 2;     // 32 KB
 constexpr int kGemmThreads = 576;                    // 18 warps: TMA, MMA, 16 decode/epilogue
 constexpr int kDecodeThreads = 512;
+constexpr int kGroups = 2;                          // decode warp groups of the single-CTA kernel, one K step each
+constexpr int kGroupWarps = kDecodeThreads / 32 / kGroups;
+static_assert(kWStages == kGroups, "a decode group owns its weight stage");
 constexpr long long kTimeoutCycles = 1ll << 31;
 
 struct GemmArgs {
@@ -200,12 +203,14 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
   auto full_c = [&](int s) { return bars + 80 + 8 * s; };    // up to 4
   auto empty_c = [&](int s) { return bars + 112 + 8 * s; };  // up to 4
   const uint32_t acc_full = bars + 144;
+  const uint32_t acc_empty = bars + 152;  // every decode warp has read the accumulators of a tile
 
   if (tid == 0) {
     for (int s = 0; s < kXStages; ++s) { mbar_init(full_x(s), 1); mbar_init(empty_x(s), 1); }
-    for (int s = 0; s < kWStages; ++s) { mbar_init(full_w(s), kDecodeThreads / 32); mbar_init(empty_w(s), 1); }
-    for (int s = 0; s < p.nc; ++s) { mbar_init(full_c(s), 1); mbar_init(empty_c(s), kDecodeThreads / 32); }
+    for (int s = 0; s < kWStages; ++s) { mbar_init(full_w(s), kGroupWarps); mbar_init(empty_w(s), 1); }
+    for (int s = 0; s < p.nc; ++s) { mbar_init(full_c(s), 1); mbar_init(empty_c(s), kGroupWarps); }
     mbar_init(acc_full, 1);
+    mbar_init(acc_empty, kDecodeThreads / 32);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -260,10 +265,12 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      int it = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
+      int it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
         const TileCoord tc = tile_coord(p, tile);
         const bool two = tc.m0 + 128 < tc.m_end;
+        if (tcount > 0 && !mbar_wait(acc_empty, (tcount - 1) & 1, abort_flag, p.status, 9)) goto done_mma;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int sx = it % kXStages, sw = it % kWStages;
           if (!mbar_wait(full_x(sx), (it / kXStages) & 1, abort_flag, p.status, 2)) goto done_mma;
@@ -286,16 +293,18 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
     }
   } else {
     // ---------------- decode + epilogue warps ----------------
-    // thread d: weight row d % 256 of the tile, K half d / 256 of every 64-wide step
-    // (four 16-byte chunks of the swizzled weight tile).
+    // A warp's trip through one K step is a chain of barrier round trips (codes full, weight stage empty, proxy
+    // fence, arrival) that costs more than the step's MMAs however little it decodes.  So the 16 warps form two
+    // groups; group g takes the steps with it % 2 == g, a whole 256-row stage each (thread = one weight row, all 64
+    // K elements), and owns weight stage g and code stage g (a parity wait is only sound while the waiter is less
+    // than two phases ahead of its barrier, which stages shared between groups would not guarantee).
     const int d = tid - 64;
-    const int r = d & 255, kh = d >> 8;
+    const int r = d & 255, g = d >> 8;
     const uint32_t lane_base = lut_s + lane * 4;
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
     const int grp = (warp - 2) >> 2;        // 0..3
     const int half = grp & 1;               // accumulator (token half) this warp drains
     const int chalf = grp >> 1;             // which 128 of its 256 columns
-    const bool norm_vec = (p.ld_norms % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.norms) & 15) == 0);
     const uint32_t wrow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
     const int sw7 = r & 7;
     int it = 0, tcount = 0;
@@ -306,35 +315,20 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
       int row = n0 + r;
       const bool row_ok = row < p.N;
       if (!row_ok) row = p.N - 1;
-      const __half* nrow = p.norms + (int64_t)tc.expert * p.grp_norm_stride + (int64_t)row * p.ld_norms;
+      const unsigned short* nrow =
+          reinterpret_cast<const unsigned short*>(p.norms + (int64_t)tc.expert * p.grp_norm_stride + (int64_t)row * p.ld_norms);
       bool dead = false;
-      uint4 nq = make_uint4(0, 0, 0, 0);  // norms of eight consecutive blocks
       for (int ks = 0; ks < ksteps; ++ks, ++it) {
-        const int blk = ks >> 1;
-        if ((ks & 15) == 0) {  // every 8 blocks
-          if (norm_vec && blk + 8 <= (p.K >> 7)) {
-            nq = __ldg(reinterpret_cast<const uint4*>(nrow + blk));
-          } else {
-            unsigned short t8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              t8[i] = blk + i < (p.K >> 7) ? __ldg(reinterpret_cast<const unsigned short*>(nrow) + blk + i) : (unsigned short)0;
-            nq = make_uint4(t8[0] | (t8[1] << 16), t8[2] | (t8[3] << 16), t8[4] | (t8[5] << 16), t8[6] | (t8[7] << 16));
-          }
-        }
-        const int b8 = blk & 7;
-        const uint32_t nword = b8 < 2 ? nq.x : (b8 < 4 ? nq.y : (b8 < 6 ? nq.z : nq.w));
-        const float nf = row_ok ? __half2float(__ushort_as_half((unsigned short)((b8 & 1) ? (nword >> 16) : (nword & 0xffff)))) : 0.f;
-        const uint32_t n2 = pack_bf16(nf, nf);
-        // this step's codes from the TMA-filled stage, then hand the stage back
+        if ((it & (kGroups - 1)) != g) continue;  // warp-uniform
+        const float nf = row_ok ? __half2float(__ushort_as_half(__ldg(nrow + (ks >> 1)))) : 0.f;  // in flight across the waits
         const int sc = it % p.nc;
         {
           const bool ok = mbar_wait(full_c(sc), (it / p.nc) & 1, abort_flag, p.status, 7);
           if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }  // leave together or not at all
         }
-        constexpr int CW = PACKED ? 1 : 2;
+        constexpr int CW = PACKED ? 2 : 4;  // 16-byte pieces of this row's codes
         uint4 c[CW];
-        const uint8_t* csrc = sm + c_off + sc * kCodeStage + r * kCodeRow + kh * (kCodeRow / 2);
+        const uint8_t* csrc = sm + c_off + sc * kCodeStage + r * kCodeRow;
 #pragma unroll
         for (int i = 0; i < CW; ++i) c[i] = *reinterpret_cast<const uint4*>(csrc + 16 * i);
         // the stage goes back only after the loads have delivered: an arrival issued straight behind
@@ -347,38 +341,38 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_c(sc));
+        const uint32_t n2 = pack_bf16(nf, nf);
         const int sw = it % kWStages;
         {
           const bool ok = mbar_wait(empty_w(sw), ((it / kWStages) & 1) ^ 1, abort_flag, p.status, 4);
           if (!__all_sync(0xffffffffu, ok)) { dead = true; break; }
         }
         uint8_t* wt = sm + kWOff + sw * kWTileBytes + wrow;
-        if (PACKED) {
-          // one code byte -> two adjacent K elements; word j (4 bytes) -> chunk 4 kh + j (8 elements, 16 B)
-          const uint32_t wq[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t w = wq[j];
-            uint4 o;
-            o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
-            o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
-            o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
-            o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
-            *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw7) << 4)) = o;
-          }
-        } else {
-          // one code byte -> one K element; words 2j, 2j+1 -> chunk 4 kh + j
-          const uint4 c1 = c[CW - 1];
-          const uint32_t wq[8] = {c[0].x, c[0].y, c[0].z, c[0].w, c1.x, c1.y, c1.z, c1.w};
+        for (int i = 0; i < CW; ++i) {
+          const uint32_t wq[4] = {c[i].x, c[i].y, c[i].z, c[i].w};
+          if (PACKED) {  // one code byte -> two adjacent K elements; word j of piece i -> chunk 4 i + j
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t wa = wq[2 * j], wb = wq[2 * j + 1];
-            uint4 o;
-            o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
-            o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
-            o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
-            o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
-            *reinterpret_cast<uint4*>(wt + (((4 * kh + j) ^ sw7) << 4)) = o;
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w = wq[j];
+              uint4 o;
+              o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
+              o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
+              o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
+              o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+              *reinterpret_cast<uint4*>(wt + (((4 * i + j) ^ sw7) << 4)) = o;
+            }
+          } else {       // one code byte -> one K element; words 2j, 2j+1 of piece i -> chunk 2 i + j
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const uint32_t wa = wq[2 * j], wb = wq[2 * j + 1];
+              uint4 o;
+              o.x = bf16x2_mul(lo_hi16(glut<0>(wa, lane_base), glut<1>(wa, lane_base)), n2);
+              o.y = bf16x2_mul(lo_hi16(glut<2>(wa, lane_base), glut<3>(wa, lane_base)), n2);
+              o.z = bf16x2_mul(lo_hi16(glut<0>(wb, lane_base), glut<1>(wb, lane_base)), n2);
+              o.w = bf16x2_mul(lo_hi16(glut<2>(wb, lane_base), glut<3>(wb, lane_base)), n2);
+              *reinterpret_cast<uint4*>(wt + (((2 * i + j) ^ sw7) << 4)) = o;
+            }
           }
         }
         // make the generic-proxy stores visible to the tensor core, then one arrive per warp
@@ -428,9 +422,10 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
           }
         }
       }
-      // TMEM reads are done before the next tile's first MMA: the fence orders them
-      // before the full_w arrivals that MMA waits for.
+      // the next tile's first MMA overwrites the accumulators: it waits for every decode warp
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
     }
   }
 
@@ -1045,7 +1040,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   const int code_row = packed ? 32 : 64;
   const int code_stage = kTileN * code_row;
   const unsigned fixed = kXStages * 2 * kXTileBytes + kWStages * kWTileBytes + a.lut_bytes + 256 + 1024;
-  a.nc = (fixed + 3 * code_stage <= 232448u) ? 3 : 2;
+  a.nc = kGroups;  // a decode group owns its code stage
   const unsigned smem_bytes = fixed + a.nc * code_stage;
 
   // codes as a 2-D byte tensor (row stride ld_codes), boxes of 256 rows x one K step
@@ -1105,7 +1100,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
       return PE_OK;
     }
     a.tiles_m = (m + kTileM - 1) / kTileM;
-    a.nc = (fixed + 3 * code_stage <= 232448u) ? 3 : 2;
+    a.nc = kGroups;
     a.lut_bytes = (packed ? 256 : n_levels) * 128;
   }
   const int tiles = a.tiles_m * a.tiles_n;
@@ -1201,7 +1196,7 @@ extern "C" int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, 
   const int code_row = packed ? 32 : 64;
   const int code_stage = kTileN * code_row;
   const unsigned fixed = kXStages * 2 * kXTileBytes + kWStages * kWTileBytes + a.lut_bytes + 256 + 1024;
-  a.nc = (fixed + 3 * code_stage <= 232448u) ? 3 : 2;
+  a.nc = kGroups;  // a decode group owns its code stage
   const unsigned smem_bytes = fixed + a.nc * code_stage;
 
   CUtensorMap cmap;
