@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "pe_common.cuh"
+#include "pe_gemv_decode.cuh"
 
 namespace pe {
 
@@ -164,6 +165,19 @@ __device__ __forceinline__ uint32_t lo_hi16(uint32_t a, uint32_t b) {
   return r;
 }
 
+// bf16 centroids of a layer with at most 8 levels as a register table for reg_decode (byte permutes instead of
+// shared-memory look-ups: the look-ups are what fills the shared-memory pipe when a weight tile serves few tokens)
+__device__ __forceinline__ RegTable bf16_reg_table(const float* ct, int n_levels) {
+  RegTable tb = {0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t hb = pack_bf16(i < n_levels ? ct[i] : 0.f, 0.f) & 0xffffu;
+    if (i < 4) { tb.lo0 |= (hb & 0xff) << (8 * i); tb.hi0 |= (hb >> 8) << (8 * i); }
+    else { tb.lo1 |= (hb & 0xff) << (8 * (i - 4)); tb.hi1 |= (hb >> 8) << (8 * (i - 4)); }
+  }
+  return tb;
+}
+
 // table entry address: lut + byte * 128 + lane * 4
 template <int BYTE>
 __device__ __forceinline__ uint32_t glut(uint32_t word, uint32_t lane_base) {
@@ -300,6 +314,8 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
     // than two phases ahead of its barrier, which stages shared between groups would not guarantee).
     const int d = tid - 64;
     const int r = d & 255, g = d >> 8;
+    const bool regtab = PACKED && p.n_levels <= 8;  // nibble codes below 8: a valid byte-permute selector
+    const RegTable tb = regtab ? bf16_reg_table(p.ct, p.n_levels) : RegTable{0, 0, 0, 0};
     const uint32_t lane_base = lut_s + lane * 4;
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
     const int grp = (warp - 2) >> 2;        // 0..3
@@ -356,10 +372,16 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
             for (int j = 0; j < 4; ++j) {
               const uint32_t w = wq[j];
               uint4 o;
-              o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
-              o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
-              o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
-              o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+              if (regtab) {
+                uint32_t a[4];
+                reg_decode(w, tb, a);
+                o.x = bf16x2_mul(a[0], n2); o.y = bf16x2_mul(a[1], n2); o.z = bf16x2_mul(a[2], n2); o.w = bf16x2_mul(a[3], n2);
+              } else {
+                o.x = bf16x2_mul(glut<0>(w, lane_base), n2);
+                o.y = bf16x2_mul(glut<1>(w, lane_base), n2);
+                o.z = bf16x2_mul(glut<2>(w, lane_base), n2);
+                o.w = bf16x2_mul(glut<3>(w, lane_base), n2);
+              }
               *reinterpret_cast<uint4*>(wt + (((4 * i + j) ^ sw7) << 4)) = o;
             }
           } else {       // one code byte -> one K element; words 2j, 2j+1 of piece i -> chunk 2 i + j
@@ -409,6 +431,18 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
               uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.y) + (int64_t)m * p.ld_y + nb0);
 #pragma unroll
               for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            } else if (p.y_dtype == PE_F32 && nb0 + 32 <= p.N && (p.ld_y % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0)) {
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (int64_t)m * p.ld_y + nb0);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(rr[4 * j]), __uint_as_float(rr[4 * j + 1]), __uint_as_float(rr[4 * j + 2]),
+                                       __uint_as_float(rr[4 * j + 3]));
+                if (p.bias) {
+                  v.x += __half2float(p.bias[nb0 + 4 * j]); v.y += __half2float(p.bias[nb0 + 4 * j + 1]);
+                  v.z += __half2float(p.bias[nb0 + 4 * j + 2]); v.w += __half2float(p.bias[nb0 + 4 * j + 3]);
+                }
+                dst[j] = v;
+              }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -696,6 +730,8 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     // (thread = one weight row, all 64 K elements): four steps are in the decode pipeline at a time.
     const int d = tid - 64;
     const int r = d & 127, g = d >> 7;
+    const bool regtab = PACKED && p.n_levels <= 8;  // nibble codes below 8: a valid byte-permute selector
+    const RegTable tb = regtab ? bf16_reg_table(p.ct, p.n_levels) : RegTable{0, 0, 0, 0};
     // nibble layers: lanes l and l + 16 share a copy of the table (a two-way bank conflict when their
     // entries differ but have the same parity; the decode warps have the time)
     const uint32_t lane_base = lut_s + (uint32_t)(lane * 4 & (kLutStride - 1));
@@ -754,10 +790,16 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
             for (int j = 0; j < 4; ++j) {
               const uint32_t w = wq[j];
               uint4 o;
-              o.x = bf16x2_mul(glut_s<0, kLutStride>(w, lane_base), n2);
-              o.y = bf16x2_mul(glut_s<1, kLutStride>(w, lane_base), n2);
-              o.z = bf16x2_mul(glut_s<2, kLutStride>(w, lane_base), n2);
-              o.w = bf16x2_mul(glut_s<3, kLutStride>(w, lane_base), n2);
+              if (regtab) {
+                uint32_t a[4];
+                reg_decode(w, tb, a);
+                o.x = bf16x2_mul(a[0], n2); o.y = bf16x2_mul(a[1], n2); o.z = bf16x2_mul(a[2], n2); o.w = bf16x2_mul(a[3], n2);
+              } else {
+                o.x = bf16x2_mul(glut_s<0, kLutStride>(w, lane_base), n2);
+                o.y = bf16x2_mul(glut_s<1, kLutStride>(w, lane_base), n2);
+                o.z = bf16x2_mul(glut_s<2, kLutStride>(w, lane_base), n2);
+                o.w = bf16x2_mul(glut_s<3, kLutStride>(w, lane_base), n2);
+              }
               *reinterpret_cast<uint4*>(wt + (((4 * i + j) ^ sw7) << 4)) = o;
             }
           } else {       // one code byte -> one K element; words 2j, 2j+1 of piece i -> chunk 2 i + j
@@ -852,6 +894,18 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
               uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.y) + (int64_t)m * p.ld_y + nb0);
 #pragma unroll
               for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            } else if (p.y_dtype == PE_F32 && nb0 + 32 <= p.N && (p.ld_y % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0)) {
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (int64_t)m * p.ld_y + nb0);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(rr[4 * j]), __uint_as_float(rr[4 * j + 1]), __uint_as_float(rr[4 * j + 2]),
+                                       __uint_as_float(rr[4 * j + 3]));
+                if (p.bias) {
+                  v.x += __half2float(p.bias[nb0 + 4 * j]); v.y += __half2float(p.bias[nb0 + 4 * j + 1]);
+                  v.z += __half2float(p.bias[nb0 + 4 * j + 2]); v.w += __half2float(p.bias[nb0 + 4 * j + 3]);
+                }
+                dst[j] = v;
+              }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -938,20 +992,25 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const void* x, int x_kin
 __global__ void __launch_bounds__(256) gemm_group_tiles_kernel(const int* expert_rows, int n_experts, int tiles_n, int max_tiles,
                                                                int4* tiles, int* n_tiles) {
   __shared__ int first_tile[1025];
+  __shared__ int2 span[1024];  // (first row, rows) of every expert: read once, in parallel
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) span[e] = make_int2(expert_rows[2 * e], expert_rows[2 * e + 1]);
+  __syncthreads();
   if (threadIdx.x == 0) {
     int t = 0;
     for (int e = 0; e < n_experts; ++e) {
       first_tile[e] = t;
-      t += ((expert_rows[2 * e + 1] + kTileM - 1) / kTileM) * tiles_n;
+      t += ((span[e].y + kTileM - 1) / kTileM) * tiles_n;
     }
     first_tile[n_experts] = t;
     *n_tiles = t < max_tiles ? t : max_tiles;
   }
   __syncthreads();
-  for (int e = 0; e < n_experts; ++e) {
-    const int first = expert_rows[2 * e], cnt = expert_rows[2 * e + 1];
+  // one warp per expert at a time
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int e = warp; e < n_experts; e += n_warps) {
+    const int first = span[e].x, cnt = span[e].y;
     const int nt = first_tile[e + 1] - first_tile[e];
-    for (int i = threadIdx.x; i < nt; i += blockDim.x) {
+    for (int i = lane; i < nt; i += 32) {
       const int mt = i / tiles_n, ntile = i - mt * tiles_n;
       const int rows = cnt - mt * kTileM;
       if (first_tile[e] + i < max_tiles)
