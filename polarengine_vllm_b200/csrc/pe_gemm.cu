@@ -962,27 +962,47 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
 __global__ void __launch_bounds__(256) gemm_prep_kernel(const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f,
                                                         __nv_bfloat16* xq, int M, int K, int pair_layout, const int* x_rows,
                                                         const int* valid_rows) {
+  // Grid-stride over the (row, block) items, four per trip with their loads issued together: one item is only 256
+  // bytes in and 256 out, and a warp that handles one item per launch slot spends its life in launch and latency.
+  constexpr int U = 4;
   const int lane = threadIdx.x & 31;
   const int nb = K / kBlock;
-  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (warp >= (int64_t)M * nb) return;
-  const int m = (int)(warp / nb), blk = (int)(warp - (int64_t)m * nb);
+  const int64_t items = (int64_t)M * nb;
+  const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const bool vin = (ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
-  const bool live = !valid_rows || m < valid_rows[0] + valid_rows[1];
-  const int64_t src_row = (x_rows && live) ? x_rows[m] : m;
-  float v[4];
-  load4_as_float(x, x_dtype, src_row * ld_x, blk * kBlock + lane * 4, live ? (x_kind == PE_X_RAW ? in_f : K) : 0, vin, v);
-  if (x_kind == PE_X_RAW) warp_fwht128(v, lane);
-  __nv_bfloat16* dst = xq + (int64_t)m * K + blk * kBlock;
-  if (pair_layout) {
-    float o[4];
+  const int n_live = valid_rows ? valid_rows[0] + valid_rows[1] : M;
+  const int limit = x_kind == PE_X_RAW ? in_f : K;
+  for (int64_t w0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w0 < items; w0 += n_warps * U) {
+    Raw4 raw[U];
+    int m[U], blk[U];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[i], 16);
-    if (lane < 16)  // positions 8*lane .. 8*lane+7 = pairs (k, k+64), k = 4*lane..4*lane+3
-      *reinterpret_cast<uint4*>(dst + 8 * lane) = make_uint4(pack_bf16(v[0], o[0]), pack_bf16(v[1], o[1]),
-                                                             pack_bf16(v[2], o[2]), pack_bf16(v[3], o[3]));
-  } else {
-    *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+    for (int u = 0; u < U; ++u) {
+      const int64_t w = w0 + u * n_warps;
+      const bool on = w < items;
+      m[u] = on ? (int)(w / nb) : 0;
+      blk[u] = on ? (int)(w - (int64_t)m[u] * nb) : 0;
+      const bool live = on && m[u] < n_live;
+      const int64_t src_row = (x_rows && live) ? x_rows[m[u]] : m[u];
+      raw[u] = load4_raw(x, x_dtype, src_row * ld_x, blk[u] * kBlock + lane * 4, live ? limit : 0, vin);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (w0 + u * n_warps >= items) break;  // warp-uniform
+      float v[4];
+      cvt4(raw[u], x_dtype, v);
+      if (x_kind == PE_X_RAW) warp_fwht128(v, lane);
+      __nv_bfloat16* dst = xq + (int64_t)m[u] * K + blk[u] * kBlock;
+      if (pair_layout) {
+        float o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        if (lane < 16)  // positions 8*lane .. 8*lane+7 = pairs (k, k+64), k = 4*lane..4*lane+3
+          *reinterpret_cast<uint4*>(dst + 8 * lane) = make_uint4(pack_bf16(v[0], o[0]), pack_bf16(v[1], o[1]),
+                                                                 pack_bf16(v[2], o[2]), pack_bf16(v[3], o[3]));
+      } else {
+        *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+      }
+    }
   }
 }
 
@@ -1022,6 +1042,13 @@ __global__ void __launch_bounds__(256) gemm_group_tiles_kernel(const int* expert
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// CTAs of the preparation kernel: eight resident per SM, fewer for small inputs (a warp takes four items per trip)
+static unsigned prep_grid(int64_t items, int sms) {
+  const int64_t want = (items + 31) / 32;
+  const int64_t cap = (int64_t)sms * 8;
+  return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
+}
 
 static EncodeTiledFn encode_fn() {
   static EncodeTiledFn fn = nullptr;
@@ -1071,8 +1098,8 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   PE_CUDA_TRY(cudaMemsetAsync(status, 0, 4, st));
   const int nb = in_f_padded / kBlock;
   const int64_t warps = (int64_t)m * nb;
-  gemm_prep_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, m, in_f_padded,
-                                                                 packed ? 1 : 0, nullptr, nullptr);
+  gemm_prep_kernel<<<prep_grid(warps, sms), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, m, in_f_padded,
+                                                           packed ? 1 : 0, nullptr, nullptr);
   PE_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap map;
@@ -1228,8 +1255,8 @@ extern "C" int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, 
   PE_CUDA_TRY(cudaGetLastError());
   const int nb = in_f_padded / kBlock;
   const int64_t warps = (int64_t)rows * nb;
-  gemm_prep_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, rows, in_f_padded,
-                                                                 packed ? 1 : 0, x_rows, expert_rows + 2 * (n_experts - 1));
+  gemm_prep_kernel<<<prep_grid(warps, sms), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, rows, in_f_padded,
+                                                           packed ? 1 : 0, x_rows, expert_rows + 2 * (n_experts - 1));
   PE_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap map;
