@@ -28,7 +28,8 @@ def run_gemm(codes, norms, cts, x, bits, rotated=False, out_dtype=torch.float16,
 
 @pytest.mark.parametrize("bits", [3, 4, 5, 6])
 @pytest.mark.parametrize("m,n,k", [(64, 256, 256), (256, 512, 1024), (128, 256, 128), (300, 1856, 2688),
-                                   (100, 2688, 1920), (17, 130, 384), (1024, 4096, 4096)])
+                                   (100, 2688, 1920), (17, 130, 384), (1024, 4096, 4096),
+                                   (64, 40000, 256)])  # the last: more 256-row tiles than SMs, several tiles per CTA
 def test_gemm_matches_oracle(m, n, k, bits):
     codes, norms, cts = rand_layer(n, k, bits, seed=m + n + bits)
     x = rand_x(m, k, seed=3, dtype=torch.bfloat16)
