@@ -178,6 +178,13 @@ int pe_pack_nibble(const int8_t* codes, uint8_t* packed, int64_t out_f, int64_t 
  * (polar_gemm.py:485-534), plus the cast/bias epilogue of linear_method.py:214-221. */
 size_t pe_gemv_workspace_bytes(int batch, int out_f, int in_f_padded);
 int pe_gemv_status(void* workspace, size_t workspace_bytes, int clear, void* stream);
+
+/* 1 if pe_gemv runs batches of 3..8 rows of this layer on its row-major arrays with the column-owner
+ * tensor-core kernel (weights decoded once per step and used for every row of the batch; no scratch
+ * memory, no tiled copy of the layer needed), 0 if such batches go to the tile kernel, which streams the
+ * tiled copy (pe_retile / pe_gemv_tiled) best.  No launch, no device access beyond the SM count. */
+int pe_gemv_small_batch_takes(int packed, int64_t ld_codes, const void* norms, int64_t ld_norms, int out_f,
+                              int in_f_padded);
 int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
             const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f,

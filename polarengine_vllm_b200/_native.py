@@ -59,6 +59,7 @@ SIGNATURES = {
     "pe_decode_attention": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pe_gemv_pro": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, ctypes.c_float, _vp, _i, _vp, _i, _i, _vp]),
     "pe_gemv_status": (_i, [_vp, _sz, _i, _vp]),
+    "pe_gemv_small_batch_takes": (_i, [_i, _i64, _vp, _i64, _i, _i]),
     "pe_gemv_noalloc_status": (_i, [_i, _vp]),
     "pe_rope_attention": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp, _sz, _vp]),
     "pe_gemv_noalloc_max_bytes": (_sz, []),

@@ -1073,8 +1073,18 @@ static int gemv_run(const void* codes, int packed, int64_t ld_codes, const void*
                                     workspace_bytes >= kCounterBytes ? workspace : nullptr, stream);
     if (r <= 0) return r;
   }
+  if (!tiles && batch >= 3 && batch <= 8) {  // small batches on the row-major layout: column-owner kernel, no scratch
+    const int r = gemv_cols8_try(codes, packed, ld_codes, norms, ld_norms, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
+                                 y_dtype, ld_y, bias, batch, out_f, in_f_padded, static_cast<cudaStream_t>(stream));
+    if (r <= 0) return r;
+  }
   return gemv_tile_run(codes, packed, ld_codes, norms, ld_norms, tiles, ct_scaled, n_levels, x, x_kind, x_dtype, ld_x, in_f, y,
                        y_dtype, ld_y, bias, batch, out_f, in_f_padded, workspace, workspace_bytes, stream);
+}
+
+extern "C" int pe_gemv_small_batch_takes(int packed, int64_t ld_codes, const void* norms, int64_t ld_norms, int out_f,
+                                         int in_f_padded) {
+  return gemv_cols8_takes(packed, ld_codes, norms, ld_norms, out_f, in_f_padded) ? 1 : 0;
 }
 
 extern "C" int pe_gemv(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,

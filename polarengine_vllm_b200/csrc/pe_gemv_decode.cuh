@@ -134,4 +134,12 @@ int gemv_rows_try(const void* codes, int packed, int64_t ld_codes, const void* n
                   void* y, int y_dtype, int64_t ld_y, const void* bias, int batch, int out_f, int in_f_padded,
                   int* status, cudaStream_t stream);
 
+// The column-owner kernel for 3..8 activation rows (pe_gemv_cols8.cu), row-major layout only.  Returns PE_OK after a
+// launch, 1 if the shape is not its kind, or a negative error code; gemv_cols8_takes answers the same question
+// without launching.
+int gemv_cols8_try(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms, const float* ct_scaled,
+                   int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f, void* y, int y_dtype,
+                   int64_t ld_y, const void* bias, int batch, int out_f, int in_f_padded, cudaStream_t stream);
+bool gemv_cols8_takes(int packed, int64_t ld_codes, const void* norms, int64_t ld_norms, int out_f, int in_f_padded);
+
 }  // namespace pe

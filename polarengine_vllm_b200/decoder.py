@@ -26,7 +26,7 @@ import torch.nn.functional as F
 
 from .decode_ops import add_rmsnorm, decode_attention, rope_attention, rope_cache, silu_mul
 from . import _native as nv
-from .kernels import quant_embedding, quant_matmul, quant_matmul_pro, retile
+from .kernels import SMALL_BATCH_MAX, quant_embedding, quant_matmul, quant_matmul_pro, retile, small_batch_takes
 from .packing import pack_codes_half_block
 from .parallel import PeerExchange, shard_codes_for_tp, shard_norms_for_tp
 from .utils import get_centroids, get_ct_scaled
@@ -87,7 +87,8 @@ class QWeight:
                                 out_dtype, **kw)
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
-        if self.tiles is None and 3 <= x.shape[0] <= 16 and not torch.cuda.is_current_stream_capturing():
+        if (self.tiles is None and 3 <= x.shape[0] <= 16 and not torch.cuda.is_current_stream_capturing()
+                and not (x.shape[0] <= SMALL_BATCH_MAX and small_batch_takes(self.codes, self.packed, self.norms, self.out_f, self.in_f))):
             self.tiles = retile(self.codes, self.packed, self.norms)
         return quant_matmul(self.codes, self.packed, self.norms, self.ct, x, False, self.out_f, self.in_f, self.in_f, out_dtype,
                             tiles=self.tiles)

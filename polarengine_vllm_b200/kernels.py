@@ -38,13 +38,24 @@ def retile(codes: torch.Tensor, packed: bool, norms: torch.Tensor) -> torch.Tens
     return out
 
 
+SMALL_BATCH_MAX = 8
+
+
+def small_batch_takes(codes: torch.Tensor, packed: bool, norms: torch.Tensor, out_f: int, in_f_padded: int) -> bool:
+    """True if batches of 3..8 rows of this layer run on the row-major arrays (column-owner tensor-core kernel):
+    such batches need no tiled copy of the layer."""
+    return bool(nv.lib().pe_gemv_small_batch_takes(int(packed), codes.stride(0) * codes.element_size(), norms.data_ptr(),
+                                                   norms.stride(0), out_f, in_f_padded))
+
+
 def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scaled: torch.Tensor, x: torch.Tensor,
                  rotated: bool, out_f: int, in_f: int, in_f_padded: int, out_dtype: torch.dtype = torch.float32,
                  bias: Optional[torch.Tensor] = None, tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y (batch, out_f) for x (batch, in_f or in_f_padded); the single entry to the
     native kernels used by everything else in the package.  ``tiles`` (from
     :func:`retile`) lets batches of 3..16 rows stream the tiled copy of the layer; one or
-    two rows read the row-major arrays (whole weight rows per CTA, no scratch traffic)."""
+    two rows, and 3..8 rows of the layers :func:`small_batch_takes` accepts, read the row-major arrays (whole
+    weight rows per CTA, no scratch traffic)."""
     dev = nv.require_cuda(codes, norms, ct_scaled, x)
     nv.ensure_init(dev)
     if x.dim() != 2 or x.stride(1) != 1:
@@ -71,7 +82,7 @@ def quant_matmul(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct_scal
         for m0 in range(0, batch, GEMV_MAX_BATCH):
             m1 = min(batch, m0 + GEMV_MAX_BATCH)
             xs, ys = x[m0:m1], y[m0:m1]
-            if tiles is not None and batch > 2:
+            if tiles is not None and batch > 2 and not (batch <= SMALL_BATCH_MAX and small_batch_takes(codes, packed, norms, out_f, in_f_padded)):
                 nv.check(l.pe_gemv_tiled(tiles.data_ptr(), int(packed), ct.data_ptr(), ct.numel(), xs.data_ptr(),
                                          nv.PE_X_ROTATED if rotated else nv.PE_X_RAW, nv.dtype_code(xs), xs.stride(0),
                                          in_f, ys.data_ptr(), nv.dtype_code(ys), ys.stride(0),

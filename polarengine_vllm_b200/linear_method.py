@@ -22,7 +22,7 @@ from typing import Any, Dict, List, Optional
 
 import torch
 
-from .kernels import pack_codes_int4, quant_matmul, retile
+from .kernels import SMALL_BATCH_MAX, pack_codes_int4, quant_matmul, retile, small_batch_takes
 from .packing import unpack_codes_half_block, unpack_codes_q5
 from .utils import get_ct_scaled
 
@@ -142,7 +142,9 @@ class PolarQuantLinearMethod(_Base):
         packed = bool(getattr(layer, "packed", False))
         w = layer.codes_packed if packed else layer.codes
         if (self.decode_tiled and 3 <= x2.shape[0] <= 16 and getattr(layer, "codes_tiled", None) is None
-                and not torch.cuda.is_current_stream_capturing()):
+                and not torch.cuda.is_current_stream_capturing()
+                and not (x2.shape[0] <= SMALL_BATCH_MAX
+                         and small_batch_takes(w.data, packed, layer.norms.data.reshape(layer.out_f, -1), layer.out_f, layer.in_f_padded))):
             layer.codes_tiled = retile(w.data, packed, layer.norms.data)
         # one native entry for every batch size: <= 16 rows run the fused decode kernel,
         # more rows the tensor-core kernel (rotation is done by its preparation launch)
