@@ -683,7 +683,9 @@ def main():
     dom_launches = dom_passes * RING
     dom_bytes = sum(alg_bytes(n, k, b, a.batch) for nm, n, k, b in PROJ if nm in dom)
     achieved = dom_bytes / (dom_elapsed / dom_launches) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gemv_cols_kernel<nibble codes, table, 3 chunks per warp> on down_proj 4096x12288 Q4",
+    dom_kernel = ("gemv_cols_kernel<nibble codes, table, 3 chunks per warp>" if a.batch == 1 else
+                  "gemv_rows_kernel<nibble codes, table>" if a.batch == 2 else "gemv_kernel (tile kernel)<nibble codes, table>")
+    roofline = {"bound": "hbm", "kernel": dom_kernel + " on down_proj 4096x12288 Q4",
                 "achieved": achieved, "peak": peak, "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                 "unit": "GB/s", "frac": achieved / peak, "avg_launch_us": dom_elapsed / dom_launches * 1e6,
                 "alg_bytes_per_launch": dom_bytes, "launches_timed": dom_launches,
