@@ -293,8 +293,10 @@ int pe_gemv_tiled(const void* tiles, int packed, const float* ct_scaled, int n_l
  * weights are rounded to bf16).  Two launches: activation preparation (pad, rotate when
  * x_kind is PE_X_RAW, bf16) into the workspace, then the matmul.
  *   workspace  at least pe_gemm_workspace_bytes(m, in_f_padded), 256-byte aligned.  Its
- *              first int32 is a status word written by the kernel: 0 on success, 1..5
+ *              first int32 is a status word written by the kernel: 0 on success, 1..10
  *              if a bounded device-side wait ran out (the output is then undefined).
+ * More than 256 rows run on pairs of CTAs (thread-block clusters of two, one tensor-core
+ * operation per pair); the launch needs no more than the usual one-CTA-per-SM residency.
  * Replaces polar_matmul's batched branch: polar_gemm / polar_gemm_packed
  * (polar_gemm.py:312-418, 526-534) and the epilogue of linear_method.py:214-221. */
 size_t pe_gemm_workspace_bytes(int m, int in_f_padded);
