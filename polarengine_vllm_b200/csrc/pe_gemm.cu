@@ -3,23 +3,23 @@
 //
 //   Y[m, n] = sum_k Xt[m, k] * (ct[code[n, k]] * norm[n, k / 128])        (+ bias[n])
 //
-// A CTA owns a 256 (tokens) x 256 (weight rows) output tile and walks K in steps of 64:
-//   * warp 0, one lane: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) brings two
-//     128 x 64 bf16 activation tiles per step into shared memory;
-//   * warps 2..9 (256 threads, one weight row each): stream that row's codes, look the
-//     centroids up in a lane-replicated shared table, scale by the block norm (bf16x2
-//     multiply) and store the 256 x 64 bf16 weight tile in the same swizzled K-major
-//     layout the tensor core reads -- the decoded weights never touch HBM or L2;
-//   * warp 1, one lane: eight tcgen05.mma (128 x 256 x 16, bf16 in, fp32 accumulate) per
-//     step, two accumulators of 256 TMEM columns each (all 512 columns), commit to the
-//     stage's "empty" barrier;
-//   * after the last step the decode warps read the accumulators back (tcgen05.ld),
-//     add the bias, convert and store.
-// Decoding a weight tile once per 256 tokens keeps the table lookups at a quarter of
-// the shared-memory bandwidth; three 64 KB stages keep TMA, decode and MMA overlapped.
-// The activations are prepared by a small kernel (pad + FWHT-128 for raw input, bf16,
-// and for nibble layers the (k, k+64) pairing of the half-block layout so that one code
-// byte decodes to two adjacent K elements).
+// Two persistent kernels share the scheme; both walk K in steps of 64:
+//   * one thread issues TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) for the bf16
+//     activation tiles and for the raw code rows of the step;
+//   * 16 decode warps turn code rows into a bf16 weight stage in the swizzled K-major layout the tensor
+//     core reads (table look-up or byte permutes, times the block norm) -- the decoded weights never
+//     touch HBM or L2.  The warps form groups that take alternate K steps, because one warp's trip through
+//     a step (barrier round trips, proxy fence) lasts longer than the step's MMAs;
+//   * one thread issues tcgen05.mma (bf16 in, fp32 accumulate in TMEM: two accumulators of 256 columns
+//     = all 512) and hands stages back with tcgen05.commit;
+//   * after the last step the decode warps read the accumulators back (tcgen05.ld), add the bias,
+//     convert and store.
+// gemm_kernel: one CTA per 256 tokens x 256 weight rows (up to 256 tokens, and the grouped launches of a
+// mixture-of-experts layer).  gemm_pair_kernel: a cluster of two CTAs per 512 tokens x 256 weight rows,
+// one cta_group::2 MMA per pair, each CTA decoding half of the weight tile (more than 256 tokens).
+// The activations are prepared by a small kernel (pad + FWHT-128 for raw input, bf16, and for nibble
+// layers the (k, k+64) pairing of the half-block layout so that one code byte decodes to two adjacent
+// K elements).
 //
 // Every wait is bounded: on time-out the kernel records a status code in the first word
 // of the workspace, all roles leave their loops, TMEM is released and the grid returns.
@@ -710,7 +710,7 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     done_mma:;
     } else if (lane == 0) {
       // ---------------- relay (odd CTA): "my activation stage is full" to the even CTA ----------------
-      // (a pair-wide TMA load counted on the even CTA's barrier would save this hop; it stalled when tried)
+      // (a pair-wide TMA load counted on the even CTA's barrier would save this hop; not measured on its own yet)
       const uint32_t lead = map_to_cta(bars, 0) - bars;  // same barrier, even CTA
       int it = 0;
       for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
