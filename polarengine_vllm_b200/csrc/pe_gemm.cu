@@ -544,6 +544,14 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     }
   }
 }
+// TMA load of a CTA pair: the bytes land in THIS CTA's shared memory, the completion is counted on a barrier
+// that may live in the other CTA of the pair (a mapped address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
 __device__ __forceinline__ void umma_pair_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -605,8 +613,8 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
   const uint32_t stg_free = bars + 208;   // the output staging (inside the weight stages) has been read by the TMA stores
 
   if (tid == 0) {
-    // activation stage of the even CTA: its own copy and the relayed arrival of the odd CTA's
-    for (int s = 0; s < kPairXStages; ++s) { mbar_init(full_x(s), leader ? 2 : 1); mbar_init(empty_x(s), 1); }
+    // activation stage: one barrier in the even CTA counts the bytes of both CTAs' copies
+    for (int s = 0; s < kPairXStages; ++s) { mbar_init(full_x(s), 1); mbar_init(empty_x(s), 1); }
     // weight stage: the decode warps of both CTAs
     for (int s = 0; s < kPairWStages; ++s) { mbar_init(full_w(s), 2 * kPairGroupWarps); mbar_init(empty_w(s), 1); }
     for (int s = 0; s < p.nc; ++s) { mbar_init(full_c(s), 1); mbar_init(empty_c(s), kPairGroupWarps); }
@@ -645,7 +653,9 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
 
   if (warp == 0) {
     // ---------------- TMA producer: this CTA's activation tiles ----------------
+    // Both CTAs' copies complete on the even CTA's barrier, which expects the bytes of both.
     if (lane == 0) {
+      const uint32_t lead = map_to_cta(bars, 0) - bars;
       int it = 0;
       for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
         const int m0 = (tile % p.tiles_m) * kPairTileM;
@@ -653,9 +663,9 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int sx = it % kPairXStages;
           if (!mbar_wait(empty_x(sx), ((it / kPairXStages) & 1) ^ 1, abort_flag, p.status, 1)) goto done_producer;
-          mbar_expect_tx(full_x(sx), two ? 2 * kXTileBytes : kXTileBytes);
-          tma_load_2d(base + sx * kXStage, &xmap, ks * kStepK, m0 + (int)rank * 128, full_x(sx));
-          if (two) tma_load_2d(base + sx * kXStage + kXTileBytes, &xmap, ks * kStepK, m0 + 256 + (int)rank * 128, full_x(sx));
+          if (leader) mbar_expect_tx(full_x(sx), 2 * (two ? 2 * kXTileBytes : kXTileBytes));
+          tma_load_2d_pair(base + sx * kXStage, &xmap, ks * kStepK, m0 + (int)rank * 128, full_x(sx) + lead);
+          if (two) tma_load_2d_pair(base + sx * kXStage + kXTileBytes, &xmap, ks * kStepK, m0 + 256 + (int)rank * 128, full_x(sx) + lead);
         }
       }
     done_producer:;
@@ -708,19 +718,6 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
         umma_pair_commit(peer_acc_full);
       }
     done_mma:;
-    } else if (lane == 0) {
-      // ---------------- relay (odd CTA): "my activation stage is full" to the even CTA ----------------
-      // (a pair-wide TMA load counted on the even CTA's barrier would save this hop; not measured on its own yet)
-      const uint32_t lead = map_to_cta(bars, 0) - bars;  // same barrier, even CTA
-      int it = 0;
-      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
-          const int sx = it % kPairXStages;
-          if (!mbar_wait(full_x(sx), (it / kPairXStages) & 1, abort_flag, p.status, 8)) goto done_relay;
-          mbar_arrive_remote(full_x(sx) + lead);
-        }
-      }
-    done_relay:;
     }
   } else {
     // ---------------- decode + epilogue warps ----------------
