@@ -156,7 +156,7 @@ def cpu_baseline(batch, budget_s=12.0):
 
 
 # ------------------------------------------------------------------------------------------ prefill
-def prefill_record(dev, m=4096, steps=10):
+def prefill_record(dev, m=4096, steps=20):
     """BASELINE configs[2]: M tokens x K into N, bf16 activations, Q4 nibble codes.  Per shape: TFLOP/s of
     2*M*N*K (rotation and activation preparation included in the time) and the fraction of the measured
     cuBLAS bf16 peaks (burst and sustained)."""
