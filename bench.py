@@ -156,8 +156,8 @@ def cpu_baseline(batch, budget_s=12.0):
 
 
 # ------------------------------------------------------------------------------------------ prefill
-def prefill_record(dev, m=4096, steps=20):
-    """BASELINE configs[2]: M tokens x K into N, bf16 activations, Q4 nibble codes.  Per shape: TFLOP/s of
+def prefill_record(dev, m=4096, steps=20, bits=4):
+    """BASELINE configs[2]: M tokens x K into N, bf16 activations, Q4 nibble codes (other widths with ``bits``).  Per shape: TFLOP/s of
     2*M*N*K (rotation and activation preparation included in the time) and the fraction of the measured
     cuBLAS bf16 peaks (burst and sustained)."""
     from polarengine_vllm_b200 import kernels
@@ -166,20 +166,25 @@ def prefill_record(dev, m=4096, steps=20):
     g = torch.Generator(device=dev).manual_seed(3)
     peaks = load_peaks()
     burst, sustained = float(peaks.get("bf16_tflops", 1590.0)), float(peaks.get("bf16_tflops_sustained", 1400.0))
-    rec = {"m": m, "dtype": "bf16", "bits": 4, "steps": steps, "peak_burst_tflops": burst, "peak_sustained_tflops": sustained,
+    rec = {"m": m, "dtype": "bf16", "bits": bits, "steps": steps, "peak_burst_tflops": burst, "peak_sustained_tflops": sustained,
            "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback", "shapes": {}}
     for n, k in shapes:
-        w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        if bits <= 4:  # nibble pairs, every code below 2^bits
+            lo = torch.randint(0, 1 << bits, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+            w = lo | (torch.randint(0, 1 << bits, (n, k // 2), dtype=torch.uint8, device=dev, generator=g) << 4)
+            del lo
+        else:
+            w = torch.randint(0, 1 << bits, (n, k), dtype=torch.uint8, device=dev, generator=g).view(torch.int8)
         norms = (0.2 + 0.02 * torch.rand(n, k // 128, device=dev, generator=g)).half()
-        ct = get_ct_scaled(4).to(dev)
+        ct = get_ct_scaled(bits).to(dev)
         x = torch.randn(m, k, device=dev, generator=g).bfloat16()
         for _ in range(3):
-            kernels.quant_matmul(w, True, norms, ct, x, False, n, k, k, torch.float16)
+            kernels.quant_matmul(w, bits <= 4, norms, ct, x, False, n, k, k, torch.float16)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            kernels.quant_matmul(w, True, norms, ct, x, False, n, k, k, torch.float16)
+            kernels.quant_matmul(w, bits <= 4, norms, ct, x, False, n, k, k, torch.float16)
         e1.record()
         torch.cuda.synchronize()
         per = e0.elapsed_time(e1) / 1e3 / steps
@@ -458,6 +463,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="model record: launch decode steps eagerly")
     ap.add_argument("--nccl-allreduce", action="store_true", help="model record: NCCL all-reduce instead of the fused peer-memory epilogue")
     ap.add_argument("--m", type=int, default=4096, help="tokens of the prefill record")
+    ap.add_argument("--bits", type=int, default=4, choices=[3, 4, 5, 6], help="prefill workload alone: code width of the layers")
     ap.add_argument("--tokens", type=int, default=None, help="moe workload alone: one token count instead of 64 and 2048")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -500,11 +506,11 @@ def main():
         sampler = ClockSampler(local)
         sampler.start()
         if a.workload == "prefill":
-            rec = prefill_record(dev, a.m, max(3, min(a.steps, 50)))
+            rec = prefill_record(dev, a.m, max(3, min(a.steps, 50)), a.bits)
             best = max(rec["shapes"].values(), key=lambda s: s["tflops"])
             line = dict(common, metric="prefill quantized GEMM TFLOP/s", unit="TFLOP/s", value=best["tflops"], steps=rec["steps"],
                         ms_per_step=best["ms"], scaling="weak", dtype="bf16",
-                        config={"workload": f"prefill_gemm (BASELINE configs[2]) M={a.m}, Q4"}, prefill=rec, gpu_launches=rec["gpu_launches"])
+                        config={"workload": f"prefill_gemm (BASELINE configs[2]) M={a.m}, Q{a.bits}"}, prefill=rec, gpu_launches=rec["gpu_launches"])
         elif a.workload == "model":
             rec = model_record(a, dev, rank, world, (a.batch,))
             r = rec[f"batch{a.batch}"]
