@@ -300,6 +300,10 @@ int pe_gemv_tiled(const void* tiles, int packed, const float* ct_scaled, int n_l
  * Replaces polar_matmul's batched branch: polar_gemm / polar_gemm_packed
  * (polar_gemm.py:312-418, 526-534) and the epilogue of linear_method.py:214-221. */
 size_t pe_gemm_workspace_bytes(int m, int in_f_padded);
+/* Launches of up to 256 rows on layers that give few 256-row tiles split K over the SMs when the workspace also
+ * holds their fp32 partials: this size (>= pe_gemm_workspace_bytes) makes room for them.  With less, pe_gemm runs
+ * unsplit.  Same result either way up to the order of the fp32 sums (fixed for a given shape and GPU). */
+size_t pe_gemm_workspace_bytes_splitk(int m, int out_f, int in_f_padded);
 int pe_gemm(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
             const float* ct_scaled, int n_levels, const void* x, int x_kind, int x_dtype, int64_t ld_x,
             int in_f, void* y, int y_dtype, int64_t ld_y, const void* bias, int m, int out_f,

@@ -50,6 +50,7 @@ SIGNATURES = {
     "pe_retile": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i64, _i64, _vp]),
     "pe_gemv_tiled": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "pe_gemm_workspace_bytes": (_sz, [_i, _i]),
+    "pe_gemm_workspace_bytes_splitk": (_sz, [_i, _i, _i]),
     "pe_gemm": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _i, _i64, _vp, _i, _i, _i,
                      _vp, _sz, _vp]),
     "pe_add_rmsnorm": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, ctypes.c_float, _vp]),

@@ -54,6 +54,8 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int lut_bytes;  // n_levels (256 for nibble pairs) x 128 B
   int nc;         // code stages
+  int ksplit;     // single-CTA kernel: K ranges per tile (1 = none); partial results in `part`
+  float* part;    // [ksplit][M][N] fp32
   int y_tma;      // paired kernel: the output leaves through TMA stores (16-bit output, 16-byte aligned rows)
   int* status;
   // grouped launch over a stack of matrices (the experts of a mixture layer): tile list on the device
@@ -252,17 +254,27 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
   const uint32_t tmem = *tmem_slot;
 
   const int ksteps = p.K / kStepK;
-  const int n_tiles = p.gtiles ? *p.n_gtiles : p.tiles_m * p.tiles_n;
+  // A unit of work is a tile, or -- for dense launches with few tiles -- one of `ksplit` K ranges of a tile, whose
+  // fp32 partial goes to the workspace and is summed by a second kernel.
+  const int n_tiles = (p.gtiles ? *p.n_gtiles : p.tiles_m * p.tiles_n) * p.ksplit;
+  auto unit_of = [&](int unit, int& split, int& ks0, int& ks1) {
+    const int tile = unit / p.ksplit;
+    split = unit - tile * p.ksplit;
+    ks0 = (int)((long long)split * ksteps / p.ksplit);
+    ks1 = (int)((long long)(split + 1) * ksteps / p.ksplit);
+    return tile;
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer: activations and codes ----------------
     if (lane == 0) {
       int it = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(p, tile);
+      for (int unit = blockIdx.x; unit < n_tiles && !*abort_flag; unit += gridDim.x) {
+        int split, ks0, ks1;
+        const TileCoord tc = tile_coord(p, unit_of(unit, split, ks0, ks1));
         const int m0 = tc.m0;
         const bool two = m0 + 128 < tc.m_end;
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        for (int ks = ks0; ks < ks1; ++ks, ++it) {
           const int sc = it % p.nc;
           if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6)) goto done_producer;
           mbar_expect_tx(full_c(sc), kCodeStage);
@@ -280,12 +292,13 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       int it = 0, tcount = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-        const TileCoord tc = tile_coord(p, tile);
+      for (int unit = blockIdx.x; unit < n_tiles && !*abort_flag; unit += gridDim.x, ++tcount) {
+        int split, ks0, ks1;
+        const TileCoord tc = tile_coord(p, unit_of(unit, split, ks0, ks1));
         const bool two = tc.m0 + 128 < tc.m_end;
         if (tcount > 0 && !mbar_wait(acc_empty, (tcount - 1) & 1, abort_flag, p.status, 9)) goto done_mma;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        for (int ks = ks0; ks < ks1; ++ks, ++it) {
           const int sx = it % kXStages, sw = it % kWStages;
           if (!mbar_wait(full_x(sx), (it / kXStages) & 1, abort_flag, p.status, 2)) goto done_mma;
           if (!mbar_wait(full_w(sw), (it / kWStages) & 1, abort_flag, p.status, 3)) goto done_mma;
@@ -294,7 +307,7 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
 #pragma unroll
           for (int kk = 0; kk < kStepK / 16; ++kk) {
             const uint64_t db = smem_desc_sw128(wb + kk * 32);
-            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+            const uint32_t acc = (ks > ks0 || kk > 0) ? 1u : 0u;
             umma_bf16(tmem, smem_desc_sw128(xa + kk * 32), db, kIdesc, acc);
             if (two) umma_bf16(tmem + 256, smem_desc_sw128(xa + kXTileBytes + kk * 32), db, kIdesc, acc);
           }
@@ -324,9 +337,15 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
     const uint32_t wrow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
     const int sw7 = r & 7;
     int it = 0, tcount = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-      const TileCoord tc = tile_coord(p, tile);
+    for (int unit = blockIdx.x; unit < n_tiles && !*abort_flag; unit += gridDim.x, ++tcount) {
+      int split, ks0, ks1;
+      const TileCoord tc = tile_coord(p, unit_of(unit, split, ks0, ks1));
       const int m0 = tc.m0, n0 = tc.n0;
+      // where this unit's result goes: the output, or (K split) the fp32 partial of its K range
+      void* const y_ptr = p.ksplit > 1 ? static_cast<void*>(p.part + (size_t)split * p.M * p.N) : p.y;
+      const int y_dt = p.ksplit > 1 ? (int)PE_F32 : p.y_dtype;
+      const int64_t y_ld = p.ksplit > 1 ? (int64_t)p.N : p.ld_y;
+      const __half* const bias_ptr = p.ksplit > 1 ? nullptr : p.bias;
       const bool two = m0 + 128 < tc.m_end;
       int row = n0 + r;
       const bool row_ok = row < p.N;
@@ -334,7 +353,7 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
       const unsigned short* nrow =
           reinterpret_cast<const unsigned short*>(p.norms + (int64_t)tc.expert * p.grp_norm_stride + (int64_t)row * p.ld_norms);
       bool dead = false;
-      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+      for (int ks = ks0; ks < ks1; ++ks, ++it) {
         if ((it & (kGroups - 1)) != g) continue;  // warp-uniform
         const float nf = row_ok ? __half2float(__ushort_as_half(__ldg(nrow + (ks >> 1)))) : 0.f;  // in flight across the waits
         const int sc = it % p.nc;
@@ -419,27 +438,27 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           const int nb0 = n0 + cc * 32;
           if (m < tc.m_end && nb0 < p.N) {
-            const bool full = nb0 + 32 <= p.N && (p.ld_y % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
-            if (full && p.y_dtype != PE_F32) {
+            const bool full = nb0 + 32 <= p.N && (y_ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(y_ptr) & 15) == 0);
+            if (full && y_dt != PE_F32) {
               uint32_t o[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 float a = __uint_as_float(rr[2 * j]), b = __uint_as_float(rr[2 * j + 1]);
-                if (p.bias) { a += __half2float(p.bias[nb0 + 2 * j]); b += __half2float(p.bias[nb0 + 2 * j + 1]); }
-                o[j] = p.y_dtype == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
+                if (bias_ptr) { a += __half2float(bias_ptr[nb0 + 2 * j]); b += __half2float(bias_ptr[nb0 + 2 * j + 1]); }
+                o[j] = y_dt == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
               }
-              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.y) + (int64_t)m * p.ld_y + nb0);
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(y_ptr) + (int64_t)m * y_ld + nb0);
 #pragma unroll
               for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-            } else if (p.y_dtype == PE_F32 && nb0 + 32 <= p.N && (p.ld_y % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0)) {
-              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (int64_t)m * p.ld_y + nb0);
+            } else if (y_dt == PE_F32 && nb0 + 32 <= p.N && (y_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(y_ptr) & 15) == 0)) {
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(y_ptr) + (int64_t)m * y_ld + nb0);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 float4 v = make_float4(__uint_as_float(rr[4 * j]), __uint_as_float(rr[4 * j + 1]), __uint_as_float(rr[4 * j + 2]),
                                        __uint_as_float(rr[4 * j + 3]));
-                if (p.bias) {
-                  v.x += __half2float(p.bias[nb0 + 4 * j]); v.y += __half2float(p.bias[nb0 + 4 * j + 1]);
-                  v.z += __half2float(p.bias[nb0 + 4 * j + 2]); v.w += __half2float(p.bias[nb0 + 4 * j + 3]);
+                if (bias_ptr) {
+                  v.x += __half2float(bias_ptr[nb0 + 4 * j]); v.y += __half2float(bias_ptr[nb0 + 4 * j + 1]);
+                  v.z += __half2float(bias_ptr[nb0 + 4 * j + 2]); v.w += __half2float(bias_ptr[nb0 + 4 * j + 3]);
                 }
                 dst[j] = v;
               }
@@ -448,8 +467,8 @@ gemm_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, const __
               for (int j = 0; j < 32; ++j) {
                 if (nb0 + j < p.N) {
                   float a = __uint_as_float(rr[j]);
-                  if (p.bias) a += __half2float(p.bias[nb0 + j]);
-                  store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + nb0 + j, a);
+                  if (bias_ptr) a += __half2float(bias_ptr[nb0 + j]);
+                  store_from_float(y_ptr, y_dt, (int64_t)m * y_ld + nb0 + j, a);
                 }
               }
             }
@@ -1003,6 +1022,19 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const void* x, int x_kin
   }
 }
 
+// Sum of the K-split partials of a dense launch, in split order (bit-reproducible), plus bias, to the output type.
+__global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const float* part, int ksplit, int M, int N, const __half* bias,
+                                                                 void* y, int y_dtype, int64_t ld_y) {
+  const int64_t total = (int64_t)M * N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / N), n = (int)(i - (int64_t)m * N);
+    float s = 0.f;
+    for (int k = 0; k < ksplit; ++k) s += part[(size_t)k * total + i];
+    if (bias) s += __half2float(bias[n]);
+    store_from_float(y, y_dtype, (int64_t)m * ld_y + n, s);
+  }
+}
+
 // Tile list of a grouped launch from the experts' row ranges (first, count): for every expert its
 // ceil(count / 256) activation tiles x tiles_n weight tiles, weight tiles of one activation tile adjacent
 // (CTAs that run side by side then share the activation tile in L2).  One thread scans, the block writes.
@@ -1063,10 +1095,30 @@ static EncodeTiledFn encode_fn() {
 
 using namespace pe;
 
+// K ranges per tile for a dense launch of up to 256 rows: with 16 tiles of a 4096-row layer on 148 SMs, each walking
+// the whole K, nine tenths of the GPU idle; the K steps of a tile are spread over the SMs instead.
+static int gemm_ksplit(int m, int out_f, int in_f_padded, int sms) {
+  if (m > 256) return 1;
+  const int tiles = ((m + kTileM - 1) / kTileM) * ((out_f + kTileN - 1) / kTileN);
+  const int ksteps = in_f_padded / kStepK;
+  int s = sms / tiles;
+  if (s > ksteps / 4) s = ksteps / 4;  // at least four K steps per unit
+  return s < 2 ? 1 : s;
+}
+
 // workspace: [status word, padded to 256 B][bf16 activations M x K]
 extern "C" size_t pe_gemm_workspace_bytes(int m, int in_f_padded) {
   if (m < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
   return 256 + (size_t)m * in_f_padded * 2;
+}
+
+// [the above][fp32 partials ksplit x M x N]: with this much room a launch of up to 256 rows on few tiles splits K
+extern "C" size_t pe_gemm_workspace_bytes_splitk(int m, int out_f, int in_f_padded) {
+  const size_t base = pe_gemm_workspace_bytes(m, in_f_padded);
+  if (base == 0 || out_f < 1) return 0;
+  const int sms = sm_count();
+  const int ks = sms > 0 ? gemm_ksplit(m, out_f, in_f_padded, sms) : 1;
+  return ks > 1 ? ((base + 255) & ~(size_t)255) + (size_t)ks * m * out_f * sizeof(float) : base;
 }
 
 extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const void* norms, int64_t ld_norms,
@@ -1118,7 +1170,7 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
   a.tiles_m = (m + kTileM - 1) / kTileM;
   a.tiles_n = (out_f + kTileN - 1) / kTileN;
   a.status = status;
-  a.gtiles = nullptr; a.n_gtiles = nullptr; a.grp_norm_stride = 0; a.y_tma = 0;
+  a.gtiles = nullptr; a.n_gtiles = nullptr; a.grp_norm_stride = 0; a.y_tma = 0; a.ksplit = 1; a.part = nullptr;
   a.lut_bytes = (packed ? 256 : n_levels) * 128;
   const int code_row = packed ? 32 : 64;
   const int code_stage = kTileN * code_row;
@@ -1186,7 +1238,12 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
     a.nc = kGroups;
     a.lut_bytes = (packed ? 256 : n_levels) * 128;
   }
-  const int tiles = a.tiles_m * a.tiles_n;
+  // few tiles: split K when the caller's workspace has room for the partials
+  a.ksplit = gemm_ksplit(m, out_f, in_f_padded, sms);
+  const size_t part_off = (pe_gemm_workspace_bytes(m, in_f_padded) + 255) & ~(size_t)255;
+  if (a.ksplit > 1 && workspace_bytes < part_off + (size_t)a.ksplit * m * out_f * sizeof(float)) a.ksplit = 1;
+  a.part = a.ksplit > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + part_off) : nullptr;
+  const int tiles = a.tiles_m * a.tiles_n * a.ksplit;
   const int grid = tiles < sms ? tiles : sms;
   if (packed) {
     PE_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
@@ -1196,6 +1253,12 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
     gemm_kernel<false><<<grid, kGemmThreads, smem_bytes, st>>>(a, map, cmap);
   }
   PE_CUDA_TRY(cudaGetLastError());
+  if (a.ksplit > 1) {
+    const int64_t total = (int64_t)m * out_f;
+    const unsigned rgrid = (unsigned)((total + 255) / 256 < (int64_t)sms * 8 ? (total + 255) / 256 : (int64_t)sms * 8);
+    gemm_splitk_reduce_kernel<<<rgrid, 256, 0, st>>>(a.part, a.ksplit, m, out_f, a.bias, y, y_dtype, ld_y);
+    PE_CUDA_TRY(cudaGetLastError());
+  }
   return PE_OK;
 }
 
@@ -1274,7 +1337,7 @@ extern "C" int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, 
   a.M = rows; a.N = out_f; a.K = in_f_padded;
   a.tiles_m = 1; a.tiles_n = tiles_n;
   a.status = status;
-  a.gtiles = tiles; a.n_gtiles = n_tiles; a.grp_norm_stride = norms_stride; a.y_tma = 0;
+  a.gtiles = tiles; a.n_gtiles = n_tiles; a.grp_norm_stride = norms_stride; a.y_tma = 0; a.ksplit = 1; a.part = nullptr;
   a.lut_bytes = (packed ? 256 : n_levels) * 128;
   const int code_row = packed ? 32 : 64;
   const int code_stage = kTileN * code_row;

@@ -16,7 +16,7 @@ def quant_gemm(codes: torch.Tensor, packed: bool, norms: torch.Tensor, ct: torch
     dev = x.device
     l = nv.lib()
     m = x.shape[0]
-    ws = nv.gemm_workspace(dev, l.pe_gemm_workspace_bytes(m, in_f_padded))
+    ws = nv.gemm_workspace(dev, l.pe_gemm_workspace_bytes_splitk(m, out_f, in_f_padded))
     nv.check(l.pe_gemm(codes.data_ptr(), int(packed), codes.stride(0) * codes.element_size(), norms.data_ptr(),
                        norms.stride(0), ct.data_ptr(), ct.numel(), x.data_ptr(),
                        nv.PE_X_ROTATED if rotated else nv.PE_X_RAW, nv.dtype_code(x), x.stride(0), in_f, y.data_ptr(),
