@@ -667,7 +667,16 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
   const uint32_t tmem = *tmem_slot;
 
   const int ksteps = p.K / kStepK;
-  const int n_tiles = p.tiles_m * p.tiles_n;
+  // A unit of work is a tile or, when the launch has few tiles, one of `ksplit` K ranges of a tile (fp32 partials
+  // in the workspace, summed by a second kernel).
+  const int n_tiles = p.tiles_m * p.tiles_n * p.ksplit;
+  auto unit_of = [&](int unit, int& split, int& ks0, int& ks1) {
+    const int tile = unit / p.ksplit;
+    split = unit - tile * p.ksplit;
+    ks0 = (int)((long long)split * ksteps / p.ksplit);
+    ks1 = (int)((long long)(split + 1) * ksteps / p.ksplit);
+    return tile;
+  };
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
   if (warp == 0) {
@@ -676,10 +685,12 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     if (lane == 0) {
       const uint32_t lead = map_to_cta(bars, 0) - bars;
       int it = 0;
-      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
+      for (int unit = pair; unit < n_tiles && !*abort_flag; unit += n_pairs) {
+        int split, ks0, ks1;
+        const int tile = unit_of(unit, split, ks0, ks1);
         const int m0 = (tile % p.tiles_m) * kPairTileM;
         const bool two = m0 + 256 < p.M;
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        for (int ks = ks0; ks < ks1; ++ks, ++it) {
           const int sx = it % kPairXStages;
           if (!mbar_wait(empty_x(sx), ((it / kPairXStages) & 1) ^ 1, abort_flag, p.status, 1)) goto done_producer;
           if (leader) mbar_expect_tx(full_x(sx), 2 * (two ? 2 * kXTileBytes : kXTileBytes));
@@ -693,9 +704,11 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     // ---------------- TMA producer: this CTA's code rows (a thread of its own: it runs ahead of the activations) ----------------
     if (lane == 0) {
       int it = 0;
-      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
+      for (int unit = pair; unit < n_tiles && !*abort_flag; unit += n_pairs) {
+        int split, ks0, ks1;
+        const int tile = unit_of(unit, split, ks0, ks1);
         const int n0 = (tile / p.tiles_m) * kTileN;
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        for (int ks = ks0; ks < ks1; ++ks, ++it) {
           const int sc = it % p.nc;
           if (!mbar_wait(empty_c(sc), ((it / p.nc) & 1) ^ 1, abort_flag, p.status, 6)) goto done_codes;
           mbar_expect_tx(full_c(sc), kCodeStage);
@@ -710,12 +723,14 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
       const uint32_t peer = map_to_cta(bars, 1) - bars;  // same barrier, odd CTA
       const uint32_t peer_acc_full = acc_full + peer;
       int it = 0, tcount = 0;
-      for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
+      for (int unit = pair; unit < n_tiles && !*abort_flag; unit += n_pairs, ++tcount) {
+        int split, ks0, ks1;
+        const int tile = unit_of(unit, split, ks0, ks1);
         const int m0 = (tile % p.tiles_m) * kPairTileM;
         const bool two = m0 + 256 < p.M;
         if (tcount > 0 && !mbar_wait_cluster(acc_empty, (tcount - 1) & 1, abort_flag, p.status, 9)) goto done_mma;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        for (int ks = ks0; ks < ks1; ++ks, ++it) {
           const int sx = it % kPairXStages, sw = it % kPairWStages;
           if (!mbar_wait_cluster(full_x(sx), (it / kPairXStages) & 1, abort_flag, p.status, 2)) goto done_mma;
           if (!mbar_wait_cluster(full_w(sw), (it / kPairWStages) & 1, abort_flag, p.status, 3)) goto done_mma;
@@ -724,7 +739,7 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
 #pragma unroll
           for (int kk = 0; kk < kStepK / 16; ++kk) {
             const uint64_t db = smem_desc_sw128(wb + kk * 32);
-            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+            const uint32_t acc = (ks > ks0 || kk > 0) ? 1u : 0u;
             umma_pair_bf16(tmem, smem_desc_sw128(xa + kk * 32), db, kIdescPair, acc);
             if (two) umma_pair_bf16(tmem + 256, smem_desc_sw128(xa + kXTileBytes + kk * 32), db, kIdescPair, acc);
           }
@@ -759,15 +774,23 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
     const int sw7 = r & 7;
     const uint32_t lead = map_to_cta(bars, 0) - bars;
     int it = 0, tcount = 0;
-    for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
+    for (int unit = pair; unit < n_tiles && !*abort_flag; unit += n_pairs, ++tcount) {
+      int split, ks0, ks1;
+      const int tile = unit_of(unit, split, ks0, ks1);
       const int m0 = (tile % p.tiles_m) * kPairTileM, n0 = (tile / p.tiles_m) * kTileN;
       const bool two = m0 + 256 < p.M;
+      // where this unit's result goes: the output, or (K split) the fp32 partial of its K range
+      void* const y_ptr = p.ksplit > 1 ? static_cast<void*>(p.part + (size_t)split * p.M * p.N) : p.y;
+      const int y_dt = p.ksplit > 1 ? (int)PE_F32 : p.y_dtype;
+      const int64_t y_ld = p.ksplit > 1 ? (int64_t)p.N : p.ld_y;
+      const __half* const bias_ptr = p.ksplit > 1 ? nullptr : p.bias;
+      const bool tma_out = p.y_tma && p.ksplit == 1;
       int row = n0 + (int)rank * 128 + r;
       const bool row_ok = row < p.N;
       if (!row_ok) row = p.N - 1;
       const unsigned short* nrow = reinterpret_cast<const unsigned short*>(p.norms + (int64_t)row * p.ld_norms);
       bool dead = false;
-      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+      for (int ks = ks0; ks < ks1; ++ks, ++it) {
         if ((it & (kPairGroups - 1)) != g) continue;  // warp-uniform
         const float nf = row_ok ? __half2float(__ushort_as_half(__ldg(nrow + (ks >> 1)))) : 0.f;  // in flight across the waits
         const int sc = it % p.nc;
@@ -846,7 +869,7 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
         if (!__all_sync(0xffffffffu, ok)) break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (p.y_tma) {
+      if (tma_out) {
         // 16-bit output: every warp stages its 32 rows x 32 columns (2 KB, 64-byte swizzle) in its own piece of the
         // weight stages -- idle now: all MMAs are done and no warp decodes before the staging barrier below -- and one
         // lane sends it off as a TMA store, which writes whole 64-byte row pieces and clips at the matrix edges.
@@ -898,27 +921,27 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           const int nb0 = n0 + cc * 32;
           if (m < p.M && nb0 < p.N) {
-            const bool full = nb0 + 32 <= p.N && (p.ld_y % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
-            if (full && p.y_dtype != PE_F32) {
+            const bool full = nb0 + 32 <= p.N && (y_ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(y_ptr) & 15) == 0);
+            if (full && y_dt != PE_F32) {
               uint32_t o[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 float a = __uint_as_float(rr[2 * j]), b = __uint_as_float(rr[2 * j + 1]);
-                if (p.bias) { a += __half2float(p.bias[nb0 + 2 * j]); b += __half2float(p.bias[nb0 + 2 * j + 1]); }
-                o[j] = p.y_dtype == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
+                if (bias_ptr) { a += __half2float(bias_ptr[nb0 + 2 * j]); b += __half2float(bias_ptr[nb0 + 2 * j + 1]); }
+                o[j] = y_dt == PE_F16 ? pack_half2(a, b) : pack_bf16(a, b);
               }
-              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.y) + (int64_t)m * p.ld_y + nb0);
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(y_ptr) + (int64_t)m * y_ld + nb0);
 #pragma unroll
               for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-            } else if (p.y_dtype == PE_F32 && nb0 + 32 <= p.N && (p.ld_y % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0)) {
-              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (int64_t)m * p.ld_y + nb0);
+            } else if (y_dt == PE_F32 && nb0 + 32 <= p.N && (y_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(y_ptr) & 15) == 0)) {
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(y_ptr) + (int64_t)m * y_ld + nb0);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 float4 v = make_float4(__uint_as_float(rr[4 * j]), __uint_as_float(rr[4 * j + 1]), __uint_as_float(rr[4 * j + 2]),
                                        __uint_as_float(rr[4 * j + 3]));
-                if (p.bias) {
-                  v.x += __half2float(p.bias[nb0 + 4 * j]); v.y += __half2float(p.bias[nb0 + 4 * j + 1]);
-                  v.z += __half2float(p.bias[nb0 + 4 * j + 2]); v.w += __half2float(p.bias[nb0 + 4 * j + 3]);
+                if (bias_ptr) {
+                  v.x += __half2float(bias_ptr[nb0 + 4 * j]); v.y += __half2float(bias_ptr[nb0 + 4 * j + 1]);
+                  v.z += __half2float(bias_ptr[nb0 + 4 * j + 2]); v.w += __half2float(bias_ptr[nb0 + 4 * j + 3]);
                 }
                 dst[j] = v;
               }
@@ -927,8 +950,8 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
               for (int j = 0; j < 32; ++j) {
                 if (nb0 + j < p.N) {
                   float a = __uint_as_float(rr[j]);
-                  if (p.bias) a += __half2float(p.bias[nb0 + j]);
-                  store_from_float(p.y, p.y_dtype, (int64_t)m * p.ld_y + nb0 + j, a);
+                  if (bias_ptr) a += __half2float(bias_ptr[nb0 + j]);
+                  store_from_float(y_ptr, y_dt, (int64_t)m * y_ld + nb0 + j, a);
                 }
               }
             }
@@ -943,7 +966,7 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
         if (leader) mbar_arrive(acc_empty);
         else mbar_arrive_remote(acc_empty + lead);
       }
-      if (p.y_tma) {
+      if (tma_out) {
         // no warp writes a weight stage of the next tile before every warp's staging has been read
         if (lane == 0) {
           asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -1106,6 +1129,15 @@ static int gemm_ksplit(int m, int out_f, int in_f_padded, int sms) {
   return s < 2 ? 1 : s;
 }
 
+// K ranges per 512-row pair tile: as many as there are idle pairs, at least eight K steps each; two ranges only for a
+// long K (the fp32 partials and their sum cost about what halving a short tile saves).
+static int pair_ksplit(int ptiles, int ksteps, int sms) {
+  int ks = (sms / 2) / ptiles;
+  if (ks > ksteps / 8) ks = ksteps / 8;
+  if (ks == 2 && ksteps < 128) ks = 1;
+  return ks < 2 ? 1 : ks;
+}
+
 // workspace: [status word, padded to 256 B][bf16 activations M x K]
 extern "C" size_t pe_gemm_workspace_bytes(int m, int in_f_padded) {
   if (m < 1 || in_f_padded < kBlock || in_f_padded % kBlock) return 0;
@@ -1117,7 +1149,11 @@ extern "C" size_t pe_gemm_workspace_bytes_splitk(int m, int out_f, int in_f_padd
   const size_t base = pe_gemm_workspace_bytes(m, in_f_padded);
   if (base == 0 || out_f < 1) return 0;
   const int sms = sm_count();
-  const int ks = sms > 0 ? gemm_ksplit(m, out_f, in_f_padded, sms) : 1;
+  int ks = sms > 0 ? gemm_ksplit(m, out_f, in_f_padded, sms) : 1;
+  if (m > 256 && sms >= 2) {  // pairs of CTAs, 512-row tiles, at least eight K steps per unit
+    const int ptiles = ((m + kPairTileM - 1) / kPairTileM) * ((out_f + kTileN - 1) / kTileN);
+    ks = pair_ksplit(ptiles, in_f_padded / kStepK, sms);
+  }
   return ks > 1 ? ((base + 255) & ~(size_t)255) + (size_t)ks * m * out_f * sizeof(float) : base;
 }
 
@@ -1213,7 +1249,15 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
                 CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
           return PE_ERR_CUDA;
       }
-      const int pair_tiles = a.tiles_m * a.tiles_n;
+      // few pair tiles: split K when the workspace has room for the partials
+      {
+        const int ptiles = a.tiles_m * a.tiles_n, ksteps = in_f_padded / kStepK;
+        a.ksplit = pair_ksplit(ptiles, ksteps, sms);
+        const size_t part_off = (pe_gemm_workspace_bytes(m, in_f_padded) + 255) & ~(size_t)255;
+        if (a.ksplit > 1 && workspace_bytes < part_off + (size_t)a.ksplit * m * out_f * sizeof(float)) a.ksplit = 1;
+        a.part = a.ksplit > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + part_off) : nullptr;
+      }
+      const int pair_tiles = a.tiles_m * a.tiles_n * a.ksplit;
       const int pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * pairs);
@@ -1232,9 +1276,16 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
         PE_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
         PE_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<false>, a, map, pmap, ymap));
       }
+      if (a.ksplit > 1) {
+        const int64_t total = (int64_t)m * out_f;
+        const unsigned rgrid = (unsigned)((total + 255) / 256 < (int64_t)sms * 8 ? (total + 255) / 256 : (int64_t)sms * 8);
+        gemm_splitk_reduce_kernel<<<rgrid, 256, 0, st>>>(a.part, a.ksplit, m, out_f, a.bias, y, y_dtype, ld_y);
+        PE_CUDA_TRY(cudaGetLastError());
+      }
       return PE_OK;
     }
     a.tiles_m = (m + kTileM - 1) / kTileM;
+    a.ksplit = 1; a.part = nullptr;
     a.nc = kGroups;
     a.lut_bytes = (packed ? 256 : n_levels) * 128;
   }
