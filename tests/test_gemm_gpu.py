@@ -92,6 +92,37 @@ def test_gemm_paired_ctas_ragged_edges_bias_and_dtypes(m, n):
     assert max_rel(y5, oracle.linear_dequant(x, c5, n5, t5, in_f=in_f)) <= TOL
 
 
+def test_gemm_few_tiles_with_and_without_room_for_the_k_split():
+    """A launch of up to 256 rows on few 256-row tiles splits K over the SMs when the workspace holds the fp32
+    partials (pe_gemm_workspace_bytes_splitk) and runs unsplit in a workspace of pe_gemm_workspace_bytes: same
+    values either way (only the order of the fp32 sums differs), bias and output type included."""
+    from polarengine_vllm_b200 import _native as nv, packing
+    dev = torch.device("cuda")
+    nv.ensure_init(dev)
+    m, n, k, bits = 96, 1024, 4096, 4
+    codes, norms, cts = rand_layer(n, k, bits, seed=31)
+    bias = rand_x(1, n, seed=2).reshape(n)
+    x = rand_x(m, k, seed=8, dtype=torch.bfloat16)
+    ref = oracle.linear_dequant(x, codes, norms, cts) + bias.float()
+    w = packing.pack_codes_half_block(codes.to(dev))
+    nd, ctd, xd, bd = norms.to(dev), cts.to(dev), x.to(dev), bias.to(dev).half()
+    l = nv.lib()
+    small, large = l.pe_gemm_workspace_bytes(m, k), l.pe_gemm_workspace_bytes_splitk(m, n, k)
+    assert large > small
+    out = []
+    for size in (small, large):
+        ws = torch.zeros(size, dtype=torch.uint8, device=dev)
+        y = torch.full((m, n), float("nan"), dtype=torch.float16, device=dev)
+        nv.check(l.pe_gemm(w.data_ptr(), 1, w.stride(0), nd.data_ptr(), nd.stride(0), ctd.data_ptr(), ctd.numel(), xd.data_ptr(),
+                           nv.PE_X_RAW, nv.dtype_code(xd), xd.stride(0), k, y.data_ptr(), nv.dtype_code(y), y.stride(0),
+                           bd.data_ptr(), m, n, k, ws.data_ptr(), ws.numel(), nv.stream_ptr(dev)), "pe_gemm")
+        torch.cuda.synchronize()
+        assert int(ws[:4].view(torch.int32).item()) == 0
+        assert max_rel(y, ref) <= TOL
+        out.append(y.float())
+    assert max_rel(out[0], out[1]) <= 2e-3
+
+
 def test_gemm_rotated_input_and_reference_signature():
     """polar_gemm / polar_gemm_packed of the reference take fp32 x_transformed
     (polar_gemm.py:312-418) and agree with the decode kernel (reference self-test
