@@ -1000,7 +1000,8 @@ gemm_pair_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap, con
 // valid_rows[0] + valid_rows[1] rows exist (the rest of the list is undefined and is written as zeros).
 __global__ void __launch_bounds__(256) gemm_prep_kernel(const void* x, int x_kind, int x_dtype, int64_t ld_x, int in_f,
                                                         __nv_bfloat16* xq, int M, int K, int pair_layout, const int* x_rows,
-                                                        const int* valid_rows) {
+                                                        const int* valid_rows, int* status) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;  // the matmul's status word (it follows in stream order)
   // Grid-stride over the (row, block) items, four per trip with their loads issued together: one item is only 256
   // bytes in and 256 out, and a warp that handles one item per launch slot spends its life in launch and latency.
   constexpr int U = 4;
@@ -1180,11 +1181,10 @@ extern "C" int pe_gemm(const void* codes, int packed, int64_t ld_codes, const vo
 
   int* status = static_cast<int*>(workspace);
   __nv_bfloat16* xq = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(workspace) + 256);
-  PE_CUDA_TRY(cudaMemsetAsync(status, 0, 4, st));
   const int nb = in_f_padded / kBlock;
   const int64_t warps = (int64_t)m * nb;
   gemm_prep_kernel<<<prep_grid(warps, sms), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, m, in_f_padded,
-                                                           packed ? 1 : 0, nullptr, nullptr);
+                                                           packed ? 1 : 0, nullptr, nullptr, status);
   PE_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap map;
@@ -1360,14 +1360,13 @@ extern "C" int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, 
   int* n_tiles = reinterpret_cast<int*>(ws + 256);
   int4* tiles = reinterpret_cast<int4*>(ws + 512);
   __nv_bfloat16* xq = reinterpret_cast<__nv_bfloat16*>(ws + 512 + list_bytes);
-  PE_CUDA_TRY(cudaMemsetAsync(status, 0, 4, st));
-  const int tiles_n = (out_f + kTileN - 1) / kTileN;
+  const int tiles_n = (out_f + kTileN - 1) / kTileN;  // (the preparation kernel clears the status word)
   gemm_group_tiles_kernel<<<1, 256, 0, st>>>(expert_rows, n_experts, tiles_n, max_tiles, tiles, n_tiles);
   PE_CUDA_TRY(cudaGetLastError());
   const int nb = in_f_padded / kBlock;
   const int64_t warps = (int64_t)rows * nb;
   gemm_prep_kernel<<<prep_grid(warps, sms), 256, 0, st>>>(x, x_kind, x_dtype, ld_x, in_f, xq, rows, in_f_padded,
-                                                           packed ? 1 : 0, x_rows, expert_rows + 2 * (n_experts - 1));
+                                                           packed ? 1 : 0, x_rows, expert_rows + 2 * (n_experts - 1), status);
   PE_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap map;
