@@ -231,6 +231,13 @@ int pe_gemm_grouped(const void* codes, int packed, int64_t ld_codes, int64_t cod
                     int64_t ld_y, const int32_t* expert_rows, int n_experts, int rows, int out_f, int in_f_padded,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Routing of a mixture layer as one launch (nemotron_offload.py:180-189): fp32 softmax of the router logits over
+ * the experts, the top_k largest in descending order (ties to the lower expert id), kept weights divided by
+ * their sum when `renormalize`.  logits (n_tokens, n_experts) fp32 / fp16 / bf16 with row stride ld_logits;
+ * weights (n_tokens, top_k) fp32 and ids (n_tokens, top_k) int64 out.  n_experts <= 1024, top_k <= 32. */
+int pe_moe_route(const void* logits, int dtype, int64_t ld_logits, int n_tokens, int n_experts, int top_k, int renormalize,
+                 float* weights, int64_t* ids, void* stream);
+
 /* ---- mixture-of-experts bookkeeping on the device ----------------------------------
  * pe_moe_plan groups the (token, slot) pairs of a routing decision by local expert:
  *   topk_ids (n_pairs = tokens * top_k, int64, token-major); expert_map (optional, int64,

@@ -39,6 +39,7 @@ SIGNATURES = {
     "pe_gemv_grouped_workspace_bytes": (_sz, [_i, _i, _i]),
     "pe_gemv_grouped": (_i, [_vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _vp, _i, _i64, _vp,
                             _i, _i, _i, _i, _vp, _sz, _vp]),
+    "pe_moe_route": (_i, [_vp, _i, _i64, _i, _i, _i, _i, _vp, _vp, _vp]),
     "pe_moe_plan": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "pe_gemm_grouped_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pe_gemm_grouped": (_i, [_vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i, _i64, _i, _vp, _vp, _i, _i64, _vp,

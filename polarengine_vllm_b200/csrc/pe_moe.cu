@@ -93,6 +93,69 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int64_
   store_from_float(out, out_dtype, t * ld_out + col + 3, acc.w);
 }
 
+// Routing of the reference's mixture layer (nemotron_offload.py:180-189) as one launch: fp32 softmax over the experts,
+// the top_k largest (ties go to the lower expert id, as a stable descending sort would have them), optional
+// renormalisation of the kept weights.  One warp per token; lane l holds experts l, l + 32, ...
+constexpr int kRouteMaxPerLane = 32;  // up to 1024 experts
+__global__ void __launch_bounds__(256) moe_route_kernel(const void* logits, int dtype, int64_t ld, int n_tokens, int n_experts, int top_k,
+                                                        int renormalize, float* weights, int64_t* ids) {
+  const int lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= n_tokens) return;
+  float v[kRouteMaxPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = -INFINITY;
+    if (e < n_experts) {
+      const int64_t at = (int64_t)tok * ld + e;
+      v[i] = dtype == PE_F32 ? static_cast<const float*>(logits)[at]
+             : dtype == PE_F16 ? __half2float(static_cast<const __half*>(logits)[at])
+                               : __bfloat162float(static_cast<const __nv_bfloat16*>(logits)[at]);
+      mx = fmaxf(mx, v[i]);
+    }
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    if (lane + 32 * i < n_experts) { v[i] = expf(v[i] - mx); sum += v[i]; }
+    else v[i] = -1.f;  // never picked: probabilities are >= 0
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+  const float inv = 1.f / sum;
+  float kept = 0.f, my_w = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < top_k; ++k) {
+    float best = -1.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i)
+      if (v[i] > best) { best = v[i]; best_e = lane + 32 * i; }  // lowest slot of this lane first
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, m);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, m);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kRouteMaxPerLane; ++i)
+        if (i == (best_e >> 5)) v[i] = -1.f;
+    }
+    const float w = best * inv;
+    kept += w;
+    if (lane == k) { my_w = w; my_id = best_e; }  // top_k <= 32
+  }
+  if (lane < top_k) {
+    weights[(int64_t)tok * top_k + lane] = renormalize ? my_w / kept : my_w;
+    ids[(int64_t)tok * top_k + lane] = my_id;
+  }
+}
+
 }  // namespace pe
 
 using namespace pe;
@@ -127,6 +190,17 @@ extern "C" int pe_moe_combine(const float* y, int64_t ld_y, const int32_t* pos, 
   if (blocks > 0x7fffffff) return PE_ERR_LIMIT;
   moe_combine_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(y, ld_y, pos, topk_weights, top_k, out,
                                                                                     out_dtype, ld_out, hidden, n_vec);
+  PE_CUDA_TRY(cudaGetLastError());
+  return PE_OK;
+}
+
+extern "C" int pe_moe_route(const void* logits, int dtype, int64_t ld_logits, int n_tokens, int n_experts, int top_k, int renormalize,
+                            float* weights, int64_t* ids, void* stream) {
+  if (!logits || !weights || !ids || n_tokens < 1) return PE_ERR_ARG;
+  if (dtype < PE_F32 || dtype > PE_BF16 || ld_logits < n_experts) return PE_ERR_ARG;
+  if (n_experts < 1 || n_experts > 32 * kRouteMaxPerLane || top_k < 1 || top_k > 32 || top_k > n_experts) return PE_ERR_LIMIT;
+  moe_route_kernel<<<(unsigned)((n_tokens + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, dtype, ld_logits, n_tokens,
+                                                                                                 n_experts, top_k, renormalize, weights, ids);
   PE_CUDA_TRY(cudaGetLastError());
   return PE_OK;
 }

@@ -59,7 +59,21 @@ class PolarPassthroughMoEMethod:
 
 
 def route_softmax_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
-    """fp32 softmax over experts, top-k, optional renormalisation (nemotron_offload.py:180-189)."""
+    """fp32 softmax over experts, top-k, optional renormalisation (nemotron_offload.py:180-189).  On the GPU one launch
+    (``pe_moe_route``); the torch ops below are the same math for CPU tensors."""
+    if router_logits.is_cuda and router_logits.dim() == 2 and router_logits.shape[1] <= 1024 and top_k <= 32 \
+            and router_logits.dtype in (torch.float32, torch.float16, torch.bfloat16):
+        from . import _native as nv
+        dev = router_logits.device
+        nv.ensure_init(dev)
+        lg = router_logits if router_logits.stride(1) == 1 else router_logits.contiguous()
+        t, e = lg.shape
+        w = torch.empty(t, top_k, dtype=torch.float32, device=dev)
+        ids = torch.empty(t, top_k, dtype=torch.int64, device=dev)
+        if t:
+            nv.check(nv.lib().pe_moe_route(lg.data_ptr(), nv.dtype_code(lg), lg.stride(0), t, e, top_k, int(bool(renormalize)),
+                                           w.data_ptr(), ids.data_ptr(), nv.stream_ptr(dev)), "pe_moe_route")
+        return w, ids
     p = torch.softmax(router_logits.float(), dim=-1)
     w, ids = p.topk(top_k, dim=-1)
     if renormalize:

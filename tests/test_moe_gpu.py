@@ -110,3 +110,32 @@ def test_moe_benchmark_configuration(tokens):
     sample = torch.arange(tokens) if tokens <= 64 else torch.randperm(tokens, generator=g)[:24].sort().values
     ref = oracle.moe_forward(x[sample], w[sample], ids[sample], experts)
     assert max_rel(y[sample.cuda()], ref) <= 1e-2
+
+
+@pytest.mark.parametrize("t,e,k", [(1, 128, 8), (64, 128, 8), (300, 60, 4), (7, 1000, 32)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_routing_kernel_matches_softmax_topk(t, e, k, dtype):
+    """pe_moe_route = softmax (fp32) -> top-k -> renormalise of nemotron_offload.py:180-189: the same weights as
+    torch.topk on the same logits to fp32 rounding (and the same experts in the same order where no two logits are
+    equal); with and without renormalisation."""
+    from polarengine_vllm_b200.moe_method import route_softmax_topk
+    g = torch.Generator().manual_seed(t + e)
+    logits = (torch.randn(t, e, generator=g) * 3).to(dtype)
+    for renorm in (True, False):
+        w, ids = route_softmax_topk(logits.cuda(), k, renorm)
+        p = torch.softmax(logits.float(), dim=-1)
+        rw, rids = p.topk(k, dim=-1)
+        if renorm:
+            rw = rw / rw.sum(-1, keepdim=True)
+        assert ids.dtype == torch.int64 and w.dtype == torch.float32
+        w, ids = w.cpu(), ids.cpu()
+        # the k largest probabilities in descending order (equal logits -- common in 16-bit -- may swap places or, at
+        # the k-th place, experts: either choice is a valid top-k), each weight being its own expert's probability
+        assert torch.allclose(w, rw, rtol=1e-5, atol=1e-7)
+        own = p.gather(1, ids)
+        if renorm:
+            own = own / own.sum(-1, keepdim=True)
+        assert torch.allclose(w, own, rtol=1e-5, atol=1e-7)
+        assert all(len(set(r.tolist())) == k for r in ids)
+        if dtype == torch.float32:
+            assert torch.equal(ids, rids)
