@@ -17,7 +17,7 @@ The same run then measures the rest of the metric and reports it as extra keys o
 `prefill` (4096 bf16 tokens through the tensor-core kernel on the three layer shapes), `model_decode`
 (the 36-layer decoder, tensor parallel over the N ranks, batch 1 and 8, with a numeric check of the
 sharded model against the un-sharded one) and `moe` (128-expert layer, expert parallel over the N
-ranks, 64 and 2048 tokens).  `--workload prefill|model|moe` runs one of them alone with its own line.
+ranks, 1, 64 and 2048 tokens).  `--workload prefill|model|moe` runs one of them alone with its own line.
 """
 import argparse
 import json
@@ -410,7 +410,7 @@ def moe_run(dev, rank, world, tokens, steps=None):
     return rec
 
 
-def moe_record(dev, rank, world, token_counts=(64, 2048)):
+def moe_record(dev, rank, world, token_counts=(1, 64, 2048)):
     rec = {"config": "128 experts top-8, hidden 2688, intermediate 1856, gate/up Q3, down Q4; expert weights 970 MB >> L2"}
     for t in token_counts:
         rec[f"tokens{t}"] = moe_run(dev, rank, world, t)
@@ -465,7 +465,7 @@ def main():
     ap.add_argument("--nccl-allreduce", action="store_true", help="model record: NCCL all-reduce instead of the fused peer-memory epilogue")
     ap.add_argument("--m", type=int, default=4096, help="tokens of the prefill record")
     ap.add_argument("--bits", type=int, default=4, choices=[3, 4, 5, 6], help="prefill workload alone: code width of the layers")
-    ap.add_argument("--tokens", type=int, default=None, help="moe workload alone: one token count instead of 64 and 2048")
+    ap.add_argument("--tokens", type=int, default=None, help="moe workload alone: one token count instead of 1, 64 and 2048")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -520,7 +520,7 @@ def main():
                         config={"workload": f"model_decode (BASELINE configs[3]): {a.layers} layers", "batch": a.batch,
                                 "parallelism": f"tp{world}"}, model_decode=rec, gpu_launches=a.new_tokens * rec["gpu_launches_per_step"])
         else:
-            rec = moe_record(dev, rank, world, (a.tokens,) if a.tokens else (64, 2048))
+            rec = moe_record(dev, rank, world, (a.tokens,) if a.tokens else (1, 64, 2048))
             first = next(v for k, v in rec.items() if k.startswith("tokens"))
             line = dict(common, metric="MoE layer tokens/s", unit="tok/s", value=first["tok_s"], steps=first["steps"],
                         ms_per_step=first["ms_per_layer"], scaling="strong", dtype="f16",
