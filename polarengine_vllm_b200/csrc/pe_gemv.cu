@@ -1124,7 +1124,9 @@ namespace pe {
 constexpr size_t kGroupedCounterZone = 4u << 20;
 static size_t grouped_cnt_bytes(int n_rt16) { return ((size_t)(n_rt16 + 1) * 4 + 255) & ~(size_t)255; }
 static int grouped_ctas(int max_problems, long long S, int sms) {
-  long long g = (2ll * sms) / max_problems;  // about two CTAs per SM-slot over all problems
+  // one CTA per SM over all problems when there are few of them (a CTA fills an SM: a second wave of CTAs only
+  // repeats the per-CTA set-up on half the bytes), about two per SM-slot otherwise (problems differ in size)
+  long long g = (max_problems * 8 <= sms ? 1ll * sms : 2ll * sms) / max_problems;
   if (g < 1) g = 1;
   if (g > sms) g = sms;
   if (g > S / 16) g = S / 16 < 1 ? 1 : S / 16;
